@@ -1,0 +1,87 @@
+// Shared declarations of the kernel library: element types, the error channel
+// and small device helpers. Every launcher is `extern "C"`, takes raw device
+// pointers and a stream, validates its arguments on the host, returns 0 on
+// success and a non-zero code with a message in `fb_last_error()` otherwise.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#define FB_API extern "C" __attribute__((visibility("default")))
+
+// Element types as the Python side names them.
+enum FbDType : int { FB_F32 = 0, FB_BF16 = 1 };
+
+// Tokens per cache page: the unit in which sequences take and give back cache
+// memory. Kernels index a key at position p as page_table[p / 64], row p % 64.
+constexpr int FB_PAGE = 64;
+
+int fb_fail(int code, const char* fmt, ...);  // records the message, returns code
+int fb_check_launch(const char* what);        // cudaGetLastError -> code
+
+#define FB_REQUIRE(cond, ...)                      \
+  do {                                             \
+    if (!(cond)) return fb_fail(1, __VA_ARGS__);   \
+  } while (0)
+
+// ---------------------------------------------------------------- device side
+template <typename T>
+__device__ __forceinline__ float fb_to_float(T v);
+template <>
+__device__ __forceinline__ float fb_to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float fb_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+
+template <typename T>
+__device__ __forceinline__ T fb_from_float(float v);
+template <>
+__device__ __forceinline__ float fb_from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 fb_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float fb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float fb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `scratch` holds 32 floats of shared memory. Every thread of
+// the block must call it; the result is returned to all of them.
+__device__ __forceinline__ float fb_block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = fb_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  t = fb_warp_sum(t);
+  return t;
+}
+
+// Dispatch a host-side dtype code to a template parameter.
+#define FB_DISPATCH_DTYPE(code, T, ...)                                   \
+  do {                                                                    \
+    if ((code) == FB_F32) {                                               \
+      using T = float;                                                    \
+      __VA_ARGS__;                                                        \
+    } else if ((code) == FB_BF16) {                                       \
+      using T = __nv_bfloat16;                                            \
+      __VA_ARGS__;                                                        \
+    } else {                                                              \
+      return fb_fail(1, "unknown element type code %d", (int)(code));    \
+    }                                                                     \
+  } while (0)

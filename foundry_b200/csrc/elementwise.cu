@@ -1,0 +1,159 @@
+// Row-wise kernels around the matrix products: token embedding gather,
+// residual add fused with RMS normalisation, SiLU(gate) * up, row gather.
+//
+// Formulas (reference file:line, by its path in stratorys/foundry):
+//   embedding  x[t,:] = E[ids[t],:]; an id outside the table gives a zero row
+//              (src/nn/linear.rs:54-69, src/metal/kernels/index_select.metal:23-26)
+//   RMS norm   r = 1/sqrt(sum(x^2) * (1/H) + eps); y = x * r * w, in 32-bit
+//              (src/nn/norm.rs:31-51)
+//   residual   h = x + delta (src/models/llama/model.rs:272, 277); here the sum
+//              is kept in 32-bit and never rounded to 16 bits
+//   SiLU       a = g / (1 + exp(-g)) in 32-bit, then a * u
+//              (src/nn/activation.rs:18-27, src/models/llama/mlp.rs:56)
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (size_t)t * H;
+  if (id < 0 || id >= V) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = fb_to_float<T>(src[i]);
+}
+
+FB_API int fb_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T,
+                           int H, int V, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
+  if (T == 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  FB_DISPATCH_DTYPE(table_dtype, E, (embed_gather_kernel<E><<<T, threads, 0, stream>>>(
+                                        (const E*)table, ids, out, H, V)));
+  return fb_check_launch("embed_gather");
+}
+
+// ------------------------------------------------- residual add + RMS norm
+// resid[t,:] += delta[t,:] (if delta), then out[t,:] = resid * r * w.
+// One block per row; the row is re-read from `resid`, which the same thread
+// wrote, so no synchronisation is needed between the two passes.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const float* __restrict__ weight, TO* __restrict__ out, int H,
+                                   float eps, float inv_h) {
+  __shared__ float scratch[32];
+  const size_t row = (size_t)blockIdx.x * H;
+  float* x = resid + row;
+  float ss = 0.f;
+  if (delta != nullptr) {
+    const TD* d = delta + row;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = x[i] + fb_to_float<TD>(d[i]);
+      x[i] = v;
+      ss += v * v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float v = x[i];
+      ss += v * v;
+    }
+  }
+  ss = fb_block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss * inv_h + eps);
+  if (out != nullptr) {
+    TO* y = out + row;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+      y[i] = fb_from_float<TO>(x[i] * r * weight[i]);
+  }
+}
+
+FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* weight,
+                          float eps, void* out, int out_dtype, int T, int H,
+                          cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0, "add_rmsnorm: bad sizes T=%d H=%d", T, H);
+  FB_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+  if (T == 0) return 0;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  const float inv_h = 1.0f / (float)H;
+  FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (
+      add_rmsnorm_kernel<TD, TO><<<T, threads, 0, stream>>>(
+          resid, (const TD*)delta, weight, (TO*)out, H, eps, inv_h))));
+  return fb_check_launch("add_rmsnorm");
+}
+
+// ------------------------------------------------------------- SiLU(g) * u
+// gate_up is [T, 2I]: columns [0, I) hold the gate, [I, 2I) the up projection.
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I,
+                                size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = fb_to_float<T>(gate_up[t * 2 * I + i]);
+    const float u = fb_to_float<T>(gate_up[t * 2 * I + I + i]);
+    const float a = g / (1.0f + expf(-g));
+    out[idx] = fb_from_float<T>(a * u);
+  }
+}
+
+FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I,
+                       cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T, I);
+  const size_t total = (size_t)T * I;
+  if (total == 0) return 0;
+  const int threads = 256;
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  FB_DISPATCH_DTYPE(dtype, E, (silu_mul_kernel<E><<<blocks, threads, 0, stream>>>(
+                                  (const E*)gate_up, (E*)out, I, total)));
+  return fb_check_launch("silu_mul");
+}
+
+// ---------------------------------------------------------------- row gather
+// dst[r,:] = src[rows[r],:]; a negative row index gives a zero row.
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
+                                   T* __restrict__ dst, int H) {
+  const int r = blockIdx.x;
+  const int s = rows[r];
+  T* d = dst + (size_t)r * H;
+  if (s < 0) {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = fb_from_float<T>(0.f);
+    return;
+  }
+  const T* p = src + (size_t)s * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) d[i] = p[i];
+}
+
+FB_API int fb_gather_rows(const void* src, int dtype, const int* rows, void* dst, int n, int H,
+                          cudaStream_t stream) {
+  FB_REQUIRE(n >= 0 && H > 0, "gather_rows: bad sizes n=%d H=%d", n, H);
+  if (n == 0) return 0;
+  FB_DISPATCH_DTYPE(dtype, E, (gather_rows_kernel<E><<<n, 256, 0, stream>>>(
+                                  (const E*)src, rows, (E*)dst, H)));
+  return fb_check_launch("gather_rows");
+}
+
+// ----------------------------------------------------------------------- cast
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    out[i] = fb_from_float<TO>(fb_to_float<TI>(in[i]));
+}
+
+FB_API int fb_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n,
+                   cudaStream_t stream) {
+  FB_REQUIRE(n >= 0, "cast: negative count");
+  if (n == 0) return 0;
+  const size_t want = ((size_t)n + 255) / 256;
+  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (
+      cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, (size_t)n))));
+  return fb_check_launch("cast");
+}

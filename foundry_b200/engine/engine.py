@@ -1,0 +1,139 @@
+"""The engine: a loaded model, its cache, the step function and the loop.
+
+`Engine.step` is the one step function: a batch of sequences, each bringing
+its next tokens (a whole prompt, a chunk, or one token), run as one packed
+batch from the cache, returning float32 logits at the wanted places only.
+The reference's counterpart is `CausalLm::forward` + `Decoder`
+(src/models/mod.rs:19-27, src/generate/mod.rs:92-205), which takes equal
+lengths and one shared position.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.store import SequenceCache
+from ..config import load_model_config
+from ..config.spec import ModelSpec
+from ..sampling import Sampler, SamplingParams
+from ..weights.safetensors_io import WeightFiles
+from . import generate as loop
+from .context import SequenceStep, StepContext, build_context
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "f32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r}: choose bfloat16 or float32") from None
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda" or not torch.cuda.is_available():
+        raise RuntimeError(
+            f"the engine runs on CUDA devices only (asked for {device}, CUDA available: "
+            f"{torch.cuda.is_available()}); there is no CPU path")
+    return device
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, config, dtype=torch.bfloat16, device="cuda:0",
+                 max_tokens: int = 8192, max_slots: int = 256):
+        self.device = require_cuda(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = parse_dtype(dtype)
+        self.spec, self.config = spec, config
+        self.model = Model(spec, self.dtype, self.device)
+        self._cache_args = (max_tokens, max_slots)
+        self.cache: Optional[SequenceCache] = None
+        self.sampler = Sampler(self.device)
+        self.launch_count = 0
+
+    # ---------------------------------------------------------------- load
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0",
+                    max_tokens: int = 8192, max_slots: int = 256) -> "Engine":
+        """config.json picks the architecture; model.safetensors gives the weights."""
+        arch, config = load_model_config(model_dir)
+        engine = cls(arch.build_spec(config), config, dtype, device, max_tokens, max_slots)
+        engine.model.load(WeightFiles.open(model_dir))
+        engine._make_cache()
+        return engine
+
+    @classmethod
+    def from_random(cls, config, seed: int, dtype="bfloat16", device="cuda:0",
+                    max_tokens: int = 8192, max_slots: int = 256, std: float = 0.02,
+                    norm_std: float = 0.0) -> "Engine":
+        """Random weights made on the device (no folder): for measurements at
+        sizes whose files would take long to write."""
+        from ..config.registry import resolve_architecture
+        from ..weights.random_init import random_tensors
+        import foundry_b200.models  # noqa: F401
+        arch = resolve_architecture(config.to_json())
+        engine = cls(arch.build_spec(config), config, dtype, device, max_tokens, max_slots)
+        expected = engine.model.expected_tensors()
+        store = torch.bfloat16 if engine.dtype == torch.bfloat16 else torch.float32
+        # one tensor at a time: the float32 draw of a large matrix is freed at once
+        tensors = {}
+        for name, want in expected.items():
+            tensors.update(random_tensors({name: want}, seed, dtype=store, std=std,
+                                          norm_std=norm_std, device=str(engine.device)))
+        engine.model.load_tensors(tensors)
+        engine._make_cache()
+        return engine
+
+    def _make_cache(self) -> None:
+        max_tokens, max_slots = self._cache_args
+        self.cache = SequenceCache(self.model.cache_requests(), max_tokens, max_slots, self.dtype,
+                                   self.device)
+
+    # ------------------------------------------------------- StepBackend
+    def open_sequence(self) -> int:
+        return self.cache.open_sequence()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close_sequence(slot)
+
+    def free_slots(self) -> int:
+        return self.cache.table.slots.free
+
+    def free_tokens(self) -> int:
+        return self.cache.free_tokens()
+
+    def capacity_tokens(self) -> int:
+        return self.cache.max_tokens
+
+    def max_positions(self) -> int:
+        return self.spec.max_positions
+
+    # ---------------------------------------------------------------- step
+    def step(self, steps: Sequence[SequenceStep]) -> torch.Tensor:
+        """Run the given tokens from the cache; float32 logits [wanted, vocab]
+        in the order of `steps` and of each `want`."""
+        ctx = build_context(self.cache, steps, self.spec.vocab_size, self.device,
+                            self.spec.max_positions)
+        return self.model.forward(ctx, self.cache)
+
+    def step_select(self, steps: Sequence[SequenceStep], params: SamplingParams,
+                    keys: Sequence[int], counts: Sequence[int]) -> List[int]:
+        """A step whose wanted logits are turned into tokens on the device;
+        only the token ids cross to the host."""
+        logits = self.step(steps)
+        tokens = self.sampler.select(logits, params, keys, counts)
+        return tokens.tolist()
+
+    # ------------------------------------------------------------ generate
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int,
+                 eos_token_id: Optional[Sequence[int]] = None,
+                 sampling: SamplingParams = SamplingParams(), max_batch: Optional[int] = None,
+                 ignore_eos: bool = False) -> loop.Generation:
+        stops = self.spec.eos_token_ids if eos_token_id is None else tuple(eos_token_id)
+        return loop.generate(self, prompts, max_new_tokens, stops, sampling, max_batch, ignore_eos)

@@ -1,0 +1,79 @@
+"""Grouped-query attention over the cache, as a mixer.
+
+q = n Wq^T, k = n Wk^T, v = n Wv^T (one fused product); q and k are rotated by
+the position encoding; k and v are appended to the sequence's cache pages;
+every token attends causally to its sequence's cache; o = attn Wo^T
+(src/models/llama/attention.rs:72-131). Query head a reads key-value head
+a // (heads // kv_heads) (src/nn/attention.rs:40-44); scores are scaled by
+1/sqrt(head_dim) (attention.rs:56-58). Unlike the reference, heads x head_dim
+need not equal the hidden size (it loads q_proj as [H, H], attention.rs:52).
+
+The part takes head counts, head size, window and its position encoding as
+parameters and asks the cache for keys and values of its shape; which layer
+of which model it serves is not its business.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..cache.store import KVRequest, KVView
+from ..config.spec import PartSpec
+from ..kernels import ops
+from ..weights.loader import ExpectedTensor
+from .base import POSITION_ENCODINGS, Fetch, Part, register_mixer
+from .linear import Linear
+
+
+@register_mixer("gqa_attention")
+class GQAAttention(Part):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position_encoding: Optional[PartSpec], window: Optional[int] = None, *,
+                 dtype: torch.dtype, device: torch.device):
+        if num_kv_heads <= 0 or num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 "
+                             f"from 16 to 256")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.window = head_dim, window
+        self.dtype, self.device = dtype, device
+        self.q_size, self.kv_size = num_heads * head_dim, num_kv_heads * head_dim
+        self.qkv = Linear(hidden_size, [("q_proj", self.q_size), ("k_proj", self.kv_size),
+                                        ("v_proj", self.kv_size)], dtype=dtype, device=device)
+        self.o = Linear(self.q_size, [("o_proj", hidden_size)], dtype=dtype, device=device)
+        if position_encoding is None:
+            self.rotary_dim = 0
+            self.inv_freq = torch.zeros(0, dtype=torch.float32, device=device)
+            factor = 1.0
+        else:
+            enc = POSITION_ENCODINGS.build(position_encoding, dtype=dtype, device=device)
+            self.rotary_dim, self.inv_freq, factor = enc.rotary_dim, enc.inv_freq, enc.attention_factor
+        self.scale = factor / math.sqrt(head_dim)
+
+    # ----------------------------------------------------------------- setup
+    def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
+        return {**self.qkv.expected_tensors(prefix), **self.o.expected_tensors(prefix)}
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        self.qkv.load(prefix, fetch)
+        self.o.load(prefix, fetch)
+
+    def cache_request(self) -> KVRequest:
+        return KVRequest(self.num_kv_heads, self.head_dim, self.window)
+
+    # ------------------------------------------------------------------- run
+    def forward(self, ctx, x: torch.Tensor, cache: KVView) -> torch.Tensor:
+        qkv = self.qkv.forward(x)
+        table = ctx.page_table(cache.group)
+        ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
+                          self.rotary_dim, cache.k, cache.v, self.num_heads, self.num_kv_heads,
+                          self.head_dim, ring_pages=cache.group.ring_pages,
+                          write_cache=cache.writes)
+        attn = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
+        ops.attention(ctx, qkv[:, :self.q_size], attn, table, cache.k, cache.v, self.num_heads,
+                      self.num_kv_heads, self.head_dim, self.scale, window=cache.group.window,
+                      ring_pages=cache.group.ring_pages)
+        return self.o.forward(attn)

@@ -1,0 +1,90 @@
+"""What every part of a layer is, and the registries they are looked up in.
+
+A layer is put together from parts: a mixer (attention here), a feed-forward,
+norms, a position encoding inside the mixer, and a block that arranges them.
+Each part takes its sizes and constants as parameters, names the tensors it
+loads, and runs on a `StepContext`; none knows which model it is in. The
+reference's counterparts are the structs of src/nn and src/models/llama, which
+are wired for one model (src/models/llama/model.rs:47-52).
+
+Interfaces
+----------
+Part (all kinds)
+    expected_tensors(prefix) -> {tensor name: ExpectedTensor}
+    load(prefix, fetch)            fetch(name) -> device tensor (stored dtype rule applied)
+Norm
+    add_norm(resid, delta, out)    resid += delta (float32, in place); out = norm(resid)
+PositionEncoding
+    inv_freq: float32 [rotary_dim / 2] on the device; rotary_dim; attention_factor
+Mixer
+    cache_request() -> KVRequest | StateRequest | None
+    forward(ctx, x, cache_view) -> y      x, y: [tokens, hidden] in the activation dtype
+FeedForward
+    forward(ctx, x) -> y
+Block
+    forward(ctx, resid, delta, cache_view) -> new delta (not yet added to resid)
+
+A new part is a class with these methods plus one `register_*` call; the
+engine builds it from `PartSpec(kind, params)` as `cls(**params, dtype=...,
+device=...)`.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, Optional
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.loader import ExpectedTensor
+
+Fetch = Callable[[str], torch.Tensor]
+
+
+class Part:
+    """Base of all parts: no tensors, nothing to load."""
+
+    def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
+        return {}
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        return None
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._classes: Dict[str, Any] = {}
+
+    def register(self, kind: str, cls=None, *, replace: bool = False):
+        def put(c):
+            if kind in self._classes and not replace:
+                raise ValueError(f"{self.what} {kind!r} is already registered")
+            self._classes[kind] = c
+            return c
+        return put if cls is None else put(cls)
+
+    def unregister(self, kind: str) -> None:
+        self._classes.pop(kind, None)
+
+    def kinds(self):
+        return sorted(self._classes)
+
+    def build(self, spec: PartSpec, **context):
+        try:
+            cls = self._classes[spec.kind]
+        except KeyError:
+            raise KeyError(f"no {self.what} named {spec.kind!r}; registered: {self.kinds()}") from None
+        return cls(**spec.params, **context)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")
+
+register_mixer = MIXERS.register
+register_feed_forward = FEED_FORWARDS.register
+register_norm = NORMS.register
+register_position_encoding = POSITION_ENCODINGS.register
+register_block = BLOCKS.register

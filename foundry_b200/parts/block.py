@@ -1,0 +1,58 @@
+"""The arrangement of a layer's parts.
+
+`pre_norm_residual` is the reference's decoder layer
+(src/models/llama/model.rs:254-278):
+
+    h = x + mixer(norm1(x));  x' = h + feed_forward(norm2(h))
+
+The residual stream is float32 and each sum is made in the kernel that also
+normalises for the next part, so a block receives the previous block's output
+still un-added (`delta`) and returns its own the same way.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..config.spec import LayerSpec
+from ..weights.loader import ExpectedTensor
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Fetch, Part, register_block
+
+
+@register_block("pre_norm_residual")
+class PreNormResidualBlock(Part):
+    def __init__(self, layer: LayerSpec, *, dtype: torch.dtype, device: torch.device):
+        ctx = dict(dtype=dtype, device=device)
+        self.prefix = layer.prefix
+        self.names = dict(layer.names)
+        self.mixer = MIXERS.build(layer.mixer, **ctx)
+        self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, **ctx)
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **ctx)
+        self.feed_forward_norm = NORMS.build(layer.feed_forward_norm, **ctx)
+
+    def _named(self):
+        p, n = self.prefix, self.names
+        return ((self.mixer_norm, f"{p}.{n['mixer_norm']}"),
+                (self.mixer, f"{p}.{n['mixer']}"),
+                (self.feed_forward_norm, f"{p}.{n['feed_forward_norm']}"),
+                (self.feed_forward, f"{p}.{n['feed_forward']}"))
+
+    def expected_tensors(self, prefix: str = "") -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for part, name in self._named():
+            out.update(part.expected_tensors(name))
+        return out
+
+    def load(self, prefix: str, fetch: Fetch) -> None:
+        for part, name in self._named():
+            part.load(name, fetch)
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], cache):
+        normed = self.mixer_norm.add_norm(resid, delta)
+        mixed = self.mixer.forward(ctx, normed, cache)
+        normed = self.feed_forward_norm.add_norm(resid, mixed)
+        return self.feed_forward.forward(ctx, normed)
