@@ -126,10 +126,12 @@ class SlotTable:
         self.slots = FreeList(slot_count, "slot")
         self.groups = groups
         self.length = [0] * slot_count
+        self.epoch = [0] * slot_count  # how often each slot has been opened
 
     def open(self) -> int:
         (slot,) = self.slots.take(1)
         self.length[slot] = 0
+        self.epoch[slot] += 1
         for group in self.groups:
             group.open(slot)
         return slot

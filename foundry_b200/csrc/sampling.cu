@@ -5,7 +5,7 @@
 // The reference samples in no other way. Temperature sampling is added with the
 // Gumbel-max rule: argmax_i(logit_i / T + g_i), g_i = -log(-log(u_i)), which
 // draws from softmax(logits / T) without a cumulative sum. u_i is a pure
-// function of (seed, stream key, step, i), so a sequence's draws do not depend
+// function of (seed, sequence key, step, i), so a sequence's draws do not depend
 // on the batch it runs in, and the host can restate them.
 #include "common.cuh"
 
@@ -18,20 +18,21 @@ __host__ __device__ __forceinline__ unsigned long long mix64(unsigned long long 
 }
 constexpr unsigned long long GOLDEN = 0x9e3779b97f4a7c15ULL;
 
-__device__ __forceinline__ float uniform24(unsigned long long seed, unsigned long long key,
-                                           unsigned long long step, unsigned long long i) {
-  unsigned long long z = mix64(seed + GOLDEN * (key + 1));
-  z = mix64(z + GOLDEN * (step + 1));
+// `stream` is mix64(seed + GOLDEN * (key + 1)), formed on the host once per
+// sequence, so that no launch argument changes from step to step.
+__device__ __forceinline__ float uniform24(unsigned long long stream, unsigned long long step,
+                                           unsigned long long i) {
+  unsigned long long z = mix64(stream + GOLDEN * (step + 1));
   z = mix64(z + GOLDEN * (i + 1));
   return ((float)(z >> 40) + 0.5f) * (1.0f / 16777216.0f);  // in (0, 1), exact in 32-bit
 }
 
-// temperature[r] == 0 selects greedily. keys/steps may be null when every
+// temperature[r] == 0 selects greedily. streams/steps may be null when every
 // temperature is 0.
 __global__ void __launch_bounds__(1024)
 select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int V,
-                     const float* __restrict__ temperature, unsigned long long seed,
-                     const long long* __restrict__ keys, const long long* __restrict__ steps,
+                     const float* __restrict__ temperature,
+                     const long long* __restrict__ streams, const long long* __restrict__ steps,
                      int* __restrict__ out) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
@@ -40,14 +41,14 @@ select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int
   const float temp = temperature ? temperature[r] : 0.f;
   const bool greedy = !(temp > 0.f);
   const float inv_t = greedy ? 1.f : 1.0f / temp;
-  const unsigned long long key = (!greedy && keys) ? (unsigned long long)keys[r] : 0ULL;
+  const unsigned long long stream = (!greedy && streams) ? (unsigned long long)streams[r] : 0ULL;
   const unsigned long long step = (!greedy && steps) ? (unsigned long long)steps[r] : 0ULL;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     float v = row[i];
     if (!greedy) {
-      const float u = uniform24(seed, key, step, (unsigned long long)i);
+      const float u = uniform24(stream, step, (unsigned long long)i);
       v = v * inv_t - logf(-logf(u));
     }
     // indices ascend within a thread, so `>` keeps the first of equal values;
@@ -84,13 +85,12 @@ select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int
 }  // namespace
 
 FB_API int fb_select_tokens(const float* logits, long long row_stride, int n, int V,
-                            const float* temperature, unsigned long long seed,
-                            const long long* keys, const long long* steps, int* out,
-                            cudaStream_t stream) {
+                            const float* temperature, const long long* streams,
+                            const long long* steps, int* out, cudaStream_t stream) {
   FB_REQUIRE(n >= 0 && V > 0 && row_stride >= V, "select_tokens: bad sizes n=%d V=%d", n, V);
   if (n == 0) return 0;
   const int threads = V >= 8192 ? 1024 : 256;
-  select_tokens_kernel<<<n, threads, 0, stream>>>(logits, row_stride, V, temperature, seed, keys,
+  select_tokens_kernel<<<n, threads, 0, stream>>>(logits, row_stride, V, temperature, streams,
                                                   steps, out);
   return fb_check_launch("select_tokens");
 }

@@ -1,0 +1,225 @@
+"""Single-token steps as a replayed CUDA graph.
+
+A decode step of the 3B model is some two hundred small kernels; launched one
+by one from the host they cost more than they run. The reference pays that
+price (about 1,780 dispatches a step, src/metal/stream.rs batches them 64 to
+a command buffer). Here the step of a fixed number of rows is captured once
+and replayed: the kernels read tokens, positions, lengths and page tables from
+fixed device buffers that one small copy from pinned host memory refreshes
+before each replay.
+
+Rows are padded up to a bucket size (1, 2, 4, ...). A padding row has
+sequence index -1: the cache kernels skip it and its logits are ignored, so
+padding changes no result. The chosen token of each row is written where the
+next step reads its input, so steps can follow one another without the host
+seeing the tokens (`DecodeSession.step`), or with the host feeding and reading
+them every step (`step_host`, which is what generation uses).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.pages import PAGE, pages_for
+from ..kernels import ops
+from ..sampling.params import SamplingParams
+from .context import StepContext
+
+
+def bucket_of(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class DecodeRunner:
+    """Fixed buffers and the captured graph for `bucket` rows and page tables
+    `width` pages wide."""
+
+    def __init__(self, engine, bucket: int, width: int):
+        self.engine, self.bucket, self.width = engine, bucket, width
+        dev = engine.device
+        groups = engine.cache.groups
+        b = bucket
+        # packed int32 fields: token ids | positions | seq_of_token | want_rows | slots |
+        # cu_tokens | kv_lens | one page table per group
+        sizes = [b, b, b, b, b, b + 1, b] + [b * width for _ in groups]
+        offsets = [int(o) for o in np.cumsum([0] + sizes)]
+        total = offsets[-1]
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        part = [self.dev[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
+        self.h = [self.host_np[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
+        self.meta_start = offsets[1]  # everything after the token ids
+        self.ctx = StepContext(
+            n_tokens=b, n_seqs=b, n_want=b, token_ids=part[0], positions=part[1],
+            seq_of_token=part[2], want_rows=part[3], slots=part[4], cu_tokens=part[5],
+            kv_lens=part[6], slots_host=[], cu_tokens_host=list(range(b + 1)), kv_lens_host=[],
+            is_decode=True, max_q_len=1, max_kv_len=width * PAGE)
+        for i, group in enumerate(groups):
+            self.ctx._tables[id(group)] = part[7 + i].view(b, width)
+        self.h_tables = [self.h[7 + i].reshape(b, width) for i in range(len(groups))]
+        self.row_sig: List[Optional[Tuple[int, int, int]]] = [None] * b
+        self.h[3][:] = np.arange(b)  # every row's logits are wanted
+        self.h[5][:] = np.arange(b + 1)
+        # sampling inputs: temperature per row; random stream and step count per row
+        self.temperature = torch.zeros(b, dtype=torch.float32, device=dev)
+        self.temperature_value = 0.0
+        self.meta64_host = torch.zeros(2 * b, dtype=torch.int64).pin_memory()
+        self.meta64 = torch.zeros(2 * b, dtype=torch.int64, device=dev)
+        self.next_tokens = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.tokens_host = torch.zeros(b, dtype=torch.int32).pin_memory()
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels_per_step = 0
+        self.logits: Optional[torch.Tensor] = None
+
+    def _body(self) -> None:
+        engine = self.engine
+        self.logits = engine.model.forward(self.ctx, engine.cache)
+        b = self.bucket
+        ops.select_tokens(self.logits, self.next_tokens, self.temperature, self.meta64[:b],
+                          self.meta64[b:])
+        self.ctx.token_ids.copy_(self.next_tokens)
+
+    def run(self) -> None:
+        """One step over the buffers' current contents."""
+        if not self.engine.use_graphs:
+            self._body()
+            return
+        if self.graph is None:
+            # The first call runs plainly (it loads the kernels, sizes the
+            # allocator and IS this call's step); then the same work is captured
+            # for every later call. Capturing executes nothing.
+            before = ops.launch_count()
+            self._body()
+            self.kernels_per_step = ops.launch_count() - before
+            plain_logits = self.logits
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self.engine.graph_pool()):
+                self._body()
+            ops.add_launches(-self.kernels_per_step)  # recorded, not launched
+            self.graph = graph
+            # `self.logits` is now the graph's own buffer, which replays fill;
+            # this call's logits are the plain run's
+            self.logits.copy_(plain_logits)
+            return
+        self.graph.replay()
+        ops.add_launches(self.kernels_per_step)
+
+
+class DecodeSession:
+    """Decode steps of a set of open sequences, row i being `slots[i]`.
+    `keys[i]` names row i's random stream and `counts[i]` is how many tokens
+    its sequence has generated (both only matter when sampling)."""
+
+    def __init__(self, engine, slots: Sequence[int], sampling: SamplingParams = SamplingParams(),
+                 keys: Optional[Sequence[int]] = None, counts: Optional[Sequence[int]] = None):
+        from ..sampling.sampler import stream_key
+        self.engine = engine
+        self.slots = list(slots)
+        self.sampling = sampling
+        keys = list(keys) if keys is not None else list(range(len(slots)))
+        self.keys = keys
+        self.streams = [stream_key(sampling.seed, k) for k in keys]
+        self.counts = list(counts) if counts is not None else [0] * len(slots)
+        self.runner: Optional[DecodeRunner] = None
+        self.h2d_bytes_per_step = 0
+        self.d2h_bytes_per_step = 0
+
+    def _prepare(self) -> DecodeRunner:
+        """Reserve one more token per sequence and refresh the host buffers."""
+        engine, cache = self.engine, self.engine.cache
+        n = len(self.slots)
+        lengths = [cache.length(s) for s in self.slots]
+        limit = engine.spec.max_positions
+        for s, length in zip(self.slots, lengths):
+            if length + 1 > limit:
+                raise ValueError(f"slot {s} would pass the model's {limit} positions")
+        cache.reserve({s: length + 1 for s, length in zip(self.slots, lengths)})
+        need = 1
+        for g in cache.groups:
+            need = max(need, max(len(g.pages.pages(s)) for s in self.slots))
+        bucket = bucket_of(n)
+        runner = self.runner
+        if runner is None or runner.bucket != bucket or runner.width < need:
+            width = 8
+            while width < need:
+                width *= 2
+            runner = self.runner = engine.decode_runner(bucket, width)
+        h = runner.h
+        h[1][:n] = lengths
+        h[1][n:] = 0
+        h[2][:n] = np.arange(n)
+        h[2][n:] = -1
+        h[4][:n] = self.slots
+        h[4][n:] = 0
+        h[6][:n] = lengths
+        h[6][:n] += 1
+        h[6][n:] = 0
+        epoch = cache.table.epoch
+        for i, s in enumerate(self.slots):
+            count = sum(len(g.pages.pages(s)) for g in cache.groups)
+            sig = (s, epoch[s], count)
+            if runner.row_sig[i] != sig:
+                runner.row_sig[i] = sig
+                for table, group in zip(runner.h_tables, cache.groups):
+                    pages = group.pages.pages(s)
+                    table[i, :len(pages)] = pages
+        for i in range(n, bucket):
+            runner.row_sig[i] = None
+        return runner
+
+    def _upload(self, runner: DecodeRunner, tokens: Optional[Sequence[int]]) -> None:
+        n = len(self.slots)
+        start = runner.meta_start
+        if tokens is not None:
+            runner.host_np[:n] = tokens
+            runner.host_np[n:runner.bucket] = 0
+            start = 0
+        runner.dev[start:].copy_(runner.host[start:], non_blocking=True)
+        self.h2d_bytes_per_step = (runner.host.numel() - start) * 4
+        temperature = float(self.sampling.temperature)
+        if runner.temperature_value != temperature:
+            runner.temperature.fill_(temperature)
+            runner.temperature_value = temperature
+        if temperature > 0.0:
+            b = runner.bucket
+            m = runner.meta64_host.numpy()
+            m[:n] = self.streams
+            m[b:b + n] = self.counts
+            runner.meta64.copy_(runner.meta64_host, non_blocking=True)
+            self.h2d_bytes_per_step += runner.meta64_host.numel() * 8
+
+    def set_tokens(self, tokens: Sequence[int]) -> None:
+        """Device-resident stepping (`step`) starts from these input tokens."""
+        self._pending_tokens = list(tokens)
+
+    def step(self) -> None:
+        """One step whose input tokens are the previous step's choices, which
+        stay on the device."""
+        runner = self._prepare()
+        self._upload(runner, getattr(self, "_pending_tokens", None))
+        self._pending_tokens = None
+        runner.run()
+        self.counts = [c + 1 for c in self.counts]
+
+    def step_host(self, tokens: Sequence[int]) -> List[int]:
+        """One step fed from the host; returns the chosen tokens on the host."""
+        runner = self._prepare()
+        self._upload(runner, tokens)
+        runner.run()
+        n = len(self.slots)
+        runner.tokens_host[:n].copy_(runner.next_tokens[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes_per_step = n * 4
+        self.counts = [c + 1 for c in self.counts]
+        return runner.tokens_host[:n].tolist()
+
+    def logits(self) -> torch.Tensor:
+        """float32 logits [rows, vocab] of the last step (a buffer the next step reuses)."""
+        return self.runner.logits[:len(self.slots)]

@@ -21,6 +21,7 @@ from ..sampling import Sampler, SamplingParams
 from ..weights.safetensors_io import WeightFiles
 from . import generate as loop
 from .context import SequenceStep, StepContext, build_context
+from .decode import DecodeRunner, DecodeSession
 from .model import Model
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -55,7 +56,10 @@ class Engine:
         self._cache_args = (max_tokens, max_slots)
         self.cache: Optional[SequenceCache] = None
         self.sampler = Sampler(self.device)
-        self.launch_count = 0
+        self.use_graphs = True  # replay decode steps as CUDA graphs
+        self._runners = {}
+        self._graph_pool = None
+        self._session = None
 
     # ---------------------------------------------------------------- load
     @classmethod
@@ -118,6 +122,8 @@ class Engine:
     def step(self, steps: Sequence[SequenceStep]) -> torch.Tensor:
         """Run the given tokens from the cache; float32 logits [wanted, vocab]
         in the order of `steps` and of each `want`."""
+        if self._is_decode(steps):
+            return self._decode(steps, SamplingParams(), None, None)[1].clone()
         ctx = build_context(self.cache, steps, self.spec.vocab_size, self.device,
                             self.spec.max_positions)
         return self.model.forward(ctx, self.cache)
@@ -126,9 +132,54 @@ class Engine:
                     keys: Sequence[int], counts: Sequence[int]) -> List[int]:
         """A step whose wanted logits are turned into tokens on the device;
         only the token ids cross to the host."""
+        if self._is_decode(steps):
+            return self._decode(steps, params, keys, counts)[0]
         logits = self.step(steps)
         tokens = self.sampler.select(logits, params, keys, counts)
         return tokens.tolist()
+
+    @staticmethod
+    def _is_decode(steps: Sequence[SequenceStep]) -> bool:
+        return len(steps) > 0 and all(len(s.tokens) == 1 and list(s.want) == [0] for s in steps)
+
+    def _decode(self, steps, params, keys, counts):
+        """One token per sequence, through a `DecodeSession` (fixed buffers,
+        replayed graph); returns (host tokens, logits buffer)."""
+        slots = [s.slot for s in steps]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        for s in steps:
+            if not self.cache.table.slots.is_held(s.slot):
+                raise ValueError(f"slot {s.slot} is not open")
+            if not 0 <= int(s.tokens[0]) < self.spec.vocab_size:
+                raise ValueError(f"token id {s.tokens[0]} is outside the vocabulary of "
+                                 f"{self.spec.vocab_size}")
+        keys = list(range(len(slots))) if keys is None else list(keys)
+        session = self._session
+        if session is None or session.slots != slots or session.sampling != params \
+                or session.keys != keys:
+            session = self._session = DecodeSession(self, slots, params, keys, counts)
+        elif counts is not None:
+            session.counts = list(counts)
+        tokens = session.step_host([int(s.tokens[0]) for s in steps])
+        return tokens, session.logits()
+
+    # -------------------------------------------------------------- decode
+    def decode_session(self, slots: Sequence[int], sampling: SamplingParams = SamplingParams(),
+                       keys: Optional[Sequence[int]] = None,
+                       counts: Optional[Sequence[int]] = None) -> "DecodeSession":
+        return DecodeSession(self, slots, sampling, keys, counts)
+
+    def decode_runner(self, bucket: int, width: int) -> "DecodeRunner":
+        key = (bucket, width)
+        if key not in self._runners:
+            self._runners[key] = DecodeRunner(self, bucket, width)
+        return self._runners[key]
+
+    def graph_pool(self):
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
 
     # ------------------------------------------------------------ generate
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int,

@@ -37,8 +37,8 @@ _SIGNATURES = {
     "fb_attention_simt": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                           c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_void_p],
-    "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_ull, c_void_p, c_void_p,
-                         c_void_p, c_void_p],
+    "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                         c_void_p],
 }
 
 _FUNCS = {}
@@ -62,7 +62,23 @@ def _fn(name: str):
     return fn
 
 
+_COUNT = [0]
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far (graph replays included)."""
+    return _COUNT[0]
+
+
+def add_launches(n: int) -> None:
+    _COUNT[0] += n
+
+
+add_graph_launches = add_launches
+
+
 def _call(name: str, *args) -> None:
+    _COUNT[0] += 1
     code = _fn(name)(*args)
     if code != 0:
         message = library.load().fb_last_error().decode(errors="replace")
@@ -249,17 +265,18 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
 
 # ------------------------------------------------------------------- sampling
 def select_tokens(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor],
-                  seed: int = 0, keys: Optional[torch.Tensor] = None,
+                  streams: Optional[torch.Tensor] = None,
                   steps: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Greedy where temperature is 0 (or None), Gumbel-max sampling elsewhere."""
+    """Greedy where temperature is 0 (or None), Gumbel-max sampling elsewhere.
+    `streams[r]` is the row's random stream (`sampling.stream_key(seed, key)`),
+    `steps[r]` how many tokens its sequence has generated."""
     n, V = logits.shape
     if out.numel() != n:
         raise KernelError("select_tokens: out does not hold one token per row")
     _call("fb_select_tokens", _dev(logits, "logits", torch.float32, contiguous=False),
           _rows(logits, "logits"), n, V,
           0 if temperature is None else _dev(temperature, "temperature", torch.float32),
-          seed & (2**64 - 1),
-          0 if keys is None else _dev(keys, "keys", torch.int64),
+          0 if streams is None else _dev(streams, "streams", torch.int64),
           0 if steps is None else _dev(steps, "steps", torch.int64),
           _dev(out, "out", torch.int32), _stream())
     return out

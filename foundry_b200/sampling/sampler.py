@@ -23,10 +23,21 @@ def _mix64(z: np.ndarray) -> np.ndarray:
     return z ^ (z >> np.uint64(31))
 
 
+def stream_key(seed: int, key: int) -> int:
+    """The random stream of sequence `key` under `seed`, as a signed 64-bit
+    integer: mix64(seed + GOLDEN * (key + 1)). Formed once per sequence on the
+    host; the kernel mixes in the step and the token id."""
+    z = (seed + _GOLDEN * (key + 1)) & _MASK
+    z = ((z ^ (z >> 30)) * _M1) & _MASK
+    z = ((z ^ (z >> 27)) * _M2) & _MASK
+    z ^= z >> 31
+    return z - (1 << 64) if z >= (1 << 63) else z
+
+
 def uniform24(seed: int, key: int, step: int, count: int) -> np.ndarray:
     """u_i in (0, 1) for token ids 0..count-1, as float32, bit-equal to the kernel's."""
     with np.errstate(over="ignore"):
-        z = _mix64(np.uint64(seed & _MASK) + np.uint64(_GOLDEN) * np.uint64(key + 1))
+        z = np.uint64(stream_key(seed, key) & _MASK)
         z = _mix64(z + np.uint64(_GOLDEN) * np.uint64(step + 1))
         i = np.arange(1, count + 1, dtype=np.uint64)
         z = _mix64(z + np.uint64(_GOLDEN) * i)
@@ -53,7 +64,8 @@ class Sampler:
         out = torch.empty(n, dtype=torch.int32, device=logits.device)
         if params.greedy:
             return ops.select_tokens(logits, out, None)
-        meta = torch.tensor([list(keys), list(steps)], dtype=torch.int64).to(logits.device)
+        streams = [stream_key(params.seed, int(k)) for k in keys]
+        meta = torch.tensor([streams, list(steps)], dtype=torch.int64).to(logits.device)
         temp = torch.full((n,), float(params.temperature), dtype=torch.float32,
                           device=logits.device)
-        return ops.select_tokens(logits, out, temp, params.seed, meta[0], meta[1])
+        return ops.select_tokens(logits, out, temp, meta[0], meta[1])
