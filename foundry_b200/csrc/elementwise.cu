@@ -157,3 +157,28 @@ FB_API int fb_cast(const void* in, int in_dtype, void* out, int out_dtype, long 
       cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, (size_t)n))));
   return fb_check_launch("cast");
 }
+
+// ------------------------------------------------------- sum of split-K planes
+// out[i] = sum_s planes[s * plane_stride + i], planes in float32, summed in
+// plane order (a fixed order: the result does not depend on timing).
+template <typename TO>
+__global__ void sum_planes_kernel(const float* __restrict__ planes, int S, long long n,
+                                  long long plane_stride, TO* __restrict__ out) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = planes[i];
+    for (int s = 1; s < S; ++s) acc += planes[(long long)s * plane_stride + i];
+    out[i] = fb_from_float<TO>(acc);
+  }
+}
+
+FB_API int fb_sum_planes(const float* planes, int S, long long n, long long plane_stride,
+                         void* out, int out_dtype, cudaStream_t stream) {
+  FB_REQUIRE(S >= 1 && n >= 0, "sum_planes: bad sizes S=%d n=%lld", S, n);
+  if (n == 0) return 0;
+  const long long want = (n + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  FB_DISPATCH_DTYPE(out_dtype, TO, (sum_planes_kernel<TO><<<blocks, 256, 0, stream>>>(
+                                       planes, S, n, plane_stride, (TO*)out)));
+  return fb_check_launch("sum_planes");
+}

@@ -1,0 +1,477 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//   D[i, j] = sum_k A[i, k] * B[j, k],  A: [rows_a, K], B: [rows_b, K], both K-major,
+// accumulated in 32-bit in tensor memory. A projection y = x W^T
+// (src/nn/linear.rs:19-36; the reference's own 16x16-tile kernel is
+// src/metal/kernels/matmul.metal:29-73) maps onto it in two ways:
+//   many tokens:  A = x (tokens), B = W (features): out[i * ldo + j]
+//   few tokens:   A = W (features), B = x (tokens): out[j * ldo + i]   ("swapped")
+// so that the 128-row operand is always full. In swapped form the weights
+// stream through once and the token count is only the instruction's N (16..256).
+//
+// One CTA computes one 128 x BN tile over one K range (split-K gives each CTA
+// of a tile a range of its own and a float32 partial plane of its own).
+// Roles: warp 0 issues TMA loads (one lane); warp 1 allocates tensor memory and
+// issues tcgen05.mma (one lane); warps 2-5 read the accumulator back with
+// tcgen05.ld and store. Operand tiles are 64 elements (128 bytes) wide in K,
+// laid out by TMA with the 128-byte swizzle that the MMA descriptors name.
+// No load is multicast; every CTA fetches its own tiles.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the CTA records
+// where in `fb_gemm_tc_status`, stops issuing work, lets the other roles run
+// out as well, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;            // rows of A per tile = instruction M
+constexpr int BK = 64;             // K elements per stage: 128 bytes of bf16 = one swizzle row
+constexpr int UMMA_K = 16;         // K of one tcgen05.mma for 16-bit inputs
+constexpr int THREADS = 192;       // 6 warps
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+__device__ int g_status[4];  // [0] != 0: a wait ran out; [1] where; [2] block; [3] k-block
+
+// ------------------------------------------------------------------ PTX faces
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the bound was hit or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int where, int kb) {
+  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (atomicCAS(&g_status[0], 0, 1) == 0) {
+    g_status[1] = where;
+    g_status[2] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+    g_status[3] = kb;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
+// swizzled in 128-byte mode: 8-row groups are 1024 bytes apart (stride byte
+// offset); the leading byte offset is unused because one MMA's K extent
+// (32 bytes) lies inside one swizzle row. Bits 46-47 carry the descriptor
+// version of this architecture (1); bits 61-63 the swizzle mode (2 = 128 B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: D = float32 (bits 4-5 = 1), A and B =
+// bfloat16 (bits 7-9 and 10-12 = 1), both K-major (bits 15, 16 = 0),
+// N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                     uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmParams {
+  int rows_a, rows_b, K;
+  int kblocks_per_split;      // K blocks of BK each CTA of a tile walks
+  long long stride_a, stride_b;  // out[i * stride_a + j * stride_b]
+  long long split_stride;        // elements between split-K planes
+  void* out;
+  int out_f32;                // 1: float32 output, 0: bfloat16
+};
+
+// Dynamic shared memory: [stages][A tile 128x64][B tile BNx64] bf16, 1024-aligned,
+// then the barriers.
+template <int BN>
+struct Smem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES =
+      (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
+  static constexpr int BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+  constexpr int STAGES = Smem<BN>::STAGES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // power of two >= 32
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * Smem<BN>::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int kb0 = split * p.kblocks_per_split;
+  int nkb = total_kb - kb0;
+  if (nkb > p.kblocks_per_split) nkb = p.kblocks_per_split;
+  if (nkb < 0) nkb = 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        if (!mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, i)) break;
+        uint8_t* a_dst = tiles + s * Smem<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+        mbar_expect_tx(&full[s], Smem<BN>::STAGE_BYTES);
+        const int k = (kb0 + i) * BK;
+        tma_load_2d(a_dst, &map_a, &full[s], k, tile_a * BM);
+        tma_load_2d(b_dst, &map_b, &full[s], k, tile_b * BN);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
+        ok = mbar_wait(&full[s], phase, abort_flag, 2, i);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles + s * Smem<BN>::STAGE_BYTES);
+        const uint32_t b_addr = a_addr + Smem<BN>::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // advancing K by 16 elements inside the swizzle row = +32 bytes
+          umma(tmem_base, make_desc(a_addr + k * UMMA_K * 2), make_desc(b_addr + k * UMMA_K * 2),
+               idesc, (i | k) != 0 ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);  // frees the stage when these MMAs have read it
+      }
+      if (ok) tc_commit(acc_full);  // accumulator complete
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;             // the TMEM lanes this warp may read
+    const int i_local = quarter * 32 + lane;  // row of A within the tile
+    const long long i_global = (long long)tile_a * BM + i_local;
+    bool ok = true;
+    if (nkb > 0) ok = mbar_wait(acc_full, 0, abort_flag, 3, 0);
+    tc_fence_after();
+    if (ok) {
+      float* out_f = (float*)p.out + (long long)split * p.split_stride;
+      __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
+      constexpr int CHUNK = BN < 32 ? 16 : 32;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CHUNK) {
+        float v[CHUNK];
+        if (nkb > 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+          if constexpr (CHUNK == 32) {
+            uint32_t r[32];
+            tmem_ld32(taddr, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+          } else {
+            uint32_t r[16];
+            tmem_ld16(taddr, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < CHUNK; ++e) v[e] = 0.f;
+        }
+        if (i_global < p.rows_a) {
+          const long long j0 = (long long)tile_b * BN + c;
+          const long long base = i_global * p.stride_a + j0 * p.stride_b;
+          if (p.stride_b == 1 && j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
+            // this thread's elements are contiguous: vector stores
+            if (p.out_f32) {
+#pragma unroll
+              for (int e = 0; e < CHUNK; e += 4)
+                *reinterpret_cast<float4*>(out_f + base + e) =
+                    make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < CHUNK; e += 8) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[e], v[e + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[e + 2], v[e + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[e + 4], v[e + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[e + 6], v[e + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(out_h + base + e) = pk;
+              }
+            }
+          } else {
+            // swapped form (stride_a == 1): for each j the warp's lanes are contiguous
+#pragma unroll
+            for (int e = 0; e < CHUNK; ++e) {
+              if (j0 + e < p.rows_b) {
+                const long long idx = base + (long long)e * p.stride_b;
+                if (p.out_f32) out_f[idx] = v[e];
+                else out_h[idx] = __float2bfloat16_rn(v[e]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------- host: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) ==
+            cudaSuccess && res == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    return h * 1000003u ^ (size_t)k.box_rows;
+  }
+};
+
+// A [rows, cols] bf16 matrix with row stride `ld` elements, fetched in boxes of
+// box_rows x 64 elements with the 128-byte swizzle; out-of-range elements read 0.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld,
+             int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *map = it->second;
+      return 0;
+    }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fb_fail(3, "gemm_tc: cuTensorMapEncodeTiled is not available in this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                  box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fb_fail(3, "gemm_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *map);
+  return 0;
+}
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
+           cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<BN>::BYTES);
+    if (e != cudaSuccess) return fb_fail(2, "gemm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_tc_kernel<BN><<<grid, THREADS, Smem<BN>::BYTES, stream>>>(ma, mb, p);
+  return fb_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// out = A * B^T in the layout the strides give; see the file header.
+//   a: [rows_a, K] bf16, row stride lda;  b: [rows_b, K] bf16, row stride ldb
+//   out[i * stride_a + j * stride_b (+ split * split_stride)], float32 when out_f32
+//   bn: the B-tile height (16, 32, 64, 128 or 256); splits: K ranges per tile
+// With splits > 1 the output must be float32 and holds `splits` partial planes
+// that the caller sums.
+FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, long long ldb,
+                      int rows_b, int K, void* out, long long stride_a, long long stride_b,
+                      int out_f32, int bn, int splits, long long split_stride,
+                      cudaStream_t stream) {
+  FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, K);
+  FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
+             "gemm_tc: K and the row strides must be multiples of 8 elements (16 bytes), got K=%d "
+             "lda=%lld ldb=%lld", K, lda, ldb);
+  FB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0,
+             "gemm_tc: operands must start on 16-byte boundaries");
+  FB_REQUIRE(splits >= 1 && (splits == 1 || out_f32), "gemm_tc: split-K needs a float32 output");
+  const int total_kb = (K + BK - 1) / BK;
+  FB_REQUIRE(splits <= total_kb, "gemm_tc: %d splits for %d K blocks", splits, total_kb);
+  GemmParams p;
+  p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
+  p.kblocks_per_split = (total_kb + splits - 1) / splits;
+  p.stride_a = stride_a; p.stride_b = stride_b; p.split_stride = split_stride;
+  p.out = out; p.out_f32 = out_f32;
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, rows_a, K, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mb, b, rows_b, K, ldb, bn);
+  if (rc) return rc;
+  dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
+  FB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
+  switch (bn) {
+    case 16: return launch<16>(ma, mb, p, grid, stream);
+    case 32: return launch<32>(ma, mb, p, grid, stream);
+    case 64: return launch<64>(ma, mb, p, grid, stream);
+    case 128: return launch<128>(ma, mb, p, grid, stream);
+    case 256: return launch<256>(ma, mb, p, grid, stream);
+    default: return fb_fail(1, "gemm_tc: tile height %d is not one of 16, 32, 64, 128, 256", bn);
+  }
+}
+
+// Reads and clears the device-side status: 0 when no wait ever ran out, else
+// the code of the role that gave up (1 producer, 2 MMA, 3 epilogue); `detail`
+// receives {where, block, k-block}. Synchronises the device.
+FB_API int fb_gemm_tc_status(int* detail) {
+  int host[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(host, g_status, sizeof(host));
+  if (e != cudaSuccess) return fb_fail(2, "gemm_tc_status: %s", cudaGetErrorString(e));
+  if (detail) { detail[0] = host[1]; detail[1] = host[2]; detail[2] = host[3]; }
+  if (host[0]) {
+    int zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_status, zero, sizeof(zero));
+  }
+  return host[0] ? host[1] : 0;
+}

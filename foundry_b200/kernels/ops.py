@@ -37,6 +37,10 @@ _SIGNATURES = {
     "fb_attention_simt": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
                           c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_void_p],
+    "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
+    "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
+                   c_int, c_int, c_ll, c_void_p],
+    "fb_gemm_tc_status": [c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p],
 }
@@ -228,9 +232,86 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
     return out
 
 
+SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
+
+
+def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
+            bn: int, splits: int = 1, split_stride: int = 0) -> None:
+    """Tensor-core product D[i,j] = sum_k a[i,k] b[j,k] written to
+    out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu."""
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc takes bfloat16 operands")
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"gemm_tc writes float32 or bfloat16, not {out.dtype}")
+    _call("fb_gemm_tc", _dev(a, "a", contiguous=False), _rows(a, "a"), a.shape[0],
+          _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
+          _dev(out, "out", contiguous=False), stride_a, stride_b,
+          1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, _stream())
+
+
+def gemm_tc_status():
+    """0 when no bounded wait of the tensor-core kernels ever ran out, else
+    (role, block, k-block). Synchronises the device."""
+    detail = (ctypes.c_int * 3)()
+    code = _fn("fb_gemm_tc_status")(ctypes.cast(detail, ctypes.c_void_p))
+    return 0 if code == 0 else (code, detail[1], detail[2])
+
+
+def sum_planes(planes: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = planes.sum(0) for float32 planes [S, ...], in plane order."""
+    S = planes.shape[0]
+    n = out.numel()
+    if planes.numel() != S * n:
+        raise KernelError("sum_planes: plane size differs from the output")
+    _call("fb_sum_planes", _dev(planes, "planes", torch.float32), S, n, n, _dev(out, "out"),
+          code_of(out.dtype), _stream())
+    return out
+
+
+def _tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    K = x.shape[1]
+    return (K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and x.stride(1) == 1
+            and w.stride(1) == 1 and out.stride(1) == 1)
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """bfloat16 product with 32-bit accumulation: the kernel that fits the shape."""
-    return gemm_simt(x, w, out)
+    """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
+
+    More than 128 rows: token rows fill the 128-row operand, weights the other
+    (256 wide). Up to 128 rows: swapped, the weights fill the 128-row operand and
+    stream through once, the tokens are the narrow operand; K is split over
+    CTAs until the grid covers the SMs, each split writing a float32 plane that
+    one more kernel sums in a fixed order. Shapes TMA cannot address (K or a
+    row stride not a multiple of 8 elements) take the CUDA-core kernel.
+    """
+    M, K = x.shape
+    N = w.shape[0]
+    if M == 0:
+        return out
+    if not _tc_usable(x, w, out):
+        return gemm_simt(x, w, out)
+    if M > 128:
+        bn = 256 if N >= 256 else (128 if N > 64 else 64)
+        gemm_tc(x, w, out, out.stride(0), 1, bn)
+        return out
+    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = (N + 127) // 128
+    kblocks = (K + 63) // 64
+    splits = max(1, min(kblocks // 4, (SM_COUNT + tiles // 2) // tiles))
+    if splits == 1:
+        gemm_tc(w, x, out, 1, out.stride(0), bn)
+        return out
+    per = (kblocks + splits - 1) // splits
+    splits = (kblocks + per - 1) // per  # no empty split
+    planes = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    gemm_tc(w, x, planes, 1, N, bn, splits, M * N)
+    if out.is_contiguous():
+        return sum_planes(planes, out)
+    tmp = torch.empty((M, N), dtype=out.dtype, device=x.device)
+    sum_planes(planes, tmp)
+    out.copy_(tmp)
+    return out
 
 
 # ------------------------------------------------------------------ attention
