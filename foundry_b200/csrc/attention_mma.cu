@@ -1,0 +1,594 @@
+// bfloat16 attention over the paged cache on the tensor cores, two kernels:
+//
+//   prefill   a 64-row block of one sequence's queries for one head walks the
+//             sequence's pages (64 keys each) with an online softmax; the four
+//             warps own 16 query rows each.
+//   decode    one new token per sequence: the G query heads that share a
+//             key-value head form one 16-row tile (rows >= G are padding), the
+//             four warps own 16 keys of each page, the cache range is split
+//             over CTAs, and a second kernel merges the partial results. No
+//             kernel waits on another.
+//
+// Formulas are the reference's (src/nn/attention.rs:23-60: head a reads kv head
+// a / G; src/models/llama/attention.rs:56-58: scale 1/sqrt(D);
+// src/nn/masking.rs:76-92: key j visible iff j <= query position;
+// src/nn/activation.rs:30-40: softmax with the maximum subtracted). Scores,
+// softmax statistics and the output accumulate in 32-bit; probabilities are
+// rounded to bfloat16 only as the operand of the P.V product. The reference
+// materialises [S, L] scores; nothing of that size exists here.
+//
+// Pages arrive in shared memory by cp.async (16-byte pieces, XOR-swizzled so
+// that ldmatrix is conflict-free), double-buffered. Head sizes 16, 32, 64 and
+// 128 are built; other sizes, windows and more than 16 query heads per kv head
+// are served by the CUDA-core kernel (attention_simt.cu).
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 128;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ------------------------------------------------------------- small PTX faces
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Shared-memory layout of a [rows, D] bfloat16 tile: 16-byte chunks of a row
+// are XORed with low bits of the row number.
+template <int D>
+struct Swz {
+  static constexpr int CHUNKS = D / 8;
+  static constexpr int MASK = CHUNKS >= 8 ? 7 : CHUNKS - 1;
+  static constexpr int SHIFT = CHUNKS >= 8 ? 0 : (CHUNKS == 4 ? 1 : 2);
+  __device__ static __forceinline__ int off(int row, int col) {
+    const int chunk = col >> 3;
+    return row * D + (((chunk ^ ((row >> SHIFT) & MASK))) << 3) + (col & 7);
+  }
+};
+
+// Copies `rows` x D elements (row stride `ld`) into a swizzled tile; rows at or
+// beyond `valid_rows` are zero-filled.
+template <int D>
+__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat16* src,
+                                          long long ld, int rows, int valid_rows) {
+  constexpr int CH = D / 8;
+  for (int id = threadIdx.x; id < rows * CH; id += THREADS) {
+    const int r = id / CH, c = id - r * CH;
+    const bool ok = r < valid_rows;
+    const __nv_bfloat16* s = src + (ok ? (long long)r * ld + c * 8 : 0);
+    cp_async16(smem_u32(dst + Swz<D>::off(r, c * 8)), s, ok);
+  }
+}
+
+struct AttnParams {
+  const __nv_bfloat16* q;
+  long long q_stride;
+  __nv_bfloat16* out;
+  long long out_stride;
+  const int* cu_tokens;  // [n_seqs + 1]
+  const int* kv_lens;    // [n_seqs]: length after this step
+  const int* page_table; // [n_seqs, max_pages]
+  int max_pages;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  long long page_stride, head_stride;
+  int n_seqs, A, Kh;
+  float scale_log2;  // scale * log2(e)
+  // decode only
+  int splits;
+  float* ws_o;   // [n_seqs, Kh, splits, 16, D]
+  float* ws_ml;  // [n_seqs, Kh, splits, 16, 2]
+};
+
+// --------------------------------------------------------------------- prefill
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(const AttnParams p) {
+  constexpr int KT = D / 16;  // k-steps of Q.K^T
+  constexpr int NT = D / 8;   // n-tiles of P.V
+  extern __shared__ __align__(128) uint8_t smem[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);
+  __nv_bfloat16* sK = sQ + 64 * D;          // [2][64][D]
+  __nv_bfloat16* sV = sK + 2 * 64 * D;      // [2][64][D]
+  __shared__ int s_info[2];
+
+  if (threadIdx.x == 0) {
+    int b = blockIdx.x, s = 0;
+    for (; s < p.n_seqs; ++s) {
+      const int nb = (p.cu_tokens[s + 1] - p.cu_tokens[s] + 63) / 64;
+      if (b < nb) break;
+      b -= nb;
+    }
+    s_info[0] = s < p.n_seqs ? s : -1;
+    s_info[1] = b;
+  }
+  __syncthreads();
+  const int seq = s_info[0];
+  if (seq < 0) return;
+  const int row0 = s_info[1] * 64;
+  const int head = blockIdx.y, kvh = head / (p.A / p.Kh);
+  const int tok0 = p.cu_tokens[seq], q_len = p.cu_tokens[seq + 1] - tok0;
+  const int kv_len = p.kv_lens[seq];
+  const int pos0 = kv_len - q_len + row0;  // position of this block's first query
+  const int rows_valid = min(64, q_len - row0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  const int last_key = pos0 + rows_valid - 1;
+  const int n_pages = last_key / FB_PAGE + 1;
+  const int* pages = p.page_table + (size_t)seq * p.max_pages;
+  const __nv_bfloat16* kbase = p.k_cache + (long long)kvh * p.head_stride;
+  const __nv_bfloat16* vbase = p.v_cache + (long long)kvh * p.head_stride;
+
+  load_tile<D>(sQ, p.q + (long long)(tok0 + row0) * p.q_stride + (long long)head * D, p.q_stride,
+               64, rows_valid);
+  {
+    const long long off = (long long)pages[0] * p.page_stride;
+    load_tile<D>(sK, kbase + off, D, 64, 64);
+    load_tile<D>(sV, vbase + off, D, 64, 64);
+  }
+  cp_async_commit();
+
+  uint32_t qf[KT][4];
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  const int qpos_lo = pos0 + warp * 16 + g;  // position of row g; row g + 8 is 8 further
+
+  for (int pg = 0; pg < n_pages; ++pg) {
+    const int st = pg & 1;
+    if (pg + 1 < n_pages) {
+      const long long off = (long long)pages[pg + 1] * p.page_stride;
+      load_tile<D>(sK + (st ^ 1) * 64 * D, kbase + off, D, 64, 64);
+      load_tile<D>(sV + (st ^ 1) * 64 * D, vbase + off, D, 64, 64);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (pg == 0) {
+#pragma unroll
+      for (int k = 0; k < KT; ++k)
+        ldsm_x4(qf[k], smem_u32(sQ + Swz<D>::off(warp * 16 + (lane & 15), k * 16 + (lane >> 4) * 8)));
+    }
+    const int key0 = pg * FB_PAGE;
+    // a warp whose every query lies before this page has nothing to add
+    if (key0 <= pos0 + warp * 16 + 15) {
+      const __nv_bfloat16* tK = sK + st * 64 * D;
+      const __nv_bfloat16* tV = sV + st * 64 * D;
+      float s[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KT; ++k) {
+#pragma unroll
+        for (int n2 = 0; n2 < 4; ++n2) {  // two n-tiles (16 keys) per ldmatrix.x4
+          uint32_t b[4];
+          ldsm_x4(b, smem_u32(tK + Swz<D>::off(n2 * 16 + (lane & 7) + (lane >> 4) * 8,
+                                              k * 16 + ((lane >> 3) & 1) * 8)));
+          mma_bf16(s[2 * n2], qf[k], b[0], b[1]);
+          mma_bf16(s[2 * n2 + 1], qf[k], b[2], b[3]);
+        }
+      }
+      // scale, mask, online softmax (in the log2 domain)
+      const bool need_mask = key0 + FB_PAGE - 1 > pos0 + warp * 16;
+      float mx[2] = {m[0], m[1]};
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[n][e] * p.scale_log2;
+          if (need_mask) {
+            const int key = key0 + n * 8 + 2 * t + (e & 1);
+            const int qp = qpos_lo + (e >> 1) * 8;
+            if (key > qp) v = -INFINITY;
+          }
+          s[n][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      }
+      float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) corr[r] = exp2f(m[r] - mx[r]);  // 0 on the first page
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = exp2f(s[n][e] - mx[e >> 1]);
+          s[n][e] = pv;
+          sum[e >> 1] += pv;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[r] = l[r] * corr[r] + sum[r];
+        m[r] = mx[r];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
+      // O += P V: probabilities become the A operand, 16 keys per k-step
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int n2 = 0; n2 < NT / 2; ++n2) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, smem_u32(tV + Swz<D>::off(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                    n2 * 16 + (lane >> 4) * 8)));
+          mma_bf16(o[2 * n2], a, b[0], b[1]);
+          mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();  // the stage is refilled two iterations on
+  }
+  // every valid row saw key 0, so l > 0
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + g + r * 8;
+    if (row < rows_valid) {
+      const float inv = 1.0f / l[r];
+      __nv_bfloat16* dst = p.out + (long long)(tok0 + row0 + row) * p.out_stride + (long long)head * D;
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+        *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) =
+            pack_bf16(o[n][2 * r] * inv, o[n][2 * r + 1] * inv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------- decode
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const AttnParams p) {
+  constexpr int KT = D / 16, NT = D / 8;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
+  __nv_bfloat16* sK = sQ + 16 * D;                              // [2][64][D]
+  __nv_bfloat16* sV = sK + 2 * 64 * D;                          // [2][64][D]
+  const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int G = p.A / p.Kh;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int token = p.cu_tokens[seq];
+  const int kv_len = p.kv_lens[seq];
+  const int n_pages = (kv_len + FB_PAGE - 1) / FB_PAGE;
+  const int per = (n_pages + p.splits - 1) / p.splits;
+  const int pg0 = split * per;
+  const int pg1 = min(n_pages, pg0 + per);
+
+  float* ws_o = p.ws_o + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * D;
+  float* ws_ml = p.ws_ml + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * 2;
+  if (pg0 >= pg1) {  // nothing in this range (or a padding row: kv_len == 0)
+    if (p.splits > 1) {
+      for (int i = threadIdx.x; i < G; i += THREADS) { ws_ml[2 * i] = -INFINITY; ws_ml[2 * i + 1] = 0.f; }
+    } else {
+      for (int i = threadIdx.x; i < G * D; i += THREADS)
+        p.out[(long long)token * p.out_stride + (long long)(kvh * G) * D + i] = __float2bfloat16_rn(0.f);
+    }
+    return;
+  }
+  const int* pages = p.page_table + (size_t)seq * p.max_pages;
+  const __nv_bfloat16* kbase = p.k_cache + (long long)kvh * p.head_stride;
+  const __nv_bfloat16* vbase = p.v_cache + (long long)kvh * p.head_stride;
+
+  // rows 0..G-1 of the tile are this kv head's query heads, consecutive in q
+  load_tile<D>(sQ, p.q + (long long)token * p.q_stride + (long long)(kvh * G) * D, D, 16, G);
+  {
+    const long long off = (long long)pages[pg0] * p.page_stride;
+    load_tile<D>(sK, kbase + off, D, 64, 64);
+    load_tile<D>(sV, vbase + off, D, 64, 64);
+  }
+  cp_async_commit();
+
+  uint32_t qf[KT][4];
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  for (int pg = pg0; pg < pg1; ++pg) {
+    const int st = (pg - pg0) & 1;
+    if (pg + 1 < pg1) {
+      const long long off = (long long)pages[pg + 1] * p.page_stride;
+      load_tile<D>(sK + (st ^ 1) * 64 * D, kbase + off, D, 64, 64);
+      load_tile<D>(sV + (st ^ 1) * 64 * D, vbase + off, D, 64, 64);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (pg == pg0) {
+#pragma unroll
+      for (int k = 0; k < KT; ++k)
+        ldsm_x4(qf[k], smem_u32(sQ + Swz<D>::off(lane & 15, k * 16 + (lane >> 4) * 8)));
+    }
+    const int key0 = pg * FB_PAGE + warp * 16;  // this warp's 16 keys of the page
+    if (key0 < kv_len) {
+      const __nv_bfloat16* tK = sK + st * 64 * D;
+      const __nv_bfloat16* tV = sV + st * 64 * D;
+      float s[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KT; ++k) {
+        uint32_t b[4];
+        ldsm_x4(b, smem_u32(tK + Swz<D>::off(warp * 16 + (lane & 7) + (lane >> 4) * 8,
+                                            k * 16 + ((lane >> 3) & 1) * 8)));
+        mma_bf16(s[0], qf[k], b[0], b[1]);
+        mma_bf16(s[1], qf[k], b[2], b[3]);
+      }
+      float mx[2] = {m[0], m[1]};
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[n][e] * p.scale_log2;
+          if (key0 + n * 8 + 2 * t + (e & 1) >= kv_len) v = -INFINITY;
+          s[n][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      }
+      float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < 2; ++r) corr[r] = exp2f(m[r] - mx[r]);
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = exp2f(s[n][e] - mx[e >> 1]);
+          s[n][e] = pv;
+          sum[e >> 1] += pv;
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[r] = l[r] * corr[r] + sum[r];
+        m[r] = mx[r];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
+      uint32_t a[4];
+      a[0] = pack_bf16(s[0][0], s[0][1]);
+      a[1] = pack_bf16(s[0][2], s[0][3]);
+      a[2] = pack_bf16(s[1][0], s[1][1]);
+      a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+      for (int n2 = 0; n2 < NT / 2; ++n2) {
+        uint32_t b[4];
+        ldsm_x4_trans(b, smem_u32(tV + Swz<D>::off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                  n2 * 16 + (lane >> 4) * 8)));
+        mma_bf16(o[2 * n2], a, b[0], b[1]);
+        mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // merge the four warps' (m, l, O) through shared memory (the page buffers are free now)
+  float* sO = reinterpret_cast<float*>(sK);   // [4][16][D]
+  float* sM = sO + 4 * 16 * D;                // [4][16]
+  float* sL = sM + 4 * 16;                    // [4][16]
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g + r * 8;
+    if (t == 0) { sM[warp * 16 + row] = m[r]; sL[warp * 16 + row] = l[r]; }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      sO[(warp * 16 + row) * D + n * 8 + 2 * t] = o[n][2 * r];
+      sO[(warp * 16 + row) * D + n * 8 + 2 * t + 1] = o[n][2 * r + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 16 + row]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sM[w * 16 + row];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      L += sL[w * 16 + row] * f;
+      acc += sO[(w * 16 + row) * D + d] * f;
+    }
+    if (p.splits > 1) {
+      ws_o[row * D + d] = acc;
+      if (d == 0) { ws_ml[2 * row] = M; ws_ml[2 * row + 1] = L; }
+    } else {
+      p.out[(long long)token * p.out_stride + (long long)(kvh * G + row) * D + d] =
+          __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
+  }
+}
+
+// Merges the split results of one (sequence, head): grid (n_seqs, A), D threads.
+__global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                  __nv_bfloat16* __restrict__ out, long long out_stride,
+                                  const int* __restrict__ cu_tokens, int A, int Kh, int D,
+                                  int splits) {
+  const int seq = blockIdx.x, a = blockIdx.y;
+  const int G = A / Kh, kvh = a / G, row = a - kvh * G;
+  const size_t base = (size_t)(seq * Kh + kvh) * splits;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, ws_ml[(base + s) * 32 + 2 * row]);
+  const int token = cu_tokens[seq];
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = ws_ml[(base + s) * 32 + 2 * row];
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - M);
+      L += ws_ml[(base + s) * 32 + 2 * row + 1] * f;
+      acc += ws_o[((base + s) * 16 + row) * D + d] * f;
+    }
+    out[(long long)token * out_stride + (long long)a * D + d] =
+        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+}
+
+template <int D>
+int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
+  const int bytes = (64 + 4 * 64) * D * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return fb_fail(2, "attention_prefill: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  attn_prefill_kernel<D><<<dim3(q_blocks, p.A), THREADS, bytes, stream>>>(p);
+  return fb_check_launch("attention_prefill");
+}
+
+template <int D>
+int launch_decode(const AttnParams& p, cudaStream_t stream) {
+  int bytes = (16 + 4 * 64) * D * 2;
+  const int merge = 4 * 16 * D * 4 + 2 * 4 * 16 * 4 + 16 * D * 2;
+  if (merge > bytes) bytes = merge;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  attn_decode_kernel<D><<<dim3(p.n_seqs, p.Kh, p.splits), THREADS, bytes, stream>>>(p);
+  int rc = fb_check_launch("attention_decode");
+  if (rc || p.splits == 1) return rc;
+  attn_merge_kernel<<<dim3(p.n_seqs, p.A), D < 32 ? 32 : D, 0, stream>>>(
+      p.ws_o, p.ws_ml, p.out, p.out_stride, p.cu_tokens, p.A, p.Kh, D, p.splits);
+  return fb_check_launch("attention_merge");
+}
+
+int check_common(const char* what, int n_seqs, int A, int Kh, int D, long long q_stride,
+                 long long out_stride, const void* q, const void* k, const void* v,
+                 long long page_stride, long long head_stride) {
+  FB_REQUIRE(n_seqs > 0 && A > 0 && Kh > 0 && A % Kh == 0, "%s: bad head counts A=%d Kh=%d", what, A, Kh);
+  FB_REQUIRE(D == 16 || D == 32 || D == 64 || D == 128,
+             "%s: head size %d is not built for the tensor-core kernel (16, 32, 64, 128)", what, D);
+  FB_REQUIRE(A / Kh <= 16, "%s: %d query heads per kv head exceed the 16-row tile", what, A / Kh);
+  FB_REQUIRE(q_stride % 8 == 0 && out_stride % 2 == 0 && page_stride % 8 == 0 && head_stride % 8 == 0,
+             "%s: strides must keep 16-byte alignment", what);
+  FB_REQUIRE(((uintptr_t)q % 16) == 0 && ((uintptr_t)k % 16) == 0 && ((uintptr_t)v % 16) == 0,
+             "%s: pointers must be 16-byte aligned", what);
+  return 0;
+}
+
+}  // namespace
+
+// Prompts (or any mix of token counts): q [T, A*D] rows with stride q_stride.
+// `q_blocks` bounds the number of 64-row query blocks: sum over sequences of
+// ceil(q_len / 64); blocks beyond the real count return at once.
+FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, long long out_stride,
+                                const int* cu_tokens, const int* kv_lens, const int* page_table,
+                                int max_pages, const void* k_cache, const void* v_cache,
+                                long long page_stride, long long head_stride, int n_seqs,
+                                int q_blocks, int A, int Kh, int D, float scale,
+                                cudaStream_t stream) {
+  int rc = check_common("attention_prefill", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
+                        v_cache, page_stride, head_stride);
+  if (rc) return rc;
+  if (q_blocks <= 0) return 0;
+  AttnParams p{};
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.cu_tokens = cu_tokens; p.kv_lens = kv_lens; p.page_table = page_table; p.max_pages = max_pages;
+  p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.page_stride = page_stride; p.head_stride = head_stride;
+  p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E; p.splits = 1;
+  switch (D) {
+    case 16: return launch_prefill<16>(p, q_blocks, stream);
+    case 32: return launch_prefill<32>(p, q_blocks, stream);
+    case 64: return launch_prefill<64>(p, q_blocks, stream);
+    default: return launch_prefill<128>(p, q_blocks, stream);
+  }
+}
+
+// One token per sequence. `splits` CTAs share each (sequence, kv head); with
+// splits > 1 the workspaces must hold n_seqs*Kh*splits*16*D and
+// n_seqs*Kh*splits*32 floats. A sequence with kv_lens == 0 is padding: its
+// output rows are zeros.
+FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
+                               const int* cu_tokens, const int* kv_lens, const int* page_table,
+                               int max_pages, const void* k_cache, const void* v_cache,
+                               long long page_stride, long long head_stride, int n_seqs, int A,
+                               int Kh, int D, float scale, int splits, float* ws_o, float* ws_ml,
+                               cudaStream_t stream) {
+  int rc = check_common("attention_decode", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
+                        v_cache, page_stride, head_stride);
+  if (rc) return rc;
+  FB_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: bad split count %d", splits);
+  FB_REQUIRE(splits == 1 || (ws_o && ws_ml), "attention_decode: split results need workspaces");
+  AttnParams p{};
+  p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
+  p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
+  p.cu_tokens = cu_tokens; p.kv_lens = kv_lens; p.page_table = page_table; p.max_pages = max_pages;
+  p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.page_stride = page_stride; p.head_stride = head_stride;
+  p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E;
+  p.splits = splits; p.ws_o = ws_o; p.ws_ml = ws_ml;
+  switch (D) {
+    case 16: return launch_decode<16>(p, stream);
+    case 32: return launch_decode<32>(p, stream);
+    case 64: return launch_decode<64>(p, stream);
+    default: return launch_decode<128>(p, stream);
+  }
+}

@@ -41,6 +41,12 @@ _SIGNATURES = {
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
                    c_int, c_int, c_ll, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
+    "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
+                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
+                             c_float, c_void_p],
+    "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
+                            c_int, c_void_p, c_void_p, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_void_p],
 }
@@ -315,13 +321,67 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
 
 
 # ------------------------------------------------------------------ attention
+FAST_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention kernels
+
+
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
               k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int,
               head_dim: int, scale: float, window: int = 0, ring_pages: int = 0) -> torch.Tensor:
     """Attention of a step's tokens over the cache: the kernel that fits the
-    element type and the step (prompts or single tokens)."""
-    return attention_simt(q, out, ctx.positions, ctx.seq_of_token, page_table, k_cache, v_cache,
-                          num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
+    element type and the step. bfloat16 with a built head size runs on the
+    tensor cores (one kernel for single-token steps, one for prompts); float32,
+    windows and other head sizes run on the CUDA cores."""
+    fast = (q.dtype == torch.bfloat16 and head_dim in FAST_HEAD_DIMS and window == 0
+            and ring_pages == 0 and num_heads // num_kv_heads <= 16)
+    if not fast:
+        return attention_simt(q, out, ctx.positions, ctx.seq_of_token, page_table, k_cache,
+                              v_cache, num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
+    if ctx.is_decode:
+        pairs = ctx.n_seqs * num_kv_heads
+        bound = max(1, (ctx.max_kv_len + PAGE - 1) // PAGE)
+        splits = max(1, min(bound, (4 * SM_COUNT + pairs - 1) // pairs))
+        return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
+                                num_heads, num_kv_heads, head_dim, scale, splits)
+    blocks = sum((ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] + 63) // 64
+                 for i in range(ctx.n_seqs))
+    return attention_prefill(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
+                             num_heads, num_kv_heads, head_dim, scale, blocks)
+
+
+def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
+                      num_kv_heads, head_dim, scale, q_blocks) -> torch.Tensor:
+    """Tensor-core attention for steps of any token counts; `q_blocks` is the
+    sum over sequences of ceil(tokens / 64)."""
+    _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
+    _call("fb_attention_prefill", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
+          _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
+          _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
+          v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), kv_lens.numel(), q_blocks,
+          num_heads, num_kv_heads, head_dim, float(scale), _stream())
+    return out
+
+
+def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
+                     num_kv_heads, head_dim, scale, splits) -> torch.Tensor:
+    """Tensor-core attention for one token per sequence, the cache range split
+    over `splits` CTAs per (sequence, kv head); two launches when splits > 1."""
+    _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
+    n = kv_lens.numel()
+    ws_o = ws_ml = None
+    if splits > 1:
+        ws_o = torch.empty(n * num_kv_heads * splits * 16 * head_dim, dtype=torch.float32,
+                           device=q.device)
+        ws_ml = torch.empty(n * num_kv_heads * splits * 32, dtype=torch.float32, device=q.device)
+        _COUNT[0] += 1  # the merge kernel
+    _call("fb_attention_decode", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
+          _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
+          _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
+          v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
+          head_dim, float(scale), splits, 0 if ws_o is None else ws_o.data_ptr(),
+          0 if ws_ml is None else ws_ml.data_ptr(), _stream())
+    return out
 
 
 def attention_simt(q: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,

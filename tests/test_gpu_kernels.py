@@ -172,3 +172,146 @@ def test_gemm_falls_back_for_shapes_tma_cannot_address(ops):
     close(out, x.double() @ w.double().T, 1e-3, 1e-5)
     with pytest.raises(ops.KernelError, match="multiples of 8"):
         ops.gemm_tc(x, w, out, 20, 1, 16)
+
+
+# ------------------------------------------------------------------ attention
+def make_paged_case(lens_q, lens_kv, A, Kh, D, dtype, seed=0, sharp=False):
+    """Random q and a paged cache whose pages are scattered and shared by no
+    two sequences. Returns everything the kernels take plus dense K, V."""
+    g = torch.Generator().manual_seed(seed)
+    n = len(lens_q)
+    T = sum(lens_q)
+    pages_per = [(kv + 63) // 64 for kv in lens_kv]
+    total_pages = sum(pages_per) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    width = max(pages_per)
+    table = torch.zeros(n, width, dtype=torch.int32)
+    store = torch.randn(total_pages, 2, Kh, 64, D, generator=g)  # unused rows hold noise
+    dense_k, dense_v = [], []
+    at = 0
+    for i in range(n):
+        mine = perm[at:at + pages_per[i]]
+        at += pages_per[i]
+        table[i, :len(mine)] = torch.tensor(mine, dtype=torch.int32)
+        k = torch.randn(lens_kv[i], Kh, D, generator=g)
+        v = torch.randn(lens_kv[i], Kh, D, generator=g)
+        if sharp:  # one far key per sequence stands out for every head
+            k[lens_kv[i] // 3] *= 6.0
+        for j in range(lens_kv[i]):
+            store[mine[j // 64], 0, :, j % 64] = k[j]
+            store[mine[j // 64], 1, :, j % 64] = v[j]
+        dense_k.append(k)
+        dense_v.append(v)
+    q = torch.randn(T, A * D, generator=g)
+    cu = [0]
+    for x in lens_q:
+        cu.append(cu[-1] + x)
+    positions = torch.cat([torch.arange(kv - ql, kv) for ql, kv in zip(lens_q, lens_kv)])
+    seq_of = torch.cat([torch.full((ql,), i) for i, ql in enumerate(lens_q)])
+    store = store.to(dtype).to(DEV)
+    case = dict(q=q.to(dtype).to(DEV), table=table.to(DEV), k=store[:, 0], v=store[:, 1],
+                cu=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                kv=torch.tensor(lens_kv, dtype=torch.int32, device=DEV),
+                positions=positions.int().to(DEV), seq_of=seq_of.int().to(DEV), cu_host=cu)
+    # plain attention on the rounded inputs
+    want = torch.zeros(T, A * D, dtype=torch.float64)
+    G = A // Kh
+    qd = case["q"].double().cpu().view(T, A, D)
+    for i in range(n):
+        k = dense_k[i].to(dtype).double()
+        v = dense_v[i].to(dtype).double()
+        for r in range(lens_q[i]):
+            tok, pos = cu[i] + r, lens_kv[i] - lens_q[i] + r
+            for a in range(A):
+                s = (k[:pos + 1, a // G] @ qd[tok, a]) / math.sqrt(D)
+                p = torch.softmax(s, 0)
+                want[tok, a * D:(a + 1) * D] = p @ v[:pos + 1, a // G]
+    return case, want
+
+
+ATT_CASES = [  # (q lengths, kv lengths, heads, kv heads, head_dim)
+    ([1, 1, 1], [1, 64, 65], 4, 2, 16),
+    ([1, 1, 1, 1], [200, 3, 128, 129], 6, 2, 32),
+    ([1, 1], [500, 77], 8, 8, 64),
+    ([1, 1, 1], [300, 64, 1000], 12, 4, 128),
+    ([5, 70, 1], [5, 70, 130], 4, 2, 16),
+    ([64, 65, 3], [64, 65, 200], 6, 3, 32),
+    ([130, 20], [130, 220], 4, 1, 64),
+    ([100, 7, 129], [100, 300, 129], 6, 2, 128),
+]
+
+
+@pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", ATT_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_cuda_cores(ops, lens_q, lens_kv, A, Kh, D, dtype):
+    case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, dtype, sharp=True)
+    out = torch.full_like(case["q"], 5.0)
+    ops.attention_simt(case["q"], out, case["positions"], case["seq_of"], case["table"], case["k"],
+                       case["v"], A, Kh, D, 1.0 / math.sqrt(D))
+    close(out, want, 2e-5 if dtype == torch.float32 else 3e-2, 1e-5 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", ATT_CASES)
+def test_attention_tensor_cores_any_token_counts(ops, lens_q, lens_kv, A, Kh, D):
+    case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, torch.bfloat16, seed=1, sharp=True)
+    out = torch.full_like(case["q"], 5.0)
+    blocks = sum((x + 63) // 64 for x in lens_q)
+    ops.attention_prefill(case["q"], out, case["cu"], case["kv"], case["table"], case["k"],
+                          case["v"], A, Kh, D, 1.0 / math.sqrt(D), blocks + 2)
+    close(out, want, 3e-2, 1e-2)
+
+
+@pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", [c for c in ATT_CASES if max(c[0]) == 1])
+@pytest.mark.parametrize("splits", [1, 2, 7])
+def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, splits):
+    # a padding row (length 0) sits between the real ones and must come out as zeros
+    lens_q, lens_kv = list(lens_q), list(lens_kv)
+    case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, torch.bfloat16, seed=2, sharp=True)
+    kv = torch.cat([case["kv"], torch.zeros(1, dtype=torch.int32, device=DEV)])
+    cu = torch.cat([case["cu"], case["cu"][-1:] + 1])
+    q = torch.cat([case["q"], rnd(1, A * D, dtype=torch.bfloat16)])
+    table = torch.cat([case["table"], torch.zeros_like(case["table"][:1])])
+    out = torch.full_like(q, 5.0)
+    ops.attention_decode(q, out, cu, kv, table, case["k"], case["v"], A, Kh, D,
+                         1.0 / math.sqrt(D), splits)
+    close(out[:-1], want, 3e-2, 1e-2)
+    assert float(out[-1].abs().max()) == 0.0
+
+
+def test_attention_picks_out_a_far_key(ops):
+    """One key among a thousand matches the query; the output must be that
+    key's value, whichever kernel runs."""
+    A, Kh, D, L = 4, 2, 64, 1000
+    case, _ = make_paged_case([1], [L], A, Kh, D, torch.bfloat16, seed=3)
+    k, v, table = case["k"], case["v"], case["table"]
+    k.zero_()
+    target = 137
+    page, row = int(table[0, target // 64]), target % 64
+    q = torch.zeros(1, A * D, dtype=torch.bfloat16, device=DEV)
+    q[:, ::D] = 8.0  # first element of every head
+    k[page, :, row, 0] = 8.0
+    want = v[page, :, row].float().repeat_interleave(A // Kh, 0).reshape(1, A * D)
+    for run in ("simt", "decode", "prefill"):
+        out = torch.zeros_like(q)
+        if run == "simt":
+            ops.attention_simt(q, out, case["positions"], case["seq_of"], table, k, v, A, Kh, D, 1.0)
+        elif run == "decode":
+            ops.attention_decode(q, out, case["cu"], case["kv"], table, k, v, A, Kh, D, 1.0, 5)
+        else:
+            ops.attention_prefill(q, out, case["cu"], case["kv"], table, k, v, A, Kh, D, 1.0, 1)
+        close(out, want, 2e-2, 1e-2)
+
+
+def test_attention_refuses_sizes_it_does_not_build(ops):
+    case, _ = make_paged_case([1], [10], 4, 2, 48, torch.bfloat16)
+    out = torch.zeros_like(case["q"])
+    with pytest.raises(ops.KernelError, match="head size 48"):
+        ops.attention_decode(case["q"], out, case["cu"], case["kv"], case["table"], case["k"],
+                             case["v"], 4, 2, 48, 1.0, 1)
+    # the dispatcher serves the same size on the CUDA cores
+    ops.attention_simt(case["q"], out, case["positions"], case["seq_of"], case["table"], case["k"],
+                       case["v"], 4, 2, 48, 1.0 / math.sqrt(48))
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        bad, _ = make_paged_case([1], [10], 2, 2, 24, torch.bfloat16)
+        ops.attention_simt(bad["q"], torch.zeros_like(bad["q"]), bad["positions"], bad["seq_of"],
+                           bad["table"], bad["k"], bad["v"], 2, 2, 24, 1.0)

@@ -181,7 +181,16 @@ def test_trace_run_program(tiny_folders, oracle, tmp_path, dtype):
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
     vocab = expected[0].shape[1]
+    all_got, all_want = [], []
     for s, rows in zip(steps, plan):
         got = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab)
         want = np.concatenate([expected[r][p:p + n] for r, p, n in rows], 0)
-        tiny.assert_logits_close(got, want, dtype, f"trace step {s['step']}")
+        assert got.shape == want.shape, f"trace step {s['step']}"
+        if dtype == "float32":
+            tiny.assert_logits_close(got, want, dtype, f"trace step {s['step']}")
+        else:  # a step of two rows is too small a sample for a 99.9 % rule: bound its worst
+            scale = max(1.0, float(np.abs(want).max()))
+            assert np.abs(got - want).max() <= 5e-2 * scale, f"trace step {s['step']}"
+        all_got.append(got)
+        all_want.append(want)
+    tiny.assert_logits_close(np.concatenate(all_got), np.concatenate(all_want), dtype, "whole trace")
