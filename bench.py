@@ -188,6 +188,7 @@ def run(args) -> dict:
     max_batch = max(batch, 64 if not args.skip_points else batch)
     engine = Engine.from_random(cfg, seed=0, dtype="bfloat16",
                                 max_tokens=max_batch * CONTEXT, max_slots=max_batch, norm_std=0.0)
+    engine.use_graphs = not args.no_graphs
 
     # ---------------------------------------------------------------- prefill
     prompt = token_rows(SplitMix64(1), 1, PREFILL_TOKENS, 128000)[0]
@@ -276,6 +277,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=0,
                         help="fewer layers than the configuration's 28 (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--no-graphs", action="store_true",
+                        help="launch decode kernels one by one (for profilers)")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

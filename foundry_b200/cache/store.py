@@ -111,8 +111,9 @@ class SequenceCache:
             if isinstance(req, KVRequest):
                 by_key.setdefault(req, []).append(entry)
             elif isinstance(req, StateRequest):
-                self.state[entry] = torch.zeros((self.max_slots, *req.shape), dtype=req.dtype,
-                                                device=device)
+                # one row more than slots: padding rows of a step point at the last row
+                self.state[entry] = torch.zeros((self.max_slots + 1, *req.shape),
+                                                dtype=req.dtype, device=device)
             elif req is not None:
                 raise TypeError(f"cache entry {entry}: unknown request {req!r}")
         self.groups: List[KVGroup] = []
@@ -126,6 +127,7 @@ class SequenceCache:
             for e in entries:
                 self.group_of[e] = group
         self.table = SlotTable(self.max_slots, [g.pages for g in self.groups])
+        self.scratch_slot = self.max_slots  # state row that padding rows may scribble on
 
     # --------------------------------------------------------------- slots
     def open_sequence(self) -> int:

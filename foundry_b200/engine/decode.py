@@ -100,7 +100,11 @@ class DecodeRunner:
             plain_logits = self.logits
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, pool=self.engine.graph_pool()):
+            # "relaxed": torch's pinned-memory allocator may query an event of an
+            # earlier host copy while the capture is open; that call touches
+            # nothing of this capture and must not invalidate it
+            with torch.cuda.graph(graph, pool=self.engine.graph_pool(),
+                                  capture_error_mode="relaxed"):
                 self._body()
             ops.add_launches(-self.kernels_per_step)  # recorded, not launched
             self.graph = graph
@@ -157,7 +161,7 @@ class DecodeSession:
         h[2][:n] = np.arange(n)
         h[2][n:] = -1
         h[4][:n] = self.slots
-        h[4][n:] = 0
+        h[4][n:] = cache.scratch_slot
         h[6][:n] = lengths
         h[6][:n] += 1
         h[6][n:] = 0

@@ -1,0 +1,232 @@
+"""Generation through the entry points: greedy tokens against the plain
+implementation, stop tokens, rows that end earlier, slots used again, more
+requests than slots, temperature sampling restated on the host, long decoding,
+the first tokens of a sequence, and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+
+
+def engine_for(folder, dtype, **kw):
+    import foundry_b200 as fb
+    kw.setdefault("max_tokens", 1024)
+    kw.setdefault("max_slots", 8)
+    return fb.Engine.from_folder(folder, dtype=dtype, **kw)
+
+
+def plain_greedy_is_decisive(cfg, w, prompt, tokens, margin):
+    """Whether every greedy choice of the plain model along `tokens` beats the
+    runner-up by `margin`: then a 16-bit engine must choose the same."""
+    seq = list(prompt)
+    for t in tokens:
+        row = plain.forward(cfg, w, seq)[-1]
+        top = torch.topk(row, 2).values
+        if float(top[0] - top[1]) < margin:
+            return False
+        seq.append(t)
+    return True
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_equals_the_plain_model(tiny_folders, name):
+    cfg, w = plain.read_model(tiny_folders[name])
+    prompts = [tiny.random_tokens(40 + i, n, cfg["vocab_size"]) for i, n in enumerate((5, 11, 17, 1, 40))]
+    want = [plain.greedy_generate(cfg, w, p, 8) for p in prompts]
+    engine = engine_for(tiny_folders[name], "float32")
+    out = engine.generate(prompts, 8, eos_token_id=[])
+    assert out.token_ids == want
+    assert out.finish_reason == ["length"] * 5 and len(out.decode_steps) == 7
+    # bfloat16: equal wherever the plain model's choice is not a near tie
+    # (the reference's generation rule, src/eval/generation.rs:132-176)
+    got = engine_for(tiny_folders[name], "bfloat16").generate(prompts, 8, eos_token_id=[]).token_ids
+    for p, g, t in zip(prompts, got, want):
+        if g != t:
+            k = next(i for i, (a, b) in enumerate(zip(g, t)) if a != b)
+            row = plain.forward(cfg, w, list(p) + t[:k])[-1]
+            assert float(row[t[k]] - row[g[k]]) < 0.05, (g, t)
+    engine.cache.table.check()
+    assert engine.cache.table.slots.held == 0
+
+
+def test_stop_tokens_early_rows_and_slot_reuse(tiny_folders):
+    """Make a stop token of what the plain model generates third for one
+    prompt: that row ends there (keeping the token) while the others go on,
+    and later batches run in the slots and pages it gave back."""
+    name = "tiny_b"
+    cfg, w = plain.read_model(tiny_folders[name])
+    prompts = [tiny.random_tokens(60 + i, n, cfg["vocab_size"]) for i, n in enumerate((7, 30, 3, 12, 9, 21))]
+    free_run = [plain.greedy_generate(cfg, w, p, 10) for p in prompts]
+    stop = free_run[0][2]
+    want = [plain.greedy_generate(cfg, w, p, 10, eos=[stop]) for p in prompts]
+    engine = engine_for(tiny_folders[name], "float32", max_slots=2, max_tokens=256)
+    out = engine.generate(prompts, 10, eos_token_id=[stop])
+    assert out.token_ids == want
+    assert out.token_ids[0][-1] == stop and len(out.token_ids[0]) <= 3
+    assert out.finish_reason[0] == "stop"
+    assert out.batches == [[0, 1], [2, 3], [4, 5]]
+    assert engine.cache.table.slots.held == 0
+    engine.cache.table.check()
+    # the config's own stop tokens apply when none are given
+    assert engine_for(tiny_folders[name], "float32").generate(prompts[:1], 4).token_ids[0] == \
+        plain.greedy_generate(cfg, w, prompts[0], 4, eos=cfg["eos_token_id"])
+
+
+def test_temperature_sampling_is_the_host_restatement(tiny_folders):
+    """Each sampled token is the argmax of logits / T + Gumbel noise, the noise
+    being a function of (seed, request, count) only: recomputed here from the
+    plain model's logits, and the same in another batching."""
+    from foundry_b200 import SamplingParams
+    name = "tiny_b"
+    cfg, w = plain.read_model(tiny_folders[name])
+    prompts = [tiny.random_tokens(80 + i, n, cfg["vocab_size"]) for i, n in enumerate((1, 7, 40, 90))]
+    params = SamplingParams(temperature=0.8, seed=1234)
+    engine = engine_for(tiny_folders[name], "float32")
+    out = engine.generate(prompts, 16, eos_token_id=[], sampling=params)
+    assert [len(r) for r in out.token_ids] == [16] * 4
+    for r, (prompt, row) in enumerate(zip(prompts, out.token_ids)):
+        seq = list(prompt)
+        for count, token in enumerate(row):
+            scores = plain.sample_scores(plain.forward(cfg, w, seq)[-1], 0.8, 1234, r, count)
+            best = int(torch.argmax(scores))
+            # equal, or a near tie of the two perturbed scores
+            assert token == best or float(scores[best] - scores[token]) < 1e-3, (r, count)
+            seq.append(token)
+    assert len({tuple(r) for r in out.token_ids}) > 1
+    one_by_one = engine_for(tiny_folders[name], "float32", max_slots=1).generate(
+        prompts, 16, eos_token_id=[], sampling=params)
+    assert one_by_one.token_ids == out.token_ids and len(one_by_one.batches) == 4
+    other_seed = engine.generate(prompts, 16, eos_token_id=[],
+                                 sampling=SamplingParams(temperature=0.8, seed=99))
+    assert other_seed.token_ids != out.token_ids
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_stays_on_the_plain_model(tiny_folders, dtype):
+    """200 single-token steps after a short prompt, across several page
+    boundaries and graph re-captures: every step's logits are checked."""
+    from foundry_b200.engine import SequenceStep
+    name = "tiny_b"
+    cfg, w = plain.read_model(tiny_folders[name])
+    tokens = tiny.random_tokens(5, 230, cfg["vocab_size"])
+    want = plain.forward(cfg, w, tokens).numpy()
+    engine = engine_for(tiny_folders[name], dtype)
+    slot = engine.open_sequence()
+    rows = [engine.step([SequenceStep(slot, tokens[:30], list(range(30)))]).cpu().numpy()]
+    for t in tokens[30:]:
+        rows.append(engine.step([SequenceStep(slot, [t], [0])]).cpu().numpy())
+    engine.close_sequence(slot)
+    tiny.assert_logits_close(np.concatenate(rows), want, dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_tokens_of_a_sequence(tiny_folders, dtype):
+    """Position 0 and its neighbours, started in every way: a one-token prompt,
+    then tokens one by one; two tokens then one; and the same in a slot that a
+    longer sequence used before (stale keys behind the new length)."""
+    from foundry_b200.engine import SequenceStep
+    name = "tiny_a"
+    cfg, w = plain.read_model(tiny_folders[name])
+    tokens = tiny.random_tokens(9, 6, cfg["vocab_size"])
+    want = plain.forward(cfg, w, tokens).numpy()
+    engine = engine_for(tiny_folders[name], dtype, max_slots=1, max_tokens=128)
+    for cuts in ([1, 1, 1, 1, 1, 1], [2, 1, 3], [6], [1, 5]):
+        stale = engine.open_sequence()  # fill the only slot's pages with other keys
+        engine.step([SequenceStep(stale, tiny.random_tokens(3, 100, cfg["vocab_size"]), [])])
+        engine.close_sequence(stale)
+        slot = engine.open_sequence()
+        assert slot == stale
+        rows, at = [], 0
+        for n in cuts:
+            rows.append(engine.step([SequenceStep(slot, tokens[at:at + n], list(range(n)))]).cpu().numpy())
+            at += n
+        engine.close_sequence(slot)
+        tiny.assert_logits_close(np.concatenate(rows), want, dtype, f"cuts {cuts}")
+
+
+def test_padding_changes_no_result(tiny_folders):
+    """Three live sequences run in a four-row graph; the same three sequences
+    beside a fourth give the same logits row for row."""
+    from foundry_b200.engine import SequenceStep
+    name = "tiny_b"
+    cfg, _ = plain.read_model(tiny_folders[name])
+    engine = engine_for(tiny_folders[name], "float32")
+    prompts = [tiny.random_tokens(20 + i, n, cfg["vocab_size"]) for i, n in enumerate((9, 33, 64, 5))]
+
+    def run(count):
+        slots = [engine.open_sequence() for _ in range(count)]
+        engine.step([SequenceStep(s, p, []) for s, p in zip(slots, prompts)])
+        out = [engine.step([SequenceStep(s, [7 + i], [0]) for s in slots]).cpu().numpy()
+               for i in range(3)]
+        for s in slots:
+            engine.close_sequence(s)
+        return np.stack(out)
+
+    three, four = run(3), run(4)
+    assert np.array_equal(three, four[:, :3])
+
+
+def test_refusals_of_the_step_function(tiny_folders):
+    from foundry_b200.cache import CacheFull
+    from foundry_b200.engine import SequenceStep
+    engine = engine_for(tiny_folders["tiny_a"], "float32", max_slots=2, max_tokens=128)
+    slot = engine.open_sequence()
+    with pytest.raises(ValueError, match="vocabulary"):
+        engine.step([SequenceStep(slot, [256], [0])])
+    with pytest.raises(ValueError, match="twice"):
+        engine.step([SequenceStep(slot, [1], [0]), SequenceStep(slot, [2], [0])])
+    with pytest.raises(ValueError, match="not open"):
+        engine.step([SequenceStep(1, [1, 2], [0])])
+    with pytest.raises(ValueError, match="no token"):
+        engine.step([SequenceStep(slot, [], [])])
+    with pytest.raises(ValueError, match="wanted place"):
+        engine.step([SequenceStep(slot, [1, 2], [2])])
+    with pytest.raises(ValueError, match="positions"):
+        engine.step([SequenceStep(slot, [1] * 129, [])])
+    other = engine.open_sequence()
+    engine.step([SequenceStep(slot, [1] * 65, [])])
+    with pytest.raises(CacheFull):
+        engine.step([SequenceStep(other, [1] * 65, [])])  # 2 pages held, 2 more wanted of 2
+    assert engine.cache.length(other) == 0 and engine.cache.length(slot) == 65  # nothing changed
+    engine.cache.table.check()
+
+
+def test_command_line_run(tiny_folders):
+    cfg, w = plain.read_model(tiny_folders["tiny_a"])
+    prompt = [5, 17, 3, 200]
+    want = plain.greedy_generate(cfg, w, prompt, 6, eos=[cfg["eos_token_id"]])
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "run", "--model",
+                           tiny_folders["tiny_a"], "--prompt-ids", "5,17,3,200", "--max-new-tokens",
+                           "6", "--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert json.loads(proc.stdout.strip()) == want
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "run", "--model",
+                           tiny_folders["tiny_a"], "--prompt-ids", "5,999", "--max-new-tokens", "2"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode != 0 and "vocabulary" in proc.stderr
+
+
+def test_command_line_bench_writes_a_report(tiny_folders, tmp_path):
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "bench", "--model",
+                           tiny_folders["tiny_b"], "--prompt-tokens", "20", "--new-tokens", "5",
+                           "--runs", "2", "--batch-size", "3", "--out", str(tmp_path)],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    report = json.loads((tmp_path / "report.json").read_text())
+    assert report["config"]["prompt_tokens"] == 20 and len(report["runs"]) == 2
+    assert len(report["prompt_ids"]) == 3 and len(report["prompt_ids"][0]) == 20
+    assert len(report["runs"][0]["decode_step_ns"]) == 4  # new tokens count the prompt step's
+    assert all(len(r) == 5 for r in report["runs"][0]["token_ids"])
+    assert report["runs"][0]["token_ids"] == report["runs"][1]["token_ids"]
+    assert report["metrics"]["decode_tokens_per_s"]["count"] == 2
+    assert report["metadata"]["model_parameter_count"] > 0

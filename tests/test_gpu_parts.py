@@ -1,0 +1,315 @@
+"""Each part alone against the plain implementation's function for it, and the
+generality of the assembly: a toy mixer with state of its own, defined here,
+is registered, built into a model beside attention layers, loaded from a
+folder the random-weights mode wrote, and stepped in several cuttings, without
+a change to the library's files. The toy model's schedule also names a layer
+twice and lets its second run read the first run's cache."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as plain
+import tiny
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def make_ctx(cache, slots, token_lists, vocab=1000, want=None):
+    from foundry_b200.engine import SequenceStep, build_context
+    steps = [SequenceStep(s, t, list(range(len(t))) if want is None else want)
+             for s, t in zip(slots, token_lists)]
+    return build_context(cache, steps, vocab, DEV)
+
+
+def tol(dtype):
+    return dict(atol=3e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=4e-2, rtol=2e-2)
+
+
+def assert_close(got, want, dtype, scale=1.0):
+    t = tol(dtype)
+    got, want = got.double().cpu(), want.double().cpu()
+    err = (got - want).abs()
+    bound = t["atol"] * scale + t["rtol"] * want.abs()
+    frac = float((err <= bound).double().mean())
+    assert frac >= (1.0 if dtype == torch.float32 else 0.999), \
+        f"{frac:.5f} close, max err {float(err.max()):.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_part(dtype):
+    from foundry_b200.parts import RMSNorm
+    part = RMSNorm(96, 1e-6, dtype=dtype, device=DEV)
+    w = (1 + 0.1 * torch.randn(96)).to(dtype)
+    part.load("n", lambda name: w.to(DEV))
+    resid = torch.randn(7, 96, device=DEV)
+    delta = torch.randn(7, 96, device=DEV).to(dtype)
+    r0 = resid.clone()
+    out = part.add_norm(resid, delta)
+    want = plain.rms_norm(r0.double().cpu() + delta.double().cpu(), w.double(), 1e-6)
+    assert out.dtype == dtype
+    assert_close(out, want, dtype)
+    assert part.expected_tensors("x.norm") == {"x.norm.weight": part.expected_tensors("x.norm")["x.norm.weight"]}
+    assert part.expected_tensors("x.norm")["x.norm.weight"].shape == (96,)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part(dtype):
+    from foundry_b200.parts import SwiGLU
+    H, I, T = 96, 176, 9
+    part = SwiGLU(H, I, dtype=dtype, device=DEV)
+    w = {f"m.{n}.weight": (0.1 * torch.randn(*s)).to(dtype)
+         for n, s in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I)))}
+    assert {k: v.shape for k, v in part.expected_tensors("m").items()} == \
+        {k: tuple(v.shape) for k, v in w.items()}
+    part.load("m", lambda name: w[name].to(DEV))
+    x = torch.randn(T, H).to(dtype)
+    got = part.forward(None, x.to(DEV))
+    want = plain.mlp(x.double(), {k: v.double() for k, v in w.items()}, "m")
+    assert_close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_attention_part_alone_in_two_cuttings(name, dtype):
+    """The mixer with a cache of its own: whole sequences of unequal lengths in
+    one step, and the same split into a prompt part and single tokens."""
+    from foundry_b200.cache import SequenceCache
+    from foundry_b200.config import LlamaConfig
+    from foundry_b200.models.llama import build_llama_spec
+    from foundry_b200.parts import MIXERS
+    cfg = tiny.CONFIGS[name]
+    spec = build_llama_spec(LlamaConfig.parse(cfg))
+    part = MIXERS.build(spec.layers[0].mixer, dtype=dtype, device=DEV)
+    H = cfg["hidden_size"]
+    torch.manual_seed(1)
+    w = {k: (0.15 * torch.randn(*e.shape)).to(dtype) for k, e in part.expected_tensors("a").items()}
+    part.load("a", lambda n: w[n].to(DEV))
+    cache = SequenceCache({0: part.cache_request()}, 1024, 4, dtype, DEV)
+    lens = [70, 3, 33]
+    xs = [torch.randn(n, H).to(dtype) for n in lens]
+    wd = {k: v.double() for k, v in w.items()}
+    want = [plain.attention(x.double(), wd, "a", cfg, list(range(len(x)))) for x in xs]
+
+    slots = [cache.open_sequence() for _ in lens]
+    ctx = make_ctx(cache, slots, [[0] * n for n in lens])
+    got = part.forward(ctx, torch.cat(xs).to(DEV), cache.view(0, True))
+    assert_close(got, torch.cat(want), dtype, scale=float(torch.cat(want).abs().max()))
+    for s in slots:
+        cache.close_sequence(s)
+
+    slots = [cache.open_sequence() for _ in lens]
+    head = [max(1, n - 2) for n in lens]
+    ctx = make_ctx(cache, slots, [[0] * h for h in head])
+    outs = [part.forward(ctx, torch.cat([x[:h] for x, h in zip(xs, head)]).to(DEV), cache.view(0, True))]
+    pieces = {i: [o] for i, o in enumerate(torch.split(outs[0], head))}
+    for step in range(2):
+        live = [i for i, n in enumerate(lens) if head[i] + step < n]
+        ctx = make_ctx(cache, [slots[i] for i in live], [[0]] * len(live))
+        o = part.forward(ctx, torch.cat([xs[i][head[i] + step:head[i] + step + 1] for i in live]).to(DEV),
+                         cache.view(0, True))
+        for j, i in enumerate(live):
+            pieces[i].append(o[j:j + 1])
+    got = torch.cat([torch.cat(pieces[i]) for i in range(len(lens))])
+    assert_close(got, torch.cat(want), dtype, scale=float(torch.cat(want).abs().max()))
+
+
+def test_position_encoding_parts_follow_the_reference_bands():
+    """llama3 scaling at D = 128, theta = 5e5, factor 32: the three frequencies
+    the reference pins (j = 0 unscaled, j = 32 blended, j = 63 divided;
+    src/models/llama/rotary_emb.rs:203-239) against a float64 restatement."""
+    from foundry_b200.parts import llama3_inv_freq, plain_inv_freq
+    got = llama3_inv_freq(128, 500000.0, 32.0, 1.0, 4.0, 8192)
+    for j in (0, 32, 63):
+        f = 500000.0 ** (-2.0 * j / 128)
+        wl = 2 * math.pi / f
+        if wl < 8192 / 4:
+            want = f
+        elif wl > 8192 / 1:
+            want = f / 32
+        else:
+            s = (8192 / wl - 1.0) / (4.0 - 1.0)
+            want = (1 - s) * f / 32 + s * f
+        assert abs(got[j] - want) <= 1e-5 * want, j
+    assert got.dtype == np.float32 and got.shape == (64,)
+    plain64 = plain_inv_freq(64, 100000.0)  # rotary_emb.rs:241-259
+    for j in (0, 16, 31):
+        assert abs(plain64[j] - 100000.0 ** (-2.0 * j / 64)) <= 1e-5 * 100000.0 ** (-2.0 * j / 64)
+    # equal to the plain implementation's own restatement, element for element
+    for name in ("tiny_a", "tiny_b"):
+        cfg = tiny.CONFIGS[name]
+        rs = cfg["rope_scaling"]
+        mine = plain_inv_freq(cfg["head_dim"], cfg["rope_theta"]) if rs is None else \
+            llama3_inv_freq(cfg["head_dim"], cfg["rope_theta"], rs["factor"], rs["low_freq_factor"],
+                            rs["high_freq_factor"], rs["original_max_position_embeddings"])
+        assert np.array_equal(mine, plain.inv_freq(cfg))
+
+
+# --------------------------------------------------------------- the toy model
+def register_toy():
+    """A mixer with a fixed-size state per sequence: y_t = W * mean(x_0..x_t).
+    The state row of a sequence holds the running sum. Everything it needs
+    comes through the part interfaces and the step context."""
+    from foundry_b200.cache import StateRequest
+    from foundry_b200.config import (Architecture, LayerSpec, LlamaConfig, ModelSpec, PartSpec,
+                                     ScheduleEntry, register_architecture)
+    from foundry_b200.parts import Linear, Part, register_mixer
+
+    class RunningMean(Part):
+        def __init__(self, hidden_size, *, dtype, device):
+            self.h, self.dtype = hidden_size, dtype
+            self.proj = Linear(hidden_size, [("proj", hidden_size)], dtype=dtype, device=device)
+
+        def expected_tensors(self, prefix):
+            return self.proj.expected_tensors(prefix)
+
+        def load(self, prefix, fetch):
+            self.proj.load(prefix, fetch)
+
+        def cache_request(self):
+            return StateRequest((self.h,), torch.float32)
+
+        def forward(self, ctx, x, state):
+            rows = ctx.slots.long()
+            xf = x.float()
+            if ctx.is_decode:  # one token per sequence: a vector update per row
+                total = state.rows.index_select(0, rows) + xf
+                state.rows.index_copy_(0, rows, total)
+                mean = total / (ctx.positions.float() + 1.0).unsqueeze(1)
+            else:
+                parts = []
+                for i, slot in enumerate(ctx.slots_host):
+                    a, b = ctx.cu_tokens_host[i], ctx.cu_tokens_host[i + 1]
+                    total = state.rows[slot] + torch.cumsum(xf[a:b], 0)
+                    state.rows[slot] = total[-1]
+                    parts.append(total)
+                mean = torch.cat(parts) / (ctx.positions.float() + 1.0).unsqueeze(1)
+            return self.proj.forward(mean.to(self.dtype))
+
+    register_mixer("toy_running_mean", RunningMean, replace=True)
+
+    def build_spec(config):
+        from foundry_b200.models.llama import HF_NAMES, build_llama_spec
+        llama = build_llama_spec(config)
+        attn_layer = llama.layers[0]
+        toy_layer = LayerSpec(prefix="model.layers.1", block=attn_layer.block,
+                              mixer=PartSpec("toy_running_mean", {"hidden_size": config.hidden_size}),
+                              feed_forward=attn_layer.feed_forward, mixer_norm=attn_layer.mixer_norm,
+                              feed_forward_norm=attn_layer.feed_forward_norm,
+                              names={**HF_NAMES, "mixer": "toy"})
+        spec = ModelSpec(
+            architecture="ToyForCausalLM", hidden_size=llama.hidden_size,
+            vocab_size=llama.vocab_size, max_positions=llama.max_positions,
+            layers=(attn_layer, toy_layer),
+            # layer 0 runs twice with the same weights; its second run reads the keys
+            # and values its first run wrote
+            schedule=(ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 0, writes_cache=False)),
+            final_norm=llama.final_norm, embedding_name=llama.embedding_name,
+            final_norm_prefix=llama.final_norm_prefix, output_head_name=llama.output_head_name)
+        spec.validate()
+        return spec
+
+    class ToyConfig(LlamaConfig):
+        pass
+
+    def parse(doc):
+        return LlamaConfig.parse({**doc, "architectures": ["ToyForCausalLM"]})
+
+    register_architecture(Architecture("ToyForCausalLM", "llama", parse, build_spec), replace=True)
+
+
+def toy_plain_forward(cfg, w, tokens):
+    """The toy model, whole sequence, float64."""
+    ids = torch.as_tensor(tokens)
+    x = w["model.embed_tokens.weight"][ids]
+    eps = cfg["rms_norm_eps"]
+    positions = list(range(len(tokens)))
+    S, A = len(tokens), cfg["num_attention_heads"]
+    K, D = cfg["num_key_value_heads"], cfg["head_dim"]
+    cos, sin = plain.rotary_tables(cfg, positions)
+    p0 = "model.layers.0"
+
+    def attn(xin, kv=None):
+        n = plain.rms_norm(xin, w[f"{p0}.input_layernorm.weight"], eps)
+        q = plain.apply_rotary((n @ w[f"{p0}.self_attn.q_proj.weight"].T).reshape(S, A, D), cos, sin)
+        if kv is None:
+            k = plain.apply_rotary((n @ w[f"{p0}.self_attn.k_proj.weight"].T).reshape(S, K, D), cos, sin)
+            v = (n @ w[f"{p0}.self_attn.v_proj.weight"].T).reshape(S, K, D)
+        else:
+            k, v = kv
+        out = torch.empty(S, A, D, dtype=torch.float64)
+        mask = torch.tril(torch.ones(S, S, dtype=torch.bool))
+        for a in range(A):
+            s = (q[:, a] @ k[:, a // (A // K)].T) / math.sqrt(D)
+            s = s.masked_fill(~mask, float("-inf"))
+            out[:, a] = torch.softmax(s, -1) @ v[:, a // (A // K)]
+        return out.reshape(S, A * D) @ w[f"{p0}.self_attn.o_proj.weight"].T, (k, v)
+
+    def layer0(xin, kv=None):
+        a, kv = attn(xin, kv)
+        h = xin + a
+        return h + plain.mlp(plain.rms_norm(h, w[f"{p0}.post_attention_layernorm.weight"], eps), w,
+                             f"{p0}.mlp"), kv
+
+    x, kv = layer0(x)
+    p1 = "model.layers.1"
+    n = plain.rms_norm(x, w[f"{p1}.input_layernorm.weight"], eps)
+    mean = torch.cumsum(n, 0) / torch.arange(1, S + 1, dtype=torch.float64).unsqueeze(1)
+    h = x + mean @ w[f"{p1}.toy.proj.weight"].T
+    x = h + plain.mlp(plain.rms_norm(h, w[f"{p1}.post_attention_layernorm.weight"], eps), w, f"{p1}.mlp")
+    x, _ = layer0(x, kv)
+    x = plain.rms_norm(x, w["model.norm.weight"], eps)
+    head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
+    return x @ head.T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    import foundry_b200 as fb
+    from foundry_b200.config import LlamaConfig, unregister_architecture
+    from foundry_b200.engine import SequenceStep
+    from foundry_b200.parts import MIXERS
+    register_toy()
+    try:
+        cfg = {**tiny.CONFIGS["tiny_b"], "architectures": ["ToyForCausalLM"], "num_hidden_layers": 2}
+        folder = fb.write_model_folder(str(tmp_path / "toy"), LlamaConfig.parse(cfg), 5, std=0.08)
+        assert json.load(open(os.path.join(folder, "config.json")))["architectures"] == ["ToyForCausalLM"]
+        pcfg, w = plain.read_model(folder)
+        assert "model.layers.1.toy.proj.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+        engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=1024, max_slots=4)
+        assert len(engine.cache.groups) == 1 and list(engine.cache.state) == [1]
+        reqs = [tiny.random_tokens(300 + i, n, cfg["vocab_size"]) for i, n in enumerate((40, 5, 90, 67))]
+        want = [toy_plain_forward(pcfg, w, r).numpy() for r in reqs]
+        # whole
+        for r, e in zip(reqs, want):
+            s = engine.open_sequence()
+            got = engine.step([SequenceStep(s, r, list(range(len(r))))]).cpu().numpy()
+            engine.close_sequence(s)
+            tiny.assert_logits_close(got, e, dtype, "toy whole")
+        # batches of two (so slots and their state rows are used again), prompt then tokens
+        for pair in ((0, 1), (2, 3), (1, 3)):
+            slots = {i: engine.open_sequence() for i in pair}
+            done = {i: max(1, len(reqs[i]) - 6) for i in pair}
+            rows = {i: [] for i in pair}
+            out = engine.step([SequenceStep(slots[i], reqs[i][:done[i]], list(range(done[i])))
+                               for i in pair]).cpu().numpy()
+            at = 0
+            for i in pair:
+                rows[i].append(out[at:at + done[i]])
+                at += done[i]
+            for _ in range(6):
+                live = [i for i in pair if done[i] < len(reqs[i])]
+                out = engine.step([SequenceStep(slots[i], [reqs[i][done[i]]], [0]) for i in live]).cpu().numpy()
+                for j, i in enumerate(live):
+                    rows[i].append(out[j:j + 1])
+                    done[i] += 1
+            for i in pair:
+                engine.close_sequence(slots[i])
+                tiny.assert_logits_close(np.concatenate(rows[i]), want[i], dtype, f"toy batched {pair}")
+    finally:
+        unregister_architecture("ToyForCausalLM")
+        MIXERS.unregister("toy_running_mean")
