@@ -39,10 +39,13 @@ FB_API int fb_embed_gather(const void* table, int table_dtype, const int* ids, f
 
 // ------------------------------------------------- residual add + RMS norm
 // resid[t,:] += delta[t,:] (if delta), then out[t,:] = resid * r * w.
-// One block per row; the row is re-read from `resid`, which the same thread
-// wrote, so no synchronisation is needed between the two passes.
+// `delta` may be `planes` float32 partial results of a split-K product
+// ([planes, T, H], `plane_stride` elements apart); they are summed in plane
+// order, then added. One block per row; the row is re-read from `resid`, which
+// the same thread wrote, so no synchronisation is needed between the passes.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   int planes, long long plane_stride,
                                    const float* __restrict__ weight, TO* __restrict__ out, int H,
                                    float eps, float inv_h) {
   __shared__ float scratch[32];
@@ -52,7 +55,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   if (delta != nullptr) {
     const TD* d = delta + row;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      const float v = x[i] + fb_to_float<TD>(d[i]);
+      float add = fb_to_float<TD>(d[i]);
+      for (int s = 1; s < planes; ++s) add += fb_to_float<TD>(d[(size_t)s * plane_stride + i]);
+      const float v = x[i] + add;
       x[i] = v;
       ss += v * v;
     }
@@ -71,37 +76,42 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
   }
 }
 
-FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* weight,
-                          float eps, void* out, int out_dtype, int T, int H,
-                          cudaStream_t stream) {
+FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int planes,
+                          long long plane_stride, const float* weight, float eps, void* out,
+                          int out_dtype, int T, int H, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && H > 0, "add_rmsnorm: bad sizes T=%d H=%d", T, H);
   FB_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+  FB_REQUIRE(planes >= 1 && (planes == 1 || delta_dtype == FB_F32),
+             "add_rmsnorm: split planes are float32");
   if (T == 0) return 0;
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const float inv_h = 1.0f / (float)H;
   FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (
       add_rmsnorm_kernel<TD, TO><<<T, threads, 0, stream>>>(
-          resid, (const TD*)delta, weight, (TO*)out, H, eps, inv_h))));
+          resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))));
   return fb_check_launch("add_rmsnorm");
 }
 
 // ------------------------------------------------------------- SiLU(g) * u
-// gate_up is [T, 2I]: columns [0, I) hold the gate, [I, 2I) the up projection.
+// gate_up is [T, 2I]. Plain layout: columns [0, I) hold the gate, [I, 2I) the
+// up projection. Interleaved layout: column 2i holds gate i, column 2i+1 up i
+// (the layout the fused product epilogue uses).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I,
-                                size_t total) {
+                                size_t total, int interleaved) {
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = fb_to_float<T>(gate_up[t * 2 * I + i]);
-    const float u = fb_to_float<T>(gate_up[t * 2 * I + I + i]);
+    const T* row = gate_up + t * 2 * I;
+    const float g = fb_to_float<T>(interleaved ? row[2 * i] : row[i]);
+    const float u = fb_to_float<T>(interleaved ? row[2 * i + 1] : row[I + i]);
     const float a = g / (1.0f + expf(-g));
     out[idx] = fb_from_float<T>(a * u);
   }
 }
 
-FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I,
+FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, int interleaved,
                        cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && I > 0, "silu_mul: bad sizes T=%d I=%d", T, I);
   const size_t total = (size_t)T * I;
@@ -110,7 +120,7 @@ FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I,
   const size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   FB_DISPATCH_DTYPE(dtype, E, (silu_mul_kernel<E><<<blocks, threads, 0, stream>>>(
-                                  (const E*)gate_up, (E*)out, I, total)));
+                                  (const E*)gate_up, (E*)out, I, total, interleaved)));
   return fb_check_launch("silu_mul");
 }
 

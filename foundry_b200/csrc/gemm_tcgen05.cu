@@ -154,6 +154,7 @@ struct GemmParams {
   long long split_stride;        // elements between split-K planes
   void* out;
   int out_f32;                // 1: float32 output, 0: bfloat16
+  int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs
 };
 
 // Dynamic shared memory: [stages][A tile 128x64][B tile BNx64] bf16, 1024-aligned,
@@ -284,7 +285,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < CHUNK; ++e) v[e] = 0.f;
         }
-        if (i_global < p.rows_a) {
+        if (p.epilogue == 1) {
+          // Feature rows come in (gate, up) pairs: 2f holds gate f, 2f+1 up f.
+          // out[token, f] = gate / (1 + exp(-gate)) * up, in 32-bit, stored bf16.
+          const long long j0 = (long long)tile_b * BN + c;
+          if (p.stride_b == 1) {
+            // features run along j: pairs sit in this thread's registers
+            if (i_global < p.rows_a) {
+#pragma unroll
+              for (int e = 0; e < CHUNK; e += 2) {
+                if (j0 + e + 1 < p.rows_b) {
+                  const float gate = v[e];
+                  out_h[i_global * p.stride_a + ((j0 + e) >> 1)] =
+                      __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * v[e + 1]);
+                }
+              }
+            }
+          } else {
+            // features run along i (the lanes): the partner row is the next lane
+#pragma unroll
+            for (int e = 0; e < CHUNK; ++e) {
+              const float other = __shfl_xor_sync(0xffffffffu, v[e], 1);
+              if ((lane & 1) == 0 && i_global + 1 < p.rows_a && j0 + e < p.rows_b) {
+                const float gate = v[e];
+                out_h[(i_global >> 1) + (j0 + e) * p.stride_b] =
+                    __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * other);
+              }
+            }
+          }
+        } else if (i_global < p.rows_a) {
           const long long j0 = (long long)tile_b * BN + c;
           const long long base = i_global * p.stride_a + j0 * p.stride_b;
           if (p.stride_b == 1 && j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
@@ -426,9 +455,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 //   bn: the B-tile height (16, 32, 64, 128 or 256); splits: K ranges per tile
 // With splits > 1 the output must be float32 and holds `splits` partial planes
 // that the caller sums.
+// epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
+// pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
+// dimension must be 1 and then indexes pairs.
 FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, long long ldb,
                       int rows_b, int K, void* out, long long stride_a, long long stride_b,
-                      int out_f32, int bn, int splits, long long split_stride,
+                      int out_f32, int bn, int splits, long long split_stride, int epilogue,
                       cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, K);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
@@ -437,13 +469,17 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   FB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0,
              "gemm_tc: operands must start on 16-byte boundaries");
   FB_REQUIRE(splits >= 1 && (splits == 1 || out_f32), "gemm_tc: split-K needs a float32 output");
+  FB_REQUIRE(epilogue == 0 || (epilogue == 1 && splits == 1 && !out_f32 &&
+                               (stride_a == 1 || stride_b == 1)),
+             "gemm_tc: the SiLU-mul epilogue needs one split, a bf16 output and features on a "
+             "unit stride");
   const int total_kb = (K + BK - 1) / BK;
   FB_REQUIRE(splits <= total_kb, "gemm_tc: %d splits for %d K blocks", splits, total_kb);
   GemmParams p;
   p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
   p.kblocks_per_split = (total_kb + splits - 1) / splits;
   p.stride_a = stride_a; p.stride_b = stride_b; p.split_stride = split_stride;
-  p.out = out; p.out_f32 = out_f32;
+  p.out = out; p.out_f32 = out_f32; p.epilogue = epilogue;
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, rows_a, K, lda, BM);
   if (rc) return rc;

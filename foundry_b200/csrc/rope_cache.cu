@@ -10,16 +10,21 @@
 // The reference rounds cos and sin to 16 bits in a table; here they are
 // computed in 32-bit from the angle, in the kernel.
 //
-// Layout: `qkv` is [T, (A + 2*Kh) * D] with row stride `qkv_stride`: A query
-// heads, then Kh key heads, then Kh value heads. Queries are rotated in place.
+// Layout: the fused projection output is [T, (A + 2*Kh) * D]: A query heads,
+// then Kh key heads, then Kh value heads.
 // A cache page of one head is FB_PAGE rows of D elements; the page of position
 // p is page_table[seq, (p / FB_PAGE) % ring] (ring = pages per sequence for a
 // windowed group, else unbounded).
 #include "common.cuh"
 
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
-                                     const int* __restrict__ positions,
+// `src` is the fused projection output: T elements, or float32 when it is
+// `planes` partial results of a split-K product (summed here in plane order).
+// Rotated queries go to `q_out` (row stride q_stride), which may be `src`
+// itself when the types agree.
+template <typename TS, typename T>
+__global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_stride, int planes,
+                                     long long plane_stride, T* __restrict__ q_out,
+                                     long long q_stride, const int* __restrict__ positions,
                                      const int* __restrict__ seq_of_token,
                                      const int* __restrict__ page_table, int max_pages,
                                      const float* __restrict__ inv_freq, int rotary_dim,
@@ -30,9 +35,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
   const int seq = seq_of_token[t];
   if (seq < 0) return;  // padding token
   const int pos = positions[t];
-  T* row = qkv + (size_t)t * qkv_stride;
+  const TS* row = src + (size_t)t * src_stride;
+  T* qrow = q_out + (size_t)t * q_stride;
   const int half = rotary_dim >> 1;
   const float fpos = (float)pos;
+  auto load = [&](int idx) -> float {
+    float v = fb_to_float<TS>(row[idx]);
+    for (int s = 1; s < planes; ++s) v += fb_to_float<TS>(row[(size_t)s * plane_stride + idx]);
+    return v;
+  };
 
   long long cache_row = 0;
   if (write_cache) {
@@ -49,48 +60,74 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, long long qkv_stride,
     const float angle = fpos * inv_freq[i];
     float s, c;
     sincosf(angle, &s, &c);
-    T* x = row + (size_t)h * D;
-    const float x1 = fb_to_float<T>(x[i]), x2 = fb_to_float<T>(x[i + half]);
+    const float x1 = load(h * D + i), x2 = load(h * D + i + half);
     const float y1 = x1 * c - x2 * s;
     const float y2 = x2 * c + x1 * s;
     if (h < A) {
-      x[i] = fb_from_float<T>(y1);
-      x[i + half] = fb_from_float<T>(y2);
+      qrow[h * D + i] = fb_from_float<T>(y1);
+      qrow[h * D + i + half] = fb_from_float<T>(y2);
     } else {
       T* dst = k_cache + cache_row + (long long)(h - A) * head_stride;
       dst[i] = fb_from_float<T>(y1);
       dst[i + half] = fb_from_float<T>(y2);
     }
   }
-  if (!write_cache) return;
-  // key elements beyond the rotary part pass through unchanged
+  // elements beyond the rotary part pass through unchanged
   const int tail = D - rotary_dim;
+  if (tail > 0 && ((const void*)src != (const void*)q_out || planes > 1)) {
+    for (int idx = threadIdx.x; idx < A * tail; idx += blockDim.x) {
+      const int h = idx / tail, i = rotary_dim + (idx - h * tail);
+      qrow[h * D + i] = fb_from_float<T>(load(h * D + i));
+    }
+  }
+  if (!write_cache) return;
   for (int idx = threadIdx.x; idx < Kh * tail; idx += blockDim.x) {
     const int h = idx / tail, i = rotary_dim + (idx - h * tail);
-    k_cache[cache_row + (long long)h * head_stride + i] = row[(size_t)(A + h) * D + i];
+    k_cache[cache_row + (long long)h * head_stride + i] = fb_from_float<T>(load((A + h) * D + i));
   }
   // values
   for (int idx = threadIdx.x; idx < Kh * D; idx += blockDim.x) {
     const int h = idx / D, i = idx - h * D;
-    v_cache[cache_row + (long long)h * head_stride + i] = row[(size_t)(A + Kh + h) * D + i];
+    v_cache[cache_row + (long long)h * head_stride + i] =
+        fb_from_float<T>(load((A + Kh + h) * D + i));
   }
 }
 
-FB_API int fb_rope_kv_write(void* qkv, int dtype, long long qkv_stride, const int* positions,
-                            const int* seq_of_token, const int* page_table, int max_pages,
-                            const float* inv_freq, int rotary_dim, void* k_cache, void* v_cache,
-                            long long page_stride, long long head_stride, int ring_pages, int T,
-                            int A, int Kh, int D, int write_cache, cudaStream_t stream) {
+// src_dtype / planes: see the kernel. dtype is the element type of q_out and the cache.
+FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride, int planes,
+                            long long plane_stride, void* q_out, int dtype, long long q_stride,
+                            const int* positions, const int* seq_of_token, const int* page_table,
+                            int max_pages, const float* inv_freq, int rotary_dim, void* k_cache,
+                            void* v_cache, long long page_stride, long long head_stride,
+                            int ring_pages, int T, int A, int Kh, int D, int write_cache,
+                            cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && A > 0 && Kh > 0 && D > 0, "rope_kv_write: bad sizes T=%d A=%d Kh=%d D=%d",
              T, A, Kh, D);
   FB_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 2 == 0,
              "rope_kv_write: rotary_dim %d must be even and at most head_dim %d", rotary_dim, D);
-  FB_REQUIRE(qkv_stride >= (long long)(A + 2 * Kh) * D, "rope_kv_write: row stride too small");
+  FB_REQUIRE(src_stride >= (long long)(A + 2 * Kh) * D && q_stride >= (long long)A * D,
+             "rope_kv_write: a row stride is too small");
+  FB_REQUIRE(planes >= 1 && (planes == 1 || src_dtype == FB_F32),
+             "rope_kv_write: split planes are float32");
+  FB_REQUIRE(src_dtype == dtype || src_dtype == FB_F32,
+             "rope_kv_write: the source is the output type or float32");
   FB_REQUIRE(!write_cache || (k_cache && v_cache && page_table && max_pages > 0),
              "rope_kv_write: cache pointers missing");
   if (T == 0) return 0;
-  FB_DISPATCH_DTYPE(dtype, E, (rope_kv_write_kernel<E><<<T, 256, 0, stream>>>(
-      (E*)qkv, qkv_stride, positions, seq_of_token, page_table, max_pages, inv_freq, rotary_dim,
-      (E*)k_cache, (E*)v_cache, page_stride, head_stride, ring_pages, A, Kh, D, write_cache)));
+#define FB_ROPE_LAUNCH(TS, TT)                                                                  \
+  rope_kv_write_kernel<TS, TT><<<T, 256, 0, stream>>>(                                          \
+      (const TS*)src, src_stride, planes, plane_stride, (TT*)q_out, q_stride, positions,        \
+      seq_of_token, page_table, max_pages, inv_freq, rotary_dim, (TT*)k_cache, (TT*)v_cache,    \
+      page_stride, head_stride, ring_pages, A, Kh, D, write_cache)
+  if (dtype == FB_F32) {
+    FB_ROPE_LAUNCH(float, float);
+  } else if (dtype == FB_BF16 && src_dtype == FB_BF16) {
+    FB_ROPE_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  } else if (dtype == FB_BF16) {
+    FB_ROPE_LAUNCH(float, __nv_bfloat16);
+  } else {
+    return fb_fail(1, "rope_kv_write: unknown element type code %d", dtype);
+  }
+#undef FB_ROPE_LAUNCH
   return fb_check_launch("rope_kv_write");
 }

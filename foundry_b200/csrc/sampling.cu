@@ -28,24 +28,27 @@ __device__ __forceinline__ float uniform24(unsigned long long stream, unsigned l
 }
 
 // temperature[r] == 0 selects greedily. streams/steps may be null when every
-// temperature is 0.
+// temperature is 0. Block (r, c) scans chunk c of row r and leaves its best
+// (score, index); with one chunk per row it writes the token itself.
 __global__ void __launch_bounds__(1024)
-select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int V,
+select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunk,
                      const float* __restrict__ temperature,
                      const long long* __restrict__ streams, const long long* __restrict__ steps,
+                     float* __restrict__ part_val, int* __restrict__ part_idx,
                      int* __restrict__ out) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
-  const int r = blockIdx.x;
+  const int r = blockIdx.x, c = blockIdx.y, chunks = gridDim.y;
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature ? temperature[r] : 0.f;
   const bool greedy = !(temp > 0.f);
   const float inv_t = greedy ? 1.f : 1.0f / temp;
   const unsigned long long stream = (!greedy && streams) ? (unsigned long long)streams[r] : 0ULL;
   const unsigned long long step = (!greedy && steps) ? (unsigned long long)steps[r] : 0ULL;
+  const int lo = c * chunk, hi = min(V, lo + chunk);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     float v = row[i];
     if (!greedy) {
       const float u = uniform24(stream, step, (unsigned long long)i);
@@ -79,18 +82,59 @@ select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int
         bv = ov; bi = oi;
       }
     }
-    if (lane == 0) out[r] = (bi == 0x7fffffff) ? 0 : bi;
+    if (lane == 0) {
+      if (chunks == 1) {
+        out[r] = (bi == 0x7fffffff) ? 0 : bi;
+      } else {
+        part_val[(size_t)r * chunks + c] = bv;
+        part_idx[(size_t)r * chunks + c] = bi;
+      }
+    }
   }
+}
+
+// One warp per row merges the chunk results (chunks <= 1024).
+__global__ void select_merge_kernel(const float* __restrict__ part_val,
+                                    const int* __restrict__ part_idx, int chunks,
+                                    int* __restrict__ out) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < chunks; c += 32) {
+    const float ov = part_val[(size_t)r * chunks + c];
+    const int oi = part_idx[(size_t)r * chunks + c];
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+      bv = ov; bi = oi;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) {
+      bv = ov; bi = oi;
+    }
+  }
+  if (lane == 0) out[r] = (bi == 0x7fffffff) ? 0 : bi;
 }
 }  // namespace
 
+// `chunks` blocks share each row; with chunks > 1 the two workspaces hold
+// n * chunks entries and a second small kernel merges them.
 FB_API int fb_select_tokens(const float* logits, long long row_stride, int n, int V,
                             const float* temperature, const long long* streams,
-                            const long long* steps, int* out, cudaStream_t stream) {
+                            const long long* steps, int* out, int chunks, float* part_val,
+                            int* part_idx, cudaStream_t stream) {
   FB_REQUIRE(n >= 0 && V > 0 && row_stride >= V, "select_tokens: bad sizes n=%d V=%d", n, V);
+  FB_REQUIRE(chunks >= 1 && chunks <= 1024 && (chunks == 1 || (part_val && part_idx)),
+             "select_tokens: bad chunk count %d or missing workspaces", chunks);
   if (n == 0) return 0;
-  const int threads = V >= 8192 ? 1024 : 256;
-  select_tokens_kernel<<<n, threads, 0, stream>>>(logits, row_stride, V, temperature, streams,
-                                                  steps, out);
-  return fb_check_launch("select_tokens");
+  const int chunk = (V + chunks - 1) / chunks;
+  const int threads = chunk >= 8192 ? 1024 : 256;
+  select_tokens_kernel<<<dim3(n, chunks), threads, 0, stream>>>(
+      logits, row_stride, V, chunk, temperature, streams, steps, part_val, part_idx, out);
+  int rc = fb_check_launch("select_tokens");
+  if (rc || chunks == 1) return rc;
+  select_merge_kernel<<<n, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+  return fb_check_launch("select_merge");
 }

@@ -99,9 +99,9 @@ class Model:
             seen.add(entry.layer)
             block = self.blocks[entry.layer]
             for part in (block.mixer, block.feed_forward):
-                for lin in vars(part).values():
-                    w = getattr(lin, "weight", None)
-                    if isinstance(w, torch.Tensor):
+                for held in vars(part).values():
+                    w = held if isinstance(held, torch.Tensor) else getattr(held, "weight", None)
+                    if isinstance(w, torch.Tensor) and w.dim() == 2:
                         total += w.numel() * w.element_size()
         total += self.output_head.numel() * self.output_head.element_size()
         return total
@@ -135,6 +135,8 @@ class Model:
         rows = torch.empty((n, spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.gather_rows(resid, ctx.want_rows, rows)
         rows_delta = None
+        if isinstance(delta, ops.Planes):
+            delta = delta.sum(self.dtype)
         if delta is not None:
             rows_delta = torch.empty((n, spec.hidden_size), dtype=delta.dtype, device=self.device)
             ops.gather_rows(delta, ctx.want_rows, rows_delta)

@@ -24,14 +24,14 @@ c_void_p, c_int, c_ll, c_float, c_ull = (ctypes.c_void_p, ctypes.c_int, ctypes.c
 
 _SIGNATURES = {
     "fb_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "fb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
-                       c_int, c_void_p],
-    "fb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "fb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_float, c_void_p, c_int,
+                       c_int, c_int, c_void_p],
+    "fb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "fb_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "fb_cast": [c_void_p, c_int, c_void_p, c_int, c_ll, c_void_p],
-    "fb_rope_kv_write": [c_void_p, c_int, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                         c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
-                         c_int, c_void_p],
+    "fb_rope_kv_write": [c_void_p, c_int, c_ll, c_int, c_ll, c_void_p, c_int, c_ll, c_void_p,
+                         c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll,
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int,
                      c_int, c_void_p],
     "fb_attention_simt": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
@@ -39,7 +39,7 @@ _SIGNATURES = {
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
-                   c_int, c_int, c_ll, c_void_p],
+                   c_int, c_int, c_ll, c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
@@ -48,7 +48,7 @@ _SIGNATURES = {
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_void_p, c_void_p, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                         c_void_p],
+                         c_int, c_void_p, c_void_p, c_void_p],
 }
 
 _FUNCS = {}
@@ -123,6 +123,27 @@ def _rows(t: torch.Tensor, name: str) -> int:
     return t.stride(0)
 
 
+class Planes:
+    """Partial results of a split-K product: float32 [splits, rows, cols] whose
+    sum over the first axis is the product. Consumers (the residual-add-norm
+    kernel, the rotary kernel) sum them in plane order while they read."""
+
+    def __init__(self, tensor: torch.Tensor):
+        self.tensor = tensor
+
+    @property
+    def shape(self):
+        return self.tensor.shape[1:]
+
+    @property
+    def count(self) -> int:
+        return self.tensor.shape[0]
+
+    def sum(self, dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty(self.shape, dtype=dtype, device=self.tensor.device)
+        return sum_planes(self.tensor, out)
+
+
 # ------------------------------------------------------------------ embedding
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t,:] = table[ids[t],:] as float32; `out` is [T, H] float32."""
@@ -136,12 +157,18 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> t
 
 
 # ------------------------------------------------------ residual + RMS norm
-def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
-                eps: float, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    """resid += delta (when given), in place, float32; out = rmsnorm(resid) * weight.
-    With `out=None` only the sum is made."""
+def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
+                out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """resid += delta (a tensor, split-K `Planes`, or None), in place, float32;
+    out = rmsnorm(resid) * weight. With `out=None` only the sum is made."""
     T, H = resid.shape
-    if delta is not None and delta.shape != resid.shape:
+    planes, plane_stride = 1, 0
+    if isinstance(delta, Planes):
+        planes, plane_stride = delta.count, T * H
+        delta = delta.tensor
+        if tuple(delta.shape[1:]) != (T, H) or not delta.is_contiguous():
+            raise KernelError(f"add_rmsnorm: planes are {tuple(delta.shape)}, resid {(T, H)}")
+    elif delta is not None and delta.shape != resid.shape:
         raise KernelError(f"add_rmsnorm: delta is {tuple(delta.shape)}, resid {tuple(resid.shape)}")
     if out is not None and out.shape != resid.shape:
         raise KernelError(f"add_rmsnorm: out is {tuple(out.shape)}, resid {tuple(resid.shape)}")
@@ -149,20 +176,21 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         raise KernelError(f"add_rmsnorm: weight is {tuple(weight.shape)}, expected {(H,)}")
     _call("fb_add_rmsnorm", _dev(resid, "resid", torch.float32),
           0 if delta is None else _dev(delta, "delta"),
-          F32 if delta is None else code_of(delta.dtype),
+          F32 if delta is None else code_of(delta.dtype), planes, plane_stride,
           _dev(weight, "weight", torch.float32), float(eps),
           0 if out is None else _dev(out, "out"),
           F32 if out is None else code_of(out.dtype), T, H, _stream())
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t,i] = silu(gate_up[t,i]) * gate_up[t,I+i]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """out[t,i] = silu(gate) * up, with gate i / up i in columns i / I+i, or in
+    columns 2i / 2i+1 when `interleaved`."""
     T, two_i = gate_up.shape
     if two_i % 2 or out.shape != (T, two_i // 2) or out.dtype != gate_up.dtype:
         raise KernelError(f"silu_mul: gate_up {tuple(gate_up.shape)} / out {tuple(out.shape)}")
     _call("fb_silu_mul", _dev(gate_up, "gate_up"), _dev(out, "out"), code_of(out.dtype), T,
-          two_i // 2, _stream())
+          two_i // 2, 1 if interleaved else 0, _stream())
     return out
 
 
@@ -184,16 +212,34 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------ rope + cache
-def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor,
                   page_table: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                   num_heads: int, num_kv_heads: int, head_dim: int, ring_pages: int = 0,
-                  write_cache: bool = True) -> None:
-    """Rotate the query heads of `qkv` in place; rotate the key heads into the
-    cache pages and copy the value heads there. `k_cache`/`v_cache` are one
-    cache entry's views [pages, kv_heads, PAGE, head_dim]."""
-    T = qkv.shape[0]
-    stride = _rows(qkv, "qkv")
+                  write_cache: bool = True, q_out: Optional[torch.Tensor] = None,
+                  dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Rotate the query heads of the fused projection output; rotate the key
+    heads into the cache pages and copy the value heads there. `qkv` is a
+    tensor (queries are then rotated in place unless `q_out` is given) or
+    split-K `Planes`, which are summed on the way (`q_out` of `dtype` is made).
+    `k_cache`/`v_cache` are one cache entry's views [pages, kv_heads, PAGE,
+    head_dim]. Returns the [T, heads * head_dim] (possibly strided) queries."""
+    planes, plane_stride = 1, 0
+    if isinstance(qkv, Planes):
+        src = qkv.tensor
+        planes = qkv.count
+        T, width = qkv.shape
+        plane_stride, src_stride = T * width, width
+        dtype = dtype or (k_cache.dtype if k_cache is not None else torch.bfloat16)
+        if q_out is None:
+            q_out = torch.empty((T, num_heads * head_dim), dtype=dtype, device=src.device)
+    else:
+        src = qkv
+        T = qkv.shape[0]
+        src_stride = _rows(qkv, "qkv")
+        dtype = qkv.dtype
+        if q_out is None:
+            q_out = qkv[:, :num_heads * head_dim]
     if positions.numel() != T or seq_of_token.numel() != T:
         raise KernelError("rope_kv_write: positions / seq_of_token do not cover the tokens")
     if inv_freq.numel() * 2 != rotary_dim:
@@ -201,14 +247,17 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
     page_stride = head_stride = 0
     kp = vp = 0
     if write_cache:
-        _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, qkv.dtype)
+        _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, dtype)
         page_stride, head_stride = k_cache.stride(0), k_cache.stride(1)
         kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
-    _call("fb_rope_kv_write", _dev(qkv, "qkv", contiguous=False), code_of(qkv.dtype), stride,
-          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+    _call("fb_rope_kv_write", _dev(src, "qkv", contiguous=False), code_of(src.dtype), src_stride,
+          planes, plane_stride, _dev(q_out, "q_out", dtype, contiguous=False), code_of(dtype),
+          _rows(q_out, "q_out"), _dev(positions, "positions", torch.int32),
+          _dev(seq_of_token, "seq_of_token", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1],
           _dev(inv_freq, "inv_freq", torch.float32), rotary_dim, kp, vp, page_stride, head_stride,
           ring_pages, T, num_heads, num_kv_heads, head_dim, 1 if write_cache else 0, _stream())
+    return q_out
 
 
 def _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, dtype) -> None:
@@ -242,7 +291,7 @@ SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
-            bn: int, splits: int = 1, split_stride: int = 0) -> None:
+            bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0) -> None:
     """Tensor-core product D[i,j] = sum_k a[i,k] b[j,k] written to
     out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu."""
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
@@ -252,7 +301,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
     _call("fb_gemm_tc", _dev(a, "a", contiguous=False), _rows(a, "a"), a.shape[0],
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
-          1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, _stream())
+          1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue, _stream())
 
 
 def gemm_tc_status():
@@ -281,37 +330,58 @@ def _tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and w.stride(1) == 1 and out.stride(1) == 1)
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def _swapped_plan(M: int, N: int, K: int):
+    """Tile width and split count for up to 128 token rows."""
+    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = (N + 127) // 128
+    kblocks = (K + 63) // 64
+    splits = max(1, min(kblocks // 4, (SM_COUNT + tiles // 2) // tiles))
+    per = (kblocks + splits - 1) // splits
+    return bn, (kblocks + per - 1) // per  # no empty split
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+              out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
     """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
 
     More than 128 rows: token rows fill the 128-row operand, weights the other
     (256 wide). Up to 128 rows: swapped, the weights fill the 128-row operand and
     stream through once, the tokens are the narrow operand; K is split over
-    CTAs until the grid covers the SMs, each split writing a float32 plane that
-    one more kernel sums in a fixed order. Shapes TMA cannot address (K or a
-    row stride not a multiple of 8 elements) take the CUDA-core kernel.
+    CTAs until the grid covers the SMs, each split writing a float32 plane.
+    With `allow_planes` the planes are returned as `Planes` for a consumer that
+    sums them as it reads; otherwise one more kernel sums them in a fixed order.
+    Shapes TMA cannot address (K or a row stride not a multiple of 8 elements)
+    take the CUDA-core kernel.
     """
     M, K = x.shape
     N = w.shape[0]
+    if out is None:
+        out_dtype = out_dtype or x.dtype
     if M == 0:
-        return out
-    if not _tc_usable(x, w, out):
+        return out if out is not None else torch.empty((0, N), dtype=out_dtype, device=x.device)
+    probe = out if out is not None else x
+    if not _tc_usable(x, w, probe):
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_simt(x, w, out)
     if M > 128:
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         bn = 256 if N >= 256 else (128 if N > 64 else 64)
         gemm_tc(x, w, out, out.stride(0), 1, bn)
         return out
-    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-    tiles = (N + 127) // 128
-    kblocks = (K + 63) // 64
-    splits = max(1, min(kblocks // 4, (SM_COUNT + tiles // 2) // tiles))
+    bn, splits = _swapped_plan(M, N, K)
     if splits == 1:
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         gemm_tc(w, x, out, 1, out.stride(0), bn)
         return out
-    per = (kblocks + splits - 1) // splits
-    splits = (kblocks + per - 1) // per  # no empty split
     planes = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
     gemm_tc(w, x, planes, 1, N, bn, splits, M * N)
+    if allow_planes and out is None:
+        return Planes(planes)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     if out.is_contiguous():
         return sum_planes(planes, out)
     tmp = torch.empty((M, N), dtype=out.dtype, device=x.device)
@@ -320,7 +390,29 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
     return out
 
 
-# ------------------------------------------------------------------ attention
+def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, I] = silu(x @ gate^T) * (x @ up^T) with `w_pairs` [2I, K] holding
+    gate i in row 2i and up i in row 2i+1; the activation runs in the product's
+    epilogue, so the [M, 2I] intermediate never reaches memory."""
+    M, K = x.shape
+    two_i = w_pairs.shape[0]
+    if out.shape != (M, two_i // 2) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise KernelError("gemm_bf16_silu_mul: out must be [M, I] bfloat16 with contiguous rows")
+    if M == 0:
+        return out
+    if not _tc_usable(x, w_pairs, out):
+        tmp = torch.empty((M, two_i), dtype=torch.bfloat16, device=x.device)
+        gemm_simt(x, w_pairs, tmp)
+        return silu_mul(tmp, out, interleaved=True)
+    if M > 128:
+        bn = 256 if two_i >= 256 else (128 if two_i > 64 else 64)
+        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1)
+    else:
+        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+        gemm_tc(w_pairs, x, out, 1, out.stride(0), bn, epilogue=1)
+    return out
+
+
 FAST_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention kernels
 
 
@@ -410,14 +502,23 @@ def select_tokens(logits: torch.Tensor, out: torch.Tensor, temperature: Optional
                   steps: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Greedy where temperature is 0 (or None), Gumbel-max sampling elsewhere.
     `streams[r]` is the row's random stream (`sampling.stream_key(seed, key)`),
-    `steps[r]` how many tokens its sequence has generated."""
+    `steps[r]` how many tokens its sequence has generated. Large vocabularies
+    are scanned by several blocks per row and merged by a second small kernel."""
     n, V = logits.shape
     if out.numel() != n:
         raise KernelError("select_tokens: out does not hold one token per row")
+    chunks = 1 if V < 16384 else min(64, (V + 2047) // 2048)
+    part_val = part_idx = None
+    if chunks > 1:
+        part_val = torch.empty(n * chunks, dtype=torch.float32, device=logits.device)
+        part_idx = torch.empty(n * chunks, dtype=torch.int32, device=logits.device)
+        _COUNT[0] += 1  # the merge kernel
     _call("fb_select_tokens", _dev(logits, "logits", torch.float32, contiguous=False),
           _rows(logits, "logits"), n, V,
           0 if temperature is None else _dev(temperature, "temperature", torch.float32),
           0 if streams is None else _dev(streams, "streams", torch.int64),
           0 if steps is None else _dev(steps, "steps", torch.int64),
-          _dev(out, "out", torch.int32), _stream())
+          _dev(out, "out", torch.int32), chunks,
+          0 if part_val is None else part_val.data_ptr(),
+          0 if part_idx is None else part_idx.data_ptr(), _stream())
     return out

@@ -65,15 +65,16 @@ class GQAAttention(Part):
         return KVRequest(self.num_kv_heads, self.head_dim, self.window)
 
     # ------------------------------------------------------------------- run
-    def forward(self, ctx, x: torch.Tensor, cache: KVView) -> torch.Tensor:
-        qkv = self.qkv.forward(x)
+    def forward(self, ctx, x: torch.Tensor, cache: KVView):
+        qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
         table = ctx.page_table(cache.group)
-        ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
-                          self.rotary_dim, cache.k, cache.v, self.num_heads, self.num_kv_heads,
-                          self.head_dim, ring_pages=cache.group.ring_pages,
-                          write_cache=cache.writes)
+        q = ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
+                              self.rotary_dim, cache.k, cache.v, self.num_heads,
+                              self.num_kv_heads, self.head_dim,
+                              ring_pages=cache.group.ring_pages, write_cache=cache.writes,
+                              dtype=x.dtype)
         attn = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
-        ops.attention(ctx, qkv[:, :self.q_size], attn, table, cache.k, cache.v, self.num_heads,
-                      self.num_kv_heads, self.head_dim, self.scale, window=cache.group.window,
+        ops.attention(ctx, q, attn, table, cache.k, cache.v, self.num_heads, self.num_kv_heads,
+                      self.head_dim, self.scale, window=cache.group.window,
                       ring_pages=cache.group.ring_pages)
-        return self.o.forward(attn)
+        return self.o.forward(attn, allow_planes=True)

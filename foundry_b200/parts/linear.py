@@ -17,19 +17,21 @@ from .base import Fetch, Part
 
 
 def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-              out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+              out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
     """out[M,N] = x[M,K] @ w[N,K]^T, accumulated in 32-bit, by the kernel that
-    fits the element type and the shape."""
+    fits the element type and the shape. With `allow_planes` a split-K product
+    may come back as `ops.Planes` (float32 partial results) for a consumer that
+    sums them while it reads."""
     M, N = x.shape[0], w.shape[0]
-    if out is None:
-        out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
     if x.dtype != w.dtype:
         raise ops.KernelError(
             f"projection input is {x.dtype} but the weight is {w.dtype}; a weight file stored "
             f"in 32 bits needs --dtype float32")
     if x.dtype == torch.float32:
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
         return ops.gemm_simt(x, w, out)
-    return ops.gemm_bf16(x, w, out)
+    return ops.gemm_bf16(x, w, out, out_dtype, allow_planes)
 
 
 class Linear(Part):
@@ -55,5 +57,5 @@ class Linear(Part):
         self.weight = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, 0).contiguous()
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        return matmul_nt(x, self.weight, out, out_dtype)
+                out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
+        return matmul_nt(x, self.weight, out, out_dtype, allow_planes)

@@ -11,7 +11,7 @@ import torch
 from ..kernels import ops
 from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part, register_feed_forward
-from .linear import Linear
+from .linear import Linear, matmul_nt
 
 
 @register_feed_forward("swiglu")
@@ -20,21 +20,29 @@ class SwiGLU(Part):
                  device: torch.device):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.dtype, self.device = dtype, device
-        self.gate_up = Linear(hidden_size, [("gate_proj", intermediate_size),
-                                            ("up_proj", intermediate_size)],
-                              dtype=dtype, device=device)
+        self.gate_up: torch.Tensor = None  # [2I, H]: row 2i is gate i, row 2i+1 is up i
         self.down = Linear(intermediate_size, [("down_proj", hidden_size)], dtype=dtype,
                            device=device)
 
     def expected_tensors(self, prefix: str) -> Dict[str, ExpectedTensor]:
-        return {**self.gate_up.expected_tensors(prefix), **self.down.expected_tensors(prefix)}
+        shape = (self.intermediate_size, self.hidden_size)
+        return {f"{prefix}.gate_proj.weight": ExpectedTensor(shape),
+                f"{prefix}.up_proj.weight": ExpectedTensor(shape),
+                **self.down.expected_tensors(prefix)}
 
     def load(self, prefix: str, fetch: Fetch) -> None:
-        self.gate_up.load(prefix, fetch)
+        gate, up = fetch(f"{prefix}.gate_proj.weight"), fetch(f"{prefix}.up_proj.weight")
+        if gate.dtype != up.dtype:
+            raise ops.KernelError(f"{prefix}: gate and up projections are stored in different dtypes")
+        # rows interleaved so that a product tile holds matching gate / up pairs
+        self.gate_up = torch.stack([gate, up], 1).reshape(2 * self.intermediate_size,
+                                                          self.hidden_size).contiguous()
         self.down.load(prefix, fetch)
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        gate_up = self.gate_up.forward(x)
+    def forward(self, ctx, x: torch.Tensor):
         hidden = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gate_up, hidden)
-        return self.down.forward(hidden)
+        if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16:
+            ops.gemm_bf16_silu_mul(x, self.gate_up, hidden)  # activation in the epilogue
+        else:
+            ops.silu_mul(matmul_nt(x, self.gate_up), hidden, interleaved=True)
+        return self.down.forward(hidden, allow_planes=True)

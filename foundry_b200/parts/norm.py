@@ -30,9 +30,9 @@ class RMSNorm(Part):
     def load(self, prefix: str, fetch: Fetch) -> None:
         self.weight = fetch(f"{prefix}.weight").to(torch.float32).contiguous()
 
-    def add_norm(self, resid: torch.Tensor, delta: Optional[torch.Tensor],
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """resid += delta (when given); returns norm(resid) in the activation dtype."""
+    def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """resid += delta (a tensor, split-K `ops.Planes`, or None); returns
+        norm(resid) in the activation dtype."""
         if out is None:
             out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)

@@ -315,3 +315,145 @@ def test_attention_refuses_sizes_it_does_not_build(ops):
         bad, _ = make_paged_case([1], [10], 2, 2, 24, torch.bfloat16)
         ops.attention_simt(bad["q"], torch.zeros_like(bad["q"]), bad["positions"], bad["seq_of"],
                            bad["table"], bad["k"], bad["v"], 2, 2, 24, 1.0)
+
+
+# ---------------------------------------------------- fused consumers of planes
+def test_add_rmsnorm_sums_split_planes(ops):
+    T, H, S = 5, 96, 3
+    planes = rnd(S, T, H)
+    resid, w = rnd(T, H, seed=1), 1.0 + 0.1 * rnd(H, seed=2)
+    r0 = resid.clone()
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(resid, ops.Planes(planes), w, 1e-5, out)
+    h = r0.double() + planes.double().sum(0)
+    close(resid, h, 1e-5, 1e-6)
+    close(out, h / torch.sqrt((h * h).mean(-1, keepdim=True) + 1e-5) * w.double(), 2e-2, 8e-3)
+
+
+def test_silu_mul_interleaved(ops):
+    T, I = 5, 88
+    gu = rnd(T, 2 * I, dtype=torch.bfloat16, scale=2.0)
+    out = torch.empty(T, I, dtype=torch.bfloat16, device=DEV)
+    ops.silu_mul(gu, out, interleaved=True)
+    g, u = gu[:, 0::2].double(), gu[:, 1::2].double()
+    close(out, g / (1 + torch.exp(-g)) * u, 2e-2, 8e-3)
+
+
+@pytest.mark.parametrize("M", [1, 8, 33, 64, 100, 129, 300])
+def test_gemm_with_silu_mul_epilogue(ops, M):
+    K, I = 200, 152  # neither a multiple of the tile sizes
+    x = rnd(M, K, dtype=torch.bfloat16, scale=0.5)
+    gate, up = rnd(I, K, dtype=torch.bfloat16, scale=0.3, seed=1), rnd(I, K, dtype=torch.bfloat16, scale=0.3, seed=2)
+    pairs = torch.stack([gate, up], 1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16_silu_mul(x, pairs, out)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    close(out, g / (1 + torch.exp(-g)) * u, 3e-2, 1e-2)
+    assert ops.gemm_tc_status() == 0
+
+
+# ------------------------------------------------------------- rope + cache
+def plain_rope(x, pos, inv_freq, rotary_dim):
+    """x [heads, D] float64; pairs (i, i + rotary_dim/2); angle as a 32-bit product."""
+    half = rotary_dim // 2
+    angle = (np.float32(pos) * inv_freq.astype(np.float32)).astype(np.float64)
+    c, s = torch.from_numpy(np.cos(angle)), torch.from_numpy(np.sin(angle))
+    y = x.clone()
+    y[:, :half] = x[:, :half] * c - x[:, half:rotary_dim] * s
+    y[:, half:rotary_dim] = x[:, half:rotary_dim] * c + x[:, :half] * s
+    return y
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("A,Kh,D,rot", [(4, 2, 16, 16), (6, 3, 32, 32), (3, 1, 48, 32), (8, 2, 128, 128)])
+@pytest.mark.parametrize("source", ["tensor", "planes"])
+def test_rope_kv_write(ops, dtype, A, Kh, D, rot, source):
+    """Positions far apart (a 32-bit angle matters at 100k), a padding token,
+    pages scattered; queries in place or from split planes; partial rotary width."""
+    positions = [0, 1, 63, 64, 100000, 7]
+    seqs = [0, 0, 1, 1, 2, -1]
+    T = len(positions)
+    width = (A + 2 * Kh) * D
+    n_pages = 1600
+    table = torch.zeros(3, 1563, dtype=torch.int32)
+    table[0, 0], table[1, 0], table[1, 1], table[2, 100000 // 64] = 5, 9, 2, 11
+    inv_freq = (10000.0 ** (-np.arange(0, rot, 2, dtype=np.float32) / rot)).astype(np.float32)
+    qkv = rnd(T, width, dtype=dtype)
+    k_cache = torch.zeros(n_pages, Kh, 64, D, dtype=dtype, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    ref = qkv.double().cpu()
+    args = (torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(seqs, dtype=torch.int32, device=DEV), table.to(DEV),
+            torch.from_numpy(inv_freq).to(DEV), rot, k_cache, v_cache, A, Kh, D)
+    if source == "tensor":
+        q = ops.rope_kv_write(qkv, *args)
+        assert q.data_ptr() == qkv.data_ptr()  # rotated in place
+    else:
+        parts = torch.stack([qkv.float() * 0.25, qkv.float() * 0.5, qkv.float() * 0.25])
+        q = ops.rope_kv_write(ops.Planes(parts.contiguous()), *args, dtype=dtype)
+    a, r = (1e-6, 1e-6) if dtype == torch.float32 else (2e-2, 8e-3)
+    for t in range(T - 1):
+        row = ref[t].view(A + 2 * Kh, D)
+        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot), a, r)
+        page = int(table[seqs[t], positions[t] // 64])
+        close(k_cache[page, :, positions[t] % 64], plain_rope(row[A:A + Kh], positions[t], inv_freq, rot), a, r)
+        close(v_cache[page, :, positions[t] % 64], row[A + Kh:], a, r)
+    # nothing else was written, and the padding token wrote nothing
+    written = {(int(table[seqs[t], positions[t] // 64]), positions[t] % 64) for t in range(T - 1)}
+    mask = torch.ones(n_pages, 64, dtype=torch.bool)
+    for p, rr in written:
+        mask[p, rr] = False
+    assert float(k_cache.float().abs().sum(dim=(1, 3)).cpu()[mask].max()) == 0.0
+
+
+# ------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("V", [384, 5001, 128256])
+def test_select_tokens_greedy_first_index_wins(ops, V):
+    logits = rnd(6, V)
+    logits[0, 17] = logits[0, V - 1] = 50.0      # equal maxima: the lower index
+    logits[1, :] = 1.0                            # all equal: index 0
+    logits[2, V - 1] = 60.0                       # the last element
+    logits[3, 5] = float("nan")                   # a NaN never wins
+    logits[4, :] = float("-inf")
+    logits[4, 123] = -1e30
+    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.select_tokens(logits, out, None)
+    want = [17, 0, V - 1, int(torch.argmax(torch.nan_to_num(logits[3], nan=-1e38))), 123,
+            int(torch.argmax(logits[5]))]
+    assert out.tolist() == want
+
+
+@pytest.mark.parametrize("V", [384, 128256])
+def test_select_tokens_sampling_matches_the_host_restatement(ops, V):
+    from foundry_b200.sampling import gumbel_scores, stream_key
+    n, seed = 4, 77
+    logits = rnd(n, V, scale=2.0)
+    keys, steps, temps = [3, 0, 9, 3], [0, 5, 2, 1], [0.8, 1.0, 0.0, 0.8]
+    out = torch.zeros(n, dtype=torch.int32, device=DEV)
+    ops.select_tokens(logits, out, torch.tensor(temps, device=DEV),
+                      torch.tensor([stream_key(seed, k) for k in keys], device=DEV),
+                      torch.tensor(steps, device=DEV))
+    host = logits.cpu().numpy()
+    for r in range(n):
+        if temps[r] == 0.0:
+            assert out[r] == int(np.argmax(host[r]))
+            continue
+        scores = gumbel_scores(host[r], temps[r], seed, keys[r], steps[r])
+        best = int(np.argmax(scores))
+        assert int(out[r]) == best or scores[best] - scores[int(out[r])] < 1e-4
+    assert out[0] != out[3] or V < 1000  # same key, another step: another draw
+
+
+def test_sampling_follows_the_distribution(ops):
+    """Over many steps the sampled frequencies approach softmax(logits / T)."""
+    from foundry_b200.sampling import stream_key
+    V, draws, T = 8, 4000, 0.7
+    base = torch.tensor([2.0, 1.0, 0.0, -1.0, 0.5, 1.5, -2.0, 0.0])
+    logits = base.repeat(draws, 1).to(DEV)
+    out = torch.zeros(draws, dtype=torch.int32, device=DEV)
+    ops.select_tokens(logits, out, torch.full((draws,), T, device=DEV),
+                      torch.full((draws,), stream_key(5, 0), dtype=torch.int64, device=DEV),
+                      torch.arange(draws, device=DEV))
+    freq = torch.bincount(out.long().cpu(), minlength=V).double() / draws
+    want = torch.softmax(base.double() / T, 0)
+    assert float((freq - want).abs().max()) < 0.03
