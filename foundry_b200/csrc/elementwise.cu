@@ -43,6 +43,88 @@ FB_API int fb_embed_gather(const void* table, int table_dtype, const int* ids, f
 // ([planes, T, H], `plane_stride` elements apart); they are summed in plane
 // order, then added. One block per row; the row is re-read from `resid`, which
 // the same thread wrote, so no synchronisation is needed between the passes.
+// Each thread owns up to ITEMS groups of four consecutive elements; all loads of
+// a group (the residual and every plane) are issued before any is used, so a
+// row costs one round trip to memory, one block reduction and one store.
+template <typename TD>
+__device__ __forceinline__ float4 load4(const TD* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename TO>
+__device__ __forceinline__ void store4(TO* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename TD, typename TO, int ITEMS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                       int planes, long long plane_stride,
+                                       const float* __restrict__ weight, TO* __restrict__ out,
+                                       int H, float eps, float inv_h) {
+  __shared__ float scratch[32];
+  const size_t row = (size_t)blockIdx.x * H;
+  float* x = resid + row;
+  float4 v[ITEMS];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int i = (threadIdx.x + it * blockDim.x) * 4;
+    v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < H) {
+      v[it] = load4<float>(x + i);
+      if (delta != nullptr) {
+        const TD* d = delta + row + i;
+        for (int s0 = 0; s0 < planes; s0 += 8) {
+          float4 part[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s)
+            part[s] = (s0 + s < planes) ? load4<TD>(d + (size_t)(s0 + s) * plane_stride)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 add = part[0];
+#pragma unroll
+          for (int s = 1; s < 8; ++s) {
+            add.x += part[s].x; add.y += part[s].y; add.z += part[s].z; add.w += part[s].w;
+          }
+          v[it].x += add.x; v[it].y += add.y; v[it].z += add.z; v[it].w += add.w;
+        }
+        store4<float>(x + i, v[it]);
+      }
+      ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
+    }
+  }
+  ss = fb_block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss * inv_h + eps);
+  if (out != nullptr) {
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int i = (threadIdx.x + it * blockDim.x) * 4;
+      if (i < H) {
+        const float4 w = load4<float>(weight + i);
+        store4<TO>(out + row + i, make_float4(v[it].x * r * w.x, v[it].y * r * w.y,
+                                              v[it].z * r * w.z, v[it].w * r * w.w));
+      }
+    }
+  }
+}
+
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    int planes, long long plane_stride,
@@ -84,8 +166,26 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
   FB_REQUIRE(planes >= 1 && (planes == 1 || delta_dtype == FB_F32),
              "add_rmsnorm: split planes are float32");
   if (T == 0) return 0;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const float inv_h = 1.0f / (float)H;
+  // vector path: rows of whole float4 groups on 16-byte boundaries, at most 4 groups a thread
+  const bool aligned = H % 4 == 0 && ((uintptr_t)resid % 16) == 0 && ((uintptr_t)weight % 16) == 0 &&
+                       ((uintptr_t)delta % 16) == 0 && ((uintptr_t)out % 16) == 0 &&
+                       plane_stride % 4 == 0;
+  if (aligned && H <= 4 * 4 * 1024) {
+    const int groups = H / 4;
+    const int threads = groups <= 128 ? 128 : groups <= 512 ? 256 : groups <= 1024 ? 512 : 1024;
+    const int items = (groups + threads - 1) / threads;
+#define FB_NORM_LAUNCH(N)                                                                     \
+    FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (                     \
+        add_rmsnorm_vec_kernel<TD, TO, N><<<T, threads, 0, stream>>>(                         \
+            resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))))
+    if (items <= 1) { FB_NORM_LAUNCH(1); }
+    else if (items == 2) { FB_NORM_LAUNCH(2); }
+    else { FB_NORM_LAUNCH(4); }
+#undef FB_NORM_LAUNCH
+    return fb_check_launch("add_rmsnorm");
+  }
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (
       add_rmsnorm_kernel<TD, TO><<<T, threads, 0, stream>>>(
           resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))));

@@ -292,12 +292,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (p.stride_b == 1) {
             // features run along j: pairs sit in this thread's registers
             if (i_global < p.rows_a) {
+              const long long base = i_global * p.stride_a + (j0 >> 1);
+              if (j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
 #pragma unroll
-              for (int e = 0; e < CHUNK; e += 2) {
-                if (j0 + e + 1 < p.rows_b) {
-                  const float gate = v[e];
-                  out_h[i_global * p.stride_a + ((j0 + e) >> 1)] =
-                      __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * v[e + 1]);
+                for (int e = 0; e < CHUNK; e += 16) {  // 8 results = 16 bytes per store
+                  float r8[8];
+#pragma unroll
+                  for (int q = 0; q < 8; ++q) {
+                    const float gate = v[e + 2 * q];
+                    r8[q] = gate / (1.0f + __expf(-gate)) * v[e + 2 * q + 1];
+                  }
+                  uint4 pk;
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(r8[0], r8[1]);
+                  __nv_bfloat162 h1 = __floats2bfloat162_rn(r8[2], r8[3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(r8[4], r8[5]);
+                  __nv_bfloat162 h3 = __floats2bfloat162_rn(r8[6], r8[7]);
+                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                  *reinterpret_cast<uint4*>(out_h + base + (e >> 1)) = pk;
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < CHUNK; e += 2) {
+                  if (j0 + e + 1 < p.rows_b) {
+                    const float gate = v[e];
+                    out_h[base + (e >> 1)] =
+                        __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * v[e + 1]);
+                  }
                 }
               }
             }
@@ -309,7 +332,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if ((lane & 1) == 0 && i_global + 1 < p.rows_a && j0 + e < p.rows_b) {
                 const float gate = v[e];
                 out_h[(i_global >> 1) + (j0 + e) * p.stride_b] =
-                    __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * other);
+                    __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * other);
               }
             }
           }

@@ -39,10 +39,21 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
   T* qrow = q_out + (size_t)t * q_stride;
   const int half = rotary_dim >> 1;
   const float fpos = (float)pos;
-  auto load = [&](int idx) -> float {
-    float v = fb_to_float<TS>(row[idx]);
-    for (int s = 1; s < planes; ++s) v += fb_to_float<TS>(row[(size_t)s * plane_stride + idx]);
-    return v;
+  // sums the planes of two elements; the loads of a group of planes are issued together
+  auto load2 = [&](int i0, int i1, float& a, float& b) {
+    a = 0.f;
+    b = 0.f;
+    for (int s0 = 0; s0 < planes; s0 += 4) {
+      float pa[4], pb[4];
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const bool ok = s0 + s < planes;
+        pa[s] = ok ? fb_to_float<TS>(row[(size_t)(s0 + s) * plane_stride + i0]) : 0.f;
+        pb[s] = ok ? fb_to_float<TS>(row[(size_t)(s0 + s) * plane_stride + i1]) : 0.f;
+      }
+#pragma unroll
+      for (int s = 0; s < 4; ++s) { a += pa[s]; b += pb[s]; }
+    }
   };
 
   long long cache_row = 0;
@@ -53,43 +64,58 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
     cache_row = (long long)page * page_stride + (long long)(pos % FB_PAGE) * D;
   }
 
-  // rotated pairs of the query and key heads
+  // One index space over everything a token needs: rotated pairs of the query
+  // and key heads, then pairs of value elements, then the elements beyond the
+  // rotary part. The blocks of a token (gridDim.y) stride through it.
   const int rot_heads = A + (write_cache ? Kh : 0);
-  for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    const float angle = fpos * inv_freq[i];
-    float s, c;
-    sincosf(angle, &s, &c);
-    const float x1 = load(h * D + i), x2 = load(h * D + i + half);
-    const float y1 = x1 * c - x2 * s;
-    const float y2 = x2 * c + x1 * s;
-    if (h < A) {
-      qrow[h * D + i] = fb_from_float<T>(y1);
-      qrow[h * D + i + half] = fb_from_float<T>(y2);
-    } else {
-      T* dst = k_cache + cache_row + (long long)(h - A) * head_stride;
-      dst[i] = fb_from_float<T>(y1);
-      dst[i + half] = fb_from_float<T>(y2);
-    }
-  }
-  // elements beyond the rotary part pass through unchanged
+  const int n_rot = rot_heads * half;
+  const int n_val = write_cache ? Kh * (D / 2) : 0;
   const int tail = D - rotary_dim;
-  if (tail > 0 && ((const void*)src != (const void*)q_out || planes > 1)) {
-    for (int idx = threadIdx.x; idx < A * tail; idx += blockDim.x) {
-      const int h = idx / tail, i = rotary_dim + (idx - h * tail);
-      qrow[h * D + i] = fb_from_float<T>(load(h * D + i));
+  const bool copy_q_tail = tail > 0 && ((const void*)src != (const void*)q_out || planes > 1);
+  const int n_tail = (tail / 2) * ((copy_q_tail ? A : 0) + (write_cache ? Kh : 0));
+  const int total = n_rot + n_val + n_tail;
+  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < total;
+       idx += gridDim.y * blockDim.x) {
+    if (idx < n_rot) {
+      const int h = idx / half, i = idx - h * half;
+      const float angle = fpos * inv_freq[i];
+      float s, c, x1, x2;
+      sincosf(angle, &s, &c);
+      load2(h * D + i, h * D + i + half, x1, x2);
+      const float y1 = x1 * c - x2 * s;
+      const float y2 = x2 * c + x1 * s;
+      if (h < A) {
+        qrow[h * D + i] = fb_from_float<T>(y1);
+        qrow[h * D + i + half] = fb_from_float<T>(y2);
+      } else {
+        T* dst = k_cache + cache_row + (long long)(h - A) * head_stride;
+        dst[i] = fb_from_float<T>(y1);
+        dst[i + half] = fb_from_float<T>(y2);
+      }
+    } else if (idx < n_rot + n_val) {
+      const int j = idx - n_rot;
+      const int h = j / (D / 2), i = 2 * (j - h * (D / 2));
+      float a, b;
+      load2((A + Kh + h) * D + i, (A + Kh + h) * D + i + 1, a, b);
+      T* dst = v_cache + cache_row + (long long)h * head_stride + i;
+      dst[0] = fb_from_float<T>(a);
+      dst[1] = fb_from_float<T>(b);
+    } else {
+      const int j = idx - n_rot - n_val;
+      int h = j / (tail / 2);
+      const int i = rotary_dim + 2 * (j - h * (tail / 2));
+      if (!copy_q_tail) h += A;  // only key heads have tails to move
+      float a, b;
+      load2(h * D + i, h * D + i + 1, a, b);
+      if (h < A) {
+        qrow[h * D + i] = fb_from_float<T>(a);
+        qrow[h * D + i + 1] = fb_from_float<T>(b);
+      } else {
+        T* dst = k_cache + cache_row + (long long)(h - A) * head_stride + i;
+        dst[0] = fb_from_float<T>(a);
+        dst[1] = fb_from_float<T>(b);
+      }
     }
-  }
-  if (!write_cache) return;
-  for (int idx = threadIdx.x; idx < Kh * tail; idx += blockDim.x) {
-    const int h = idx / tail, i = rotary_dim + (idx - h * tail);
-    k_cache[cache_row + (long long)h * head_stride + i] = fb_from_float<T>(load((A + h) * D + i));
-  }
-  // values
-  for (int idx = threadIdx.x; idx < Kh * D; idx += blockDim.x) {
-    const int h = idx / D, i = idx - h * D;
-    v_cache[cache_row + (long long)h * head_stride + i] =
-        fb_from_float<T>(load((A + Kh + h) * D + i));
   }
 }
 
@@ -114,8 +140,14 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   FB_REQUIRE(!write_cache || (k_cache && v_cache && page_table && max_pages > 0),
              "rope_kv_write: cache pointers missing");
   if (T == 0) return 0;
+  FB_REQUIRE(D % 2 == 0, "rope_kv_write: head_dim %d must be even", D);
+  // few tokens: several blocks per token so that the step's latency is one round trip
+  const int work = (A + 2 * Kh) * D / 2;
+  int per_token = T >= 256 ? 1 : (work + 255) / 256;
+  if (per_token > 16) per_token = 16;
+  dim3 grid(T, per_token);
 #define FB_ROPE_LAUNCH(TS, TT)                                                                  \
-  rope_kv_write_kernel<TS, TT><<<T, 256, 0, stream>>>(                                          \
+  rope_kv_write_kernel<TS, TT><<<grid, 128, 0, stream>>>(                                       \
       (const TS*)src, src_stride, planes, plane_stride, (TT*)q_out, q_stride, positions,        \
       seq_of_token, page_table, max_pages, inv_freq, rotary_dim, (TT*)k_cache, (TT*)v_cache,    \
       page_stride, head_stride, ring_pages, A, Kh, D, write_cache)
