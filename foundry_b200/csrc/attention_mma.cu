@@ -592,3 +592,69 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
     default: return launch_decode<128>(p, stream);
   }
 }
+
+// ------------------------------------------------- the entry point that allocates nothing
+// See attention_static.h for who calls it and why.
+#include <mutex>
+
+#include "attention_static.h"
+
+// The splits' partial results live here instead of in a caller's workspace.
+// In host code `g_static_scratch` is only a handle for the symbol: its device
+// address must be asked for with cudaGetSymbolAddress before a kernel gets it.
+static __device__ __align__(256) float g_static_scratch[FB_ATTENTION_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_addr[MAX_DEVICES] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the scratch array on the current device; looked up once.
+int static_scratch(float** addr) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fb_fail(2, "attention_decode_static: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= MAX_DEVICES)
+    return fb_fail(1, "attention_decode_static: device %d is beyond the %d this library tracks",
+                   device, MAX_DEVICES);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[device] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fb_fail(2, "attention_decode_static: cudaGetSymbolAddress failed: %s",
+                     cudaGetErrorString(e));
+    g_static_scratch_addr[device] = ptr;
+  }
+  *addr = g_static_scratch_addr[device];
+  return 0;
+}
+}  // namespace
+
+FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* out,
+                                      long long out_stride, const int* cu_tokens,
+                                      const int* kv_lens, const int* page_table, int max_pages,
+                                      const void* k_cache, const void* v_cache,
+                                      long long page_stride, long long head_stride, int n_seqs,
+                                      int A, int Kh, int D, float scale, int splits,
+                                      cudaStream_t stream) {
+  FB_REQUIRE(n_seqs > 0 && Kh > 0 && D > 0 && splits >= 1,
+             "attention_decode_static: bad sizes n_seqs=%d Kh=%d D=%d splits=%d", n_seqs, Kh, D,
+             splits);
+  const long long units = (long long)n_seqs * Kh * splits;
+  const long long need = units * (16LL * D + 32);
+  FB_REQUIRE(need <= (long long)FB_ATTENTION_STATIC_SCRATCH_FLOATS,
+             "attention_decode_static: %d sequences x %d kv heads x %d splits at head size %d need "
+             "%lld floats of scratch, the built-in array holds %d; use fewer splits or "
+             "fb_attention_decode with a workspace of your own",
+             n_seqs, Kh, splits, D, need, FB_ATTENTION_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc) return rc;
+  // partial outputs first, then the (max, sum) pairs; every entry a call reads it has written
+  float* ws_o = scratch;
+  float* ws_ml = scratch + units * 16 * D;
+  return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
+                             max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
+                             D, scale, splits, ws_o, ws_ml, stream);
+}

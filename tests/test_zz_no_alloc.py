@@ -1,0 +1,91 @@
+"""The entry point that allocates nothing, called through its exported C
+symbol, against the ordinary decode attention.
+
+Some callers of the kernels cannot request device memory when they call: all
+memory already belongs to their own arena, or they run where the CUDA
+allocator must not be entered. For them the library keeps the scratch of
+split-KV decode attention in a fixed device array of its own
+(`csrc/attention_static.h`). This test calls `fb_attention_decode_static`
+twice in a row with different shapes, so that the second call meets the first
+call's leftovers in the shared array, and checks both results against
+`fb_attention_decode` with a workspace from torch. It runs last, and passes
+alone in a fresh process as well as after every other test.
+"""
+import ctypes
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+SCRATCH_FLOATS = 2 * 1024 * 1024  # FB_ATTENTION_STATIC_SCRATCH_FLOATS
+
+
+def _case(n_seqs, lens, A, Kh, D, seed):
+    """Random queries and a paged cache with scattered pages."""
+    g = torch.Generator().manual_seed(seed)
+    pages_per = [(n + 63) // 64 for n in lens]
+    total = sum(pages_per) + 2
+    perm = torch.randperm(total, generator=g)
+    table = torch.zeros(n_seqs, max(pages_per), dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(pages_per):
+        table[i, :n] = perm[at:at + n].int()
+        at += n
+    store = torch.randn(total, 2, Kh, 64, D, generator=g).bfloat16().to(DEV)
+    q = torch.randn(n_seqs, A * D, generator=g).bfloat16().to(DEV)
+    cu = torch.arange(n_seqs + 1, dtype=torch.int32, device=DEV)
+    kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    return q, cu, kv, table.to(DEV), store[:, 0], store[:, 1]
+
+
+def _call_static(lib, q, out, cu, kv, table, k, v, A, Kh, D, splits):
+    fn = lib.fb_attention_decode_static
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_longlong,
+                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_longlong,
+                   ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+                   ctypes.c_int, ctypes.c_void_p]
+    return fn(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), cu.data_ptr(),
+              kv.data_ptr(), table.data_ptr(), table.shape[1], k.data_ptr(), v.data_ptr(),
+              k.stride(0), k.stride(1), kv.numel(), A, Kh, D, 1.0 / math.sqrt(D), splits,
+              torch.cuda.current_stream().cuda_stream)
+
+
+def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
+    from foundry_b200.kernels import library, ops
+    lib = library.load()
+    lib.fb_last_error.restype = ctypes.c_char_p
+    # two calls, the second smaller and of another head size: it reads nothing the first left
+    for n_seqs, lens, A, Kh, D, splits, seed in ((5, [700, 64, 1, 333, 129], 12, 4, 128, 6, 0),
+                                                 (3, [90, 200, 65], 4, 2, 32, 3, 1)):
+        q, cu, kv, table, k, v = _case(n_seqs, lens, A, Kh, D, seed)
+        want = torch.zeros_like(q)
+        ops.attention_decode(q, want, cu, kv, table, k, v, A, Kh, D, 1.0 / math.sqrt(D), splits)
+        got = torch.full_like(q, 7.0)
+        before = torch.cuda.memory_allocated()
+        rc = _call_static(lib, q, got, cu, kv, table, k, v, A, Kh, D, splits)
+        assert rc == 0, lib.fb_last_error().decode()
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+        err = (got.float() - want.float()).abs()
+        bound = 3e-2 + 1e-2 * want.float().abs()  # the tolerance of the attention kernel tests
+        assert bool((err <= bound).all()), float(err.max())
+        assert torch.equal(got, want)  # same kernels, same order of sums
+
+
+def test_static_scratch_entry_point_refuses_what_does_not_fit():
+    from foundry_b200.kernels import library
+    lib = library.load()
+    lib.fb_last_error.restype = ctypes.c_char_p
+    q, cu, kv, table, k, v = _case(2, [100, 100], 8, 8, 128, 2)
+    out = torch.zeros_like(q)
+    splits = SCRATCH_FLOATS // (2 * 8 * (16 * 128 + 32)) + 1
+    rc = _call_static(lib, q, out, cu, kv, table, k, v, 8, 8, 128, splits)
+    assert rc != 0
+    message = lib.fb_last_error().decode()
+    assert "scratch" in message and str(SCRATCH_FLOATS) in message
+    assert float(out.abs().max()) == 0.0  # nothing ran
