@@ -1,0 +1,203 @@
+// bfloat16 product for a handful of tokens (up to 16): out[t, n] = sum_k x[t,k] w[n,k].
+//
+// With so few tokens a projection (src/nn/linear.rs:19-36) is a stream of
+// weights through the chip: every weight byte is used once, for `tokens`
+// multiply-adds. This kernel is shaped for that. A CTA owns 16 weight rows;
+// its warps split K among themselves; every thread pulls 32 contiguous bytes
+// from each of its two rows per 64-element chunk, straight from global memory
+// into the registers of the tensor-core instruction's A operand
+// (mma.sync.m16n8k16, bf16 -> f32), several chunks in flight. The tokens are
+// the instruction's narrow N. The K index inside a chunk is permuted so that a
+// thread's 16 consecutive weights are what the instruction expects from it;
+// the same permutation is applied to x, so the sum is unchanged. At the end the
+// warps' partial sums meet in shared memory and the CTA writes its 16 output
+// features for every token (optionally as SiLU(gate) * up over row pairs).
+// No shared-memory staging of weights, no barriers in the main loop, no
+// workspace in global memory.
+//
+// Larger token counts run on the tcgen05 kernel (gemm_tcgen05.cu).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int CHUNK = 64;   // K elements per step of a warp
+constexpr int UNROLL = 4;   // chunks whose loads are in flight together
+
+// NT: token tiles of 8 (1 or 2). WARPS: warps per CTA, each with a K range.
+template <int NT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                   const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
+                   long long ldo, int out_f32, int T, int N, int K, int epilogue) {
+  __shared__ float red[WARPS][16][8 * NT + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);  // rows past N are discarded
+  const int chunks = (K + CHUNK - 1) / CHUNK;
+  const int per = (chunks + WARPS - 1) / WARPS;
+  const int c0 = warp * per, c1 = min(chunks, c0 + per);
+
+  // A thread's 16 elements of a 64-element chunk are [8t, 8t+8) and [32+8t, 32+8t+8):
+  // the four threads of a row group read 64 contiguous bytes per load instruction.
+  const __nv_bfloat16* w0 = w + (size_t)r0 * ldw + t * 8;
+  const __nv_bfloat16* w1 = w + (size_t)r1 * ldw + t * 8;
+  const __nv_bfloat16* xr[NT];
+  bool xok[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int tok = j * 8 + g;
+    xok[j] = tok < T;
+    xr[j] = x + (size_t)(xok[j] ? tok : 0) * ldx + t * 8;  // a padding row reads row 0, unused
+  }
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  // The thread's 16 elements feed four instructions; instruction s takes
+  // elements 4s..4s+3 as its k slots (2t, 2t+1, 2t+8, 2t+9).
+  auto multiply = [&](const uint4 (&a)[4], const uint4 (&b)[NT][2]) {
+    const uint32_t* a0 = reinterpret_cast<const uint32_t*>(&a[0]);  // row r0: 8 words
+    const uint32_t* a1 = reinterpret_cast<const uint32_t*>(&a[2]);  // row r1: 8 words
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const uint32_t* bx = reinterpret_cast<const uint32_t*>(&b[j][0]);
+        const uint32_t b0 = xok[j] ? bx[2 * s] : 0u, b1 = xok[j] ? bx[2 * s + 1] : 0u;
+        mma_bf16(acc[j], a0[2 * s], a1[2 * s], a0[2 * s + 1], a1[2 * s + 1], b0, b1);
+      }
+    }
+  };
+
+  // whole chunks, UNROLL at a time: every load is issued before the first use
+  const int full_end = min(c1, K / CHUNK);  // chunks that lie entirely inside K
+  int c = c0;
+  for (; c + UNROLL <= full_end; c += UNROLL) {
+    uint4 a[UNROLL][4];
+    uint4 b[UNROLL][NT][2];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const size_t off = (size_t)(c + u) * CHUNK;
+      a[u][0] = ld_stream(w0 + off);
+      a[u][1] = ld_stream(w0 + off + 32);
+      a[u][2] = ld_stream(w1 + off);
+      a[u][3] = ld_stream(w1 + off + 32);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        b[u][j][0] = ld_cached(xr[j] + off);
+        b[u][j][1] = ld_cached(xr[j] + off + 32);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) multiply(a[u], b[u]);
+  }
+  // the rest: single chunks, the last of which may reach beyond K
+  for (; c < c1; ++c) {
+    const size_t off = (size_t)c * CHUNK;
+    const int k = c * CHUNK + t * 8;
+    const bool lo = k + 8 <= K, hi = k + 32 + 8 <= K;
+    uint4 a[4];
+    uint4 b[NT][2];
+    a[0] = lo ? ld_stream(w0 + off) : zero;
+    a[1] = hi ? ld_stream(w0 + off + 32) : zero;
+    a[2] = lo ? ld_stream(w1 + off) : zero;
+    a[3] = hi ? ld_stream(w1 + off + 32) : zero;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      b[j][0] = lo ? ld_cached(xr[j] + off) : zero;
+      b[j][1] = hi ? ld_cached(xr[j] + off + 32) : zero;
+    }
+    multiply(a, b);
+  }
+  // acc[j][0..1]: row g, tokens j*8 + 2t, 2t+1; acc[j][2..3]: row g + 8
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    red[warp][g][j * 8 + 2 * t] = acc[j][0];
+    red[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+    red[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+    red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  float* out_f = reinterpret_cast<float*>(out);
+  __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(out);
+  if (epilogue == 0) {
+    for (int idx = threadIdx.x; idx < 16 * T; idx += WARPS * 32) {
+      const int row = idx & 15, tok = idx >> 4;
+      if (n0 + row >= N) continue;
+      float v = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < WARPS; ++wi) v += red[wi][row][tok];
+      const size_t o = (size_t)tok * ldo + n0 + row;
+      if (out_f32) out_f[o] = v;
+      else out_h[o] = __float2bfloat16_rn(v);
+    }
+  } else {
+    // rows 2p and 2p+1 hold gate p and up p: out[t, n0/2 + p] = silu(gate) * up
+    for (int idx = threadIdx.x; idx < 8 * T; idx += WARPS * 32) {
+      const int p = idx & 7, tok = idx >> 3;
+      if (n0 + 2 * p + 1 >= N) continue;
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < WARPS; ++wi) {
+        gate += red[wi][2 * p][tok];
+        up += red[wi][2 * p + 1][tok];
+      }
+      out_h[(size_t)tok * ldo + (n0 >> 1) + p] =
+          __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
+    }
+  }
+}
+
+}  // namespace
+
+// x: [T, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), T <= 16.
+// epilogue 0: out[T, N] (bf16 or float32, row stride ldo).
+// epilogue 1: w's rows are (gate, up) pairs; out[T, N / 2] bf16 = SiLU(gate) * up.
+FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                          long long ldo, int out_f32, int T, int N, int K, int epilogue,
+                          cudaStream_t stream) {
+  FB_REQUIRE(T > 0 && T <= 16 && N > 0 && K > 0, "gemm_skinny: bad sizes T=%d N=%d K=%d", T, N, K);
+  FB_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)x % 16) == 0 &&
+                 ((uintptr_t)w % 16) == 0,
+             "gemm_skinny: K, the row strides and the pointers must keep 16-byte alignment");
+  FB_REQUIRE(epilogue == 0 || (epilogue == 1 && !out_f32 && N % 2 == 0),
+             "gemm_skinny: the SiLU-mul epilogue needs a bf16 output and an even row count");
+  const int blocks = (N + 15) / 16;
+  const bool deep = K > 4096;
+#define FB_SKINNY(NT, W)                                                                   \
+  gemm_skinny_kernel<NT, W><<<blocks, W * 32, 0, stream>>>(                                \
+      (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw, out, ldo, out_f32, T, N, K, \
+      epilogue)
+  if (T <= 8) {
+    if (deep) FB_SKINNY(1, 8); else FB_SKINNY(1, 4);
+  } else {
+    if (deep) FB_SKINNY(2, 8); else FB_SKINNY(2, 4);
+  }
+#undef FB_SKINNY
+  return fb_check_launch("gemm_skinny");
+}

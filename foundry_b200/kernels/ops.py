@@ -41,6 +41,8 @@ _SIGNATURES = {
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
                    c_int, c_int, c_ll, c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
+    "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
+                       c_int, c_void_p],
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
@@ -304,6 +306,25 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue, _stream())
 
 
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
+    """Up to 16 token rows: the weight-streaming kernel (csrc/gemm_skinny.cu).
+    epilogue 1: `w` rows are (gate, up) pairs and out is [M, N/2] = SiLU(gate)*up."""
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny takes bfloat16 operands")
+    want = (M, N // 2) if epilogue else (M, N)
+    if tuple(out.shape) != want or w.shape[1] != K:
+        raise KernelError(f"gemm_skinny: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _call("fb_gemm_skinny", _dev(x, "x", contiguous=False), _rows(x, "x"),
+          _dev(w, "w", contiguous=False), _rows(w, "w"), _dev(out, "out", contiguous=False),
+          _rows(out, "out"), 1 if out.dtype == torch.float32 else 0, M, N, K, epilogue, _stream())
+    return out
+
+
+SKINNY_ROWS = 16  # token rows up to which the weight-streaming kernel is used
+
+
 def gemm_tc_status():
     """0 when no bounded wait of the tensor-core kernels ever ran out, else
     (role, block, k-block). Synchronises the device."""
@@ -344,8 +365,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
               out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
     """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
 
-    More than 128 rows: token rows fill the 128-row operand, weights the other
-    (256 wide). Up to 128 rows: swapped, the weights fill the 128-row operand and
+    Up to 16 rows: the weight-streaming kernel. More than 128 rows: token rows
+    fill the 128-row operand, weights the other (256 wide). In between: swapped, the weights fill the 128-row operand and
     stream through once, the tokens are the narrow operand; K is split over
     CTAs until the grid covers the SMs, each split writing a float32 plane.
     With `allow_planes` the planes are returned as `Planes` for a consumer that
@@ -364,6 +385,10 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_simt(x, w, out)
+    if M <= SKINNY_ROWS:
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        return gemm_skinny(x, w, out)
     if M > 128:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
@@ -404,6 +429,8 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         tmp = torch.empty((M, two_i), dtype=torch.bfloat16, device=x.device)
         gemm_simt(x, w_pairs, tmp)
         return silu_mul(tmp, out, interleaved=True)
+    if M <= SKINNY_ROWS:
+        return gemm_skinny(x, w_pairs, out, epilogue=1)
     if M > 128:
         bn = 256 if two_i >= 256 else (128 if two_i > 64 else 64)
         gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1)

@@ -457,3 +457,20 @@ def test_sampling_follows_the_distribution(ops):
     freq = torch.bincount(out.long().cpu(), minlength=V).double() / draws
     want = torch.softmax(base.double() / T, 0)
     assert float((freq - want).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("M", [1, 2, 7, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 64), (100, 72), (130, 200), (3072, 3072), (384, 8192), (50, 4104)])
+def test_gemm_skinny(ops, M, N, K):
+    """The weight-streaming kernel: ragged rows, K tails inside a chunk, both
+    warp counts, both token-tile counts, strided input and output."""
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=9)
+    want = x.double() @ w.double().T
+    out = torch.full((M, N), 7.0, device=DEV)
+    ops.gemm_skinny(x, w, out)
+    close(out, want, 2e-4 * math.sqrt(K), 1e-5)
+    wide_x = rnd(M, K + 64, dtype=torch.bfloat16, seed=10)
+    wide_out = torch.zeros(M, N + 3, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(wide_x[:, 8:8 + K], w, wide_out[:, :N])
+    close(wide_out[:, :N], wide_x[:, 8:8 + K].double() @ w.double().T, 2e-4 * math.sqrt(K) + 1e-2, 8e-3)
+    assert float(wide_out[:, N:].abs().max()) == 0.0
