@@ -116,6 +116,7 @@ struct AttnParams {
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_kernel(const AttnParams p) {
+  fb_pdl_wait();
   constexpr int KT = D / 16;  // k-steps of Q.K^T
   constexpr int NT = D / 8;   // n-tiles of P.V
   extern __shared__ __align__(128) uint8_t smem[];
@@ -287,6 +288,7 @@ attn_prefill_kernel(const AttnParams p) {
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const AttnParams p) {
+  fb_pdl_wait();
   constexpr int KT = D / 16, NT = D / 8;
   extern __shared__ __align__(128) uint8_t smem[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
@@ -464,6 +466,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* _
                                   __nv_bfloat16* __restrict__ out, long long out_stride,
                                   const int* __restrict__ cu_tokens, int A, int Kh, int D,
                                   int splits) {
+  fb_pdl_wait();
   const int seq = blockIdx.x, a = blockIdx.y;
   const int G = A / Kh, kvh = a / G, row = a - kvh * G;
   const size_t base = (size_t)(seq * Kh + kvh) * splits;
@@ -494,7 +497,7 @@ int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
     if (e != cudaSuccess) return fb_fail(2, "attention_prefill: %s", cudaGetErrorString(e));
     configured = true;
   }
-  attn_prefill_kernel<D><<<dim3(q_blocks, p.A), THREADS, bytes, stream>>>(p);
+  fb_launch(attn_prefill_kernel<D>, dim3(dim3(q_blocks, p.A)), dim3(THREADS), bytes, stream, p);
   return fb_check_launch("attention_prefill");
 }
 
@@ -510,10 +513,11 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
     configured = true;
   }
-  attn_decode_kernel<D><<<dim3(p.n_seqs, p.Kh, p.splits), THREADS, bytes, stream>>>(p);
+  fb_launch(attn_decode_kernel<D>, dim3(dim3(p.n_seqs, p.Kh, p.splits)), dim3(THREADS), bytes, stream, p);
   int rc = fb_check_launch("attention_decode");
   if (rc || p.splits == 1) return rc;
-  attn_merge_kernel<<<dim3(p.n_seqs, p.A), D < 32 ? 32 : D, 0, stream>>>(
+  const int merge_threads = D > 32 ? D : 32;
+  fb_launch(attn_merge_kernel, dim3(dim3(p.n_seqs, p.A)), dim3(merge_threads), 0, stream, 
       p.ws_o, p.ws_ml, p.out, p.out_stride, p.cu_tokens, p.A, p.Kh, D, p.splits);
   return fb_check_launch("attention_merge");
 }

@@ -52,6 +52,7 @@ attention_simt_kernel(const T* __restrict__ q, long long q_stride, T* __restrict
                       int max_pages, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                       long long page_stride, long long head_stride, int ring_pages, int window,
                       int A, int Kh, int D, float scale) {
+  fb_pdl_wait();
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -142,7 +143,7 @@ FB_API int fb_attention_simt(const void* q, long long q_stride, void* out, long 
   FB_REQUIRE(T <= 0x7fffffff / 1 && max_pages > 0, "attention: bad page table");
   if (T == 0) return 0;
   dim3 grid(T, (A + WARPS - 1) / WARPS);
-  FB_DISPATCH_DTYPE(dtype, E, (attention_simt_kernel<E><<<grid, WARPS * 32, 0, stream>>>(
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(attention_simt_kernel<E>, dim3(grid), dim3(WARPS * 32), 0, stream, 
       (const E*)q, q_stride, (E*)out, out_stride, positions, seq_of_token, page_table, max_pages,
       (const E*)k_cache, (const E*)v_cache, page_stride, head_stride, ring_pages, window, A, Kh, D,
       scale)));

@@ -18,6 +18,11 @@ int fb_check_launch(const char* what) {
   return 0;
 }
 
+int g_fb_pdl = 1;
+
+// 1 (default): kernels are launched for programmatic dependent launch; 0: plain launches.
+FB_API void fb_set_pdl(int on) { g_fb_pdl = on ? 1 : 0; }
+
 FB_API const char* fb_last_error() { return g_error; }
 
 // Bumped whenever an exported signature changes; the Python side refuses a

@@ -10,6 +10,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <utility>
 
 #define FB_API extern "C" __attribute__((visibility("default")))
 
@@ -27,6 +28,41 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
   do {                                             \
     if (!(cond)) return fb_fail(1, __VA_ARGS__);   \
   } while (0)
+
+// ------------------------------------------------------------------ launching
+// Every kernel of the library is launched through `fb_launch`, which marks the
+// launch for programmatic dependent launch: the kernel's blocks may be placed on
+// the SMs as the blocks of the kernel before it in the stream retire, without
+// waiting for that kernel's memory to be flushed first. In return every kernel
+// calls `fb_pdl_wait()` before it reads anything an earlier kernel wrote and
+// before it writes anything an earlier kernel may still read (only constants
+// such as weights may be touched before; the products request their first
+// weight tiles there). No kernel triggers its successor early
+// (griddepcontrol.launch_dependents): measured on the 3B decode step, blocks
+// of later kernels that sit waiting on the SMs slowed the weight-streaming
+// product more than the earlier start gained. `fb_set_pdl(0)` switches the mark
+// off: launches then serialise as usual and the device call does nothing.
+extern int g_fb_pdl;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_fb_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void fb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 // ---------------------------------------------------------------- device side
 template <typename T>

@@ -16,6 +16,7 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V) {
+  fb_pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * H;
@@ -32,7 +33,7 @@ FB_API int fb_embed_gather(const void* table, int table_dtype, const int* ids, f
   FB_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
   if (T == 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
-  FB_DISPATCH_DTYPE(table_dtype, E, (embed_gather_kernel<E><<<T, threads, 0, stream>>>(
+  FB_DISPATCH_DTYPE(table_dtype, E, (fb_launch(embed_gather_kernel<E>, dim3(T), dim3(threads), 0, stream, 
                                         (const E*)table, ids, out, H, V)));
   return fb_check_launch("embed_gather");
 }
@@ -79,6 +80,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
                                        int planes, long long plane_stride,
                                        const float* __restrict__ weight, TO* __restrict__ out,
                                        int H, float eps, float inv_h) {
+  fb_pdl_wait();
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H;
   float* x = resid + row;
@@ -130,6 +132,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    int planes, long long plane_stride,
                                    const float* __restrict__ weight, TO* __restrict__ out, int H,
                                    float eps, float inv_h) {
+  fb_pdl_wait();
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H;
   float* x = resid + row;
@@ -177,7 +180,7 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
     const int items = (groups + threads - 1) / threads;
 #define FB_NORM_LAUNCH(N)                                                                     \
     FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (                     \
-        add_rmsnorm_vec_kernel<TD, TO, N><<<T, threads, 0, stream>>>(                         \
+        fb_launch(add_rmsnorm_vec_kernel<TD, TO, N>, dim3(T), dim3(threads), 0, stream,                          \
             resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))))
     if (items <= 1) { FB_NORM_LAUNCH(1); }
     else if (items == 2) { FB_NORM_LAUNCH(2); }
@@ -187,7 +190,7 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
   }
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (
-      add_rmsnorm_kernel<TD, TO><<<T, threads, 0, stream>>>(
+      fb_launch(add_rmsnorm_kernel<TD, TO>, dim3(T), dim3(threads), 0, stream, 
           resid, (const TD*)delta, planes, plane_stride, weight, (TO*)out, H, eps, inv_h))));
   return fb_check_launch("add_rmsnorm");
 }
@@ -199,6 +202,7 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I,
                                 size_t total, int interleaved) {
+  fb_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
@@ -219,7 +223,7 @@ FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, 
   const int threads = 256;
   const size_t want = (total + threads - 1) / threads;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-  FB_DISPATCH_DTYPE(dtype, E, (silu_mul_kernel<E><<<blocks, threads, 0, stream>>>(
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(silu_mul_kernel<E>, dim3(blocks), dim3(threads), 0, stream, 
                                   (const E*)gate_up, (E*)out, I, total, interleaved)));
   return fb_check_launch("silu_mul");
 }
@@ -229,6 +233,7 @@ FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, 
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
                                    T* __restrict__ dst, int H) {
+  fb_pdl_wait();
   const int r = blockIdx.x;
   const int s = rows[r];
   T* d = dst + (size_t)r * H;
@@ -244,7 +249,7 @@ FB_API int fb_gather_rows(const void* src, int dtype, const int* rows, void* dst
                           cudaStream_t stream) {
   FB_REQUIRE(n >= 0 && H > 0, "gather_rows: bad sizes n=%d H=%d", n, H);
   if (n == 0) return 0;
-  FB_DISPATCH_DTYPE(dtype, E, (gather_rows_kernel<E><<<n, 256, 0, stream>>>(
+  FB_DISPATCH_DTYPE(dtype, E, (fb_launch(gather_rows_kernel<E>, dim3(n), dim3(256), 0, stream, 
                                   (const E*)src, rows, (E*)dst, H)));
   return fb_check_launch("gather_rows");
 }
@@ -252,6 +257,7 @@ FB_API int fb_gather_rows(const void* src, int dtype, const int* rows, void* dst
 // ----------------------------------------------------------------------- cast
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  fb_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
     out[i] = fb_from_float<TO>(fb_to_float<TI>(in[i]));
@@ -264,7 +270,7 @@ FB_API int fb_cast(const void* in, int in_dtype, void* out, int out_dtype, long 
   const size_t want = ((size_t)n + 255) / 256;
   const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
   FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (
-      cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)in, (TO*)out, (size_t)n))));
+      fb_launch(cast_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)in, (TO*)out, (size_t)n))));
   return fb_check_launch("cast");
 }
 
@@ -274,6 +280,7 @@ FB_API int fb_cast(const void* in, int in_dtype, void* out, int out_dtype, long 
 template <typename TO>
 __global__ void sum_planes_kernel(const float* __restrict__ planes, int S, long long n,
                                   long long plane_stride, TO* __restrict__ out) {
+  fb_pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
     float acc = planes[i];
@@ -288,7 +295,7 @@ FB_API int fb_sum_planes(const float* planes, int S, long long n, long long plan
   if (n == 0) return 0;
   const long long want = (n + 255) / 256;
   const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
-  FB_DISPATCH_DTYPE(out_dtype, TO, (sum_planes_kernel<TO><<<blocks, 256, 0, stream>>>(
+  FB_DISPATCH_DTYPE(out_dtype, TO, (fb_launch(sum_planes_kernel<TO>, dim3(blocks), dim3(256), 0, stream, 
                                        planes, S, n, plane_stride, (TO*)out)));
   return fb_check_launch("sum_planes");
 }

@@ -16,6 +16,7 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TI* __restrict__ x, const TI* __restrict__ w, TO* __restrict__ out, int M,
                  int N, int K, long long ldx, long long ldw, long long ldo) {
+  fb_pdl_wait();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -74,7 +75,7 @@ FB_API int fb_gemm_simt(const void* x, const void* w, void* out, int M, int N, i
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   FB_REQUIRE(grid.y <= 65535, "gemm_simt: M=%d exceeds the grid limit", M);
   FB_DISPATCH_DTYPE(in_dtype, TI, FB_DISPATCH_DTYPE(out_dtype, TO, (
-      gemm_simt_kernel<TI, TO><<<grid, 256, 0, stream>>>(
+      fb_launch(gemm_simt_kernel<TI, TO>, dim3(grid), dim3(256), 0, stream, 
           (const TI*)x, (const TI*)w, (TO*)out, M, N, K, ldx, ldw, ldo))));
   return fb_check_launch("gemm_simt");
 }

@@ -44,10 +44,10 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 constexpr int CHUNK = 64;   // K elements per step of a warp
-constexpr int UNROLL = 4;   // chunks whose loads are in flight together
 
 // NT: token tiles of 8 (1 or 2). WARPS: warps per CTA, each with a K range.
-template <int NT, int WARPS>
+// UNROLL: chunks whose loads are in flight together.
+template <int NT, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                    const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
@@ -95,8 +95,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
   };
 
   // whole chunks, UNROLL at a time: every load is issued before the first use
+  // The weights are constants: their first loads go out before this kernel
+  // waits for the one that produces x.
   const int full_end = min(c1, K / CHUNK);  // chunks that lie entirely inside K
   int c = c0;
+  bool waited = false;
   for (; c + UNROLL <= full_end; c += UNROLL) {
     uint4 a[UNROLL][4];
     uint4 b[UNROLL][NT][2];
@@ -107,6 +110,14 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
       a[u][1] = ld_stream(w0 + off + 32);
       a[u][2] = ld_stream(w1 + off);
       a[u][3] = ld_stream(w1 + off + 32);
+    }
+    if (!waited) {
+      fb_pdl_wait();
+      waited = true;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const size_t off = (size_t)(c + u) * CHUNK;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         b[u][j][0] = ld_cached(xr[j] + off);
@@ -116,6 +127,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) multiply(a[u], b[u]);
   }
+  if (!waited) fb_pdl_wait();
   // the rest: single chunks, the last of which may reach beyond K
   for (; c < c1; ++c) {
     const size_t off = (size_t)c * CHUNK;
@@ -188,16 +200,33 @@ FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long
   FB_REQUIRE(epilogue == 0 || (epilogue == 1 && !out_f32 && N % 2 == 0),
              "gemm_skinny: the SiLU-mul epilogue needs a bf16 output and an even row count");
   const int blocks = (N + 15) / 16;
-  const bool deep = K > 4096;
-#define FB_SKINNY(NT, W)                                                                   \
-  gemm_skinny_kernel<NT, W><<<blocks, W * 32, 0, stream>>>(                                \
-      (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw, out, ldo, out_f32, T, N, K, \
-      epilogue)
-  if (T <= 8) {
-    if (deep) FB_SKINNY(1, 8); else FB_SKINNY(1, 4);
-  } else {
-    if (deep) FB_SKINNY(2, 8); else FB_SKINNY(2, 4);
-  }
+  // Warps per CTA: enough warps on the chip to cover the memory latency (about
+  // 16 per SM), at least two chunks of K each.
+  const int chunks = (K + CHUNK - 1) / CHUNK;
+  int warps = (148 * 16 + blocks - 1) / blocks;
+  warps = warps <= 4 ? 4 : warps <= 8 ? 8 : 16;
+  while (warps > 4 && chunks / warps < 2) warps /= 2;
+  const int per = (chunks + warps - 1) / warps;
+  const int unroll = per >= 4 ? 4 : per >= 3 ? 3 : 2;
+#define FB_SKINNY(NT, W, U)                                                                   \
+  fb_launch(gemm_skinny_kernel<NT, W, U>, dim3(blocks), dim3(W * 32), 0, stream,               \
+            (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw, out, ldo, out_f32, T, N, \
+            K, epilogue)
+#define FB_SKINNY_U(NT, W)                                    \
+  do {                                                        \
+    if (unroll == 4) FB_SKINNY(NT, W, 4);                     \
+    else if (unroll == 3) FB_SKINNY(NT, W, 3);                \
+    else FB_SKINNY(NT, W, 2);                                 \
+  } while (0)
+#define FB_SKINNY_W(NT)                                       \
+  do {                                                        \
+    if (warps == 4) FB_SKINNY_U(NT, 4);                       \
+    else if (warps == 8) FB_SKINNY_U(NT, 8);                  \
+    else FB_SKINNY_U(NT, 16);                                 \
+  } while (0)
+  if (T <= 8) FB_SKINNY_W(1); else FB_SKINNY_W(2);
+#undef FB_SKINNY_W
+#undef FB_SKINNY_U
 #undef FB_SKINNY
   return fb_check_launch("gemm_skinny");
 }

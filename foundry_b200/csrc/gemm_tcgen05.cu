@@ -154,6 +154,7 @@ struct GemmParams {
   long long split_stride;        // elements between split-K planes
   void* out;
   int out_f32;                // 1: float32 output, 0: bfloat16
+  int constant_operand;       // 1: A holds constants (weights), 2: B does, 0: neither
   int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs
 };
 
@@ -216,7 +217,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
+      // The operand that holds weights does not depend on the kernel before this
+      // one: its first stages are requested at once, the other operand's after
+      // the wait. (The stages are empty at the start: no wait on `empty` yet.)
+      const int early = nkb < STAGES ? nkb : STAGES;
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a_dst = tiles + i * Smem<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+        mbar_expect_tx(&full[i], Smem<BN>::STAGE_BYTES);
+        const int k = (kb0 + i) * BK;
+        if (p.constant_operand == 1) tma_load_2d(a_dst, &map_a, &full[i], k, tile_a * BM);
+        if (p.constant_operand == 2) tma_load_2d(b_dst, &map_b, &full[i], k, tile_b * BN);
+      }
+      fb_pdl_wait();
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a_dst = tiles + i * Smem<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+        const int k = (kb0 + i) * BK;
+        if (p.constant_operand != 1) tma_load_2d(a_dst, &map_a, &full[i], k, tile_a * BM);
+        if (p.constant_operand != 2) tma_load_2d(b_dst, &map_b, &full[i], k, tile_b * BN);
+      }
+      for (int i = early; i < nkb; ++i) {
         const int s = i % STAGES;
         const uint32_t phase = (uint32_t)(i / STAGES) & 1u;
         if (!mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, i)) break;
@@ -259,6 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool ok = true;
     if (nkb > 0) ok = mbar_wait(acc_full, 0, abort_flag, 3, 0);
     tc_fence_after();
+    fb_pdl_wait();  // returns at once when operands arrived; orders the stores for nkb == 0
     if (ok) {
       float* out_f = (float*)p.out + (long long)split * p.split_stride;
       __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
@@ -466,7 +488,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
     if (e != cudaSuccess) return fb_fail(2, "gemm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc_kernel<BN><<<grid, THREADS, Smem<BN>::BYTES, stream>>>(ma, mb, p);
+  fb_launch(gemm_tc_kernel<BN>, dim3(grid), dim3(THREADS), Smem<BN>::BYTES, stream, ma, mb, p);
   return fb_check_launch("gemm_tc");
 }
 
@@ -478,13 +500,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 //   bn: the B-tile height (16, 32, 64, 128 or 256); splits: K ranges per tile
 // With splits > 1 the output must be float32 and holds `splits` partial planes
 // that the caller sums.
+// constant_operand names the operand (1: a, 2: b, 0: none) that no earlier kernel
+// in the stream writes (weights); its first loads do not wait for that kernel.
 // epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
 // pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
 // dimension must be 1 and then indexes pairs.
 FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, long long ldb,
                       int rows_b, int K, void* out, long long stride_a, long long stride_b,
                       int out_f32, int bn, int splits, long long split_stride, int epilogue,
-                      cudaStream_t stream) {
+                      int constant_operand, cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, K);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
              "gemm_tc: K and the row strides must be multiples of 8 elements (16 bytes), got K=%d "
@@ -503,6 +527,7 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   p.kblocks_per_split = (total_kb + splits - 1) / splits;
   p.stride_a = stride_a; p.stride_b = stride_b; p.split_stride = split_stride;
   p.out = out; p.out_f32 = out_f32; p.epilogue = epilogue;
+  p.constant_operand = constant_operand;
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, rows_a, K, lda, BM);
   if (rc) return rc;

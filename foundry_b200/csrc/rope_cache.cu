@@ -31,6 +31,7 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      long long page_stride, long long head_stride, int ring_pages,
                                      int A, int Kh, int D, int write_cache) {
+  fb_pdl_wait();
   const int t = blockIdx.x;
   const int seq = seq_of_token[t];
   if (seq < 0) return;  // padding token
@@ -147,7 +148,7 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   if (per_token > 16) per_token = 16;
   dim3 grid(T, per_token);
 #define FB_ROPE_LAUNCH(TS, TT)                                                                  \
-  rope_kv_write_kernel<TS, TT><<<grid, 128, 0, stream>>>(                                       \
+  fb_launch(rope_kv_write_kernel<TS, TT>, dim3(grid), dim3(128), 0, stream,                                        \
       (const TS*)src, src_stride, planes, plane_stride, (TT*)q_out, q_stride, positions,        \
       seq_of_token, page_table, max_pages, inv_freq, rotary_dim, (TT*)k_cache, (TT*)v_cache,    \
       page_stride, head_stride, ring_pages, A, Kh, D, write_cache)

@@ -36,6 +36,7 @@ select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int
                      const long long* __restrict__ streams, const long long* __restrict__ steps,
                      float* __restrict__ part_val, int* __restrict__ part_idx,
                      int* __restrict__ out) {
+  fb_pdl_wait();
   __shared__ float best_v[32];
   __shared__ int best_i[32];
   const int r = blockIdx.x, c = blockIdx.y, chunks = gridDim.y;
@@ -97,6 +98,7 @@ select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int
 __global__ void select_merge_kernel(const float* __restrict__ part_val,
                                     const int* __restrict__ part_idx, int chunks,
                                     int* __restrict__ out) {
+  fb_pdl_wait();
   const int r = blockIdx.x, lane = threadIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -131,10 +133,10 @@ FB_API int fb_select_tokens(const float* logits, long long row_stride, int n, in
   if (n == 0) return 0;
   const int chunk = (V + chunks - 1) / chunks;
   const int threads = chunk >= 8192 ? 1024 : 256;
-  select_tokens_kernel<<<dim3(n, chunks), threads, 0, stream>>>(
+  fb_launch(select_tokens_kernel, dim3(dim3(n, chunks)), dim3(threads), 0, stream, 
       logits, row_stride, V, chunk, temperature, streams, steps, part_val, part_idx, out);
   int rc = fb_check_launch("select_tokens");
   if (rc || chunks == 1) return rc;
-  select_merge_kernel<<<n, 32, 0, stream>>>(part_val, part_idx, chunks, out);
+  fb_launch(select_merge_kernel, dim3(n), dim3(32), 0, stream, part_val, part_idx, chunks, out);
   return fb_check_launch("select_merge");
 }

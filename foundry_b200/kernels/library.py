@@ -29,7 +29,7 @@ ABI_VERSION = 1
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-]
+] + os.environ.get("FOUNDRY_B200_NVCC_EXTRA", "").split()
 
 
 class KernelLibraryError(RuntimeError):

@@ -39,7 +39,7 @@ _SIGNATURES = {
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
-                   c_int, c_int, c_ll, c_int, c_void_p],
+                   c_int, c_int, c_ll, c_int, c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                        c_int, c_void_p],
@@ -293,7 +293,8 @@ SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
-            bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0) -> None:
+            bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0,
+            constant_operand: int = 0) -> None:
     """Tensor-core product D[i,j] = sum_k a[i,k] b[j,k] written to
     out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu."""
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
@@ -303,7 +304,8 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
     _call("fb_gemm_tc", _dev(a, "a", contiguous=False), _rows(a, "a"), a.shape[0],
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
-          1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue, _stream())
+          1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
+          constant_operand, _stream())
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
@@ -322,7 +324,22 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     return out
 
 
-SKINNY_ROWS = 16  # token rows up to which the weight-streaming kernel is used
+import os as _os
+
+# token rows up to which the weight-streaming kernel is used
+SKINNY_ROWS = int(_os.environ.get("FOUNDRY_B200_SKINNY_ROWS", "16"))
+
+
+def set_dependent_launch(on: bool) -> None:
+    """Switch programmatic dependent launch of the kernels on or off (on by default)."""
+    lib = library.load()
+    lib.fb_set_pdl.argtypes = [ctypes.c_int]
+    lib.fb_set_pdl.restype = None
+    lib.fb_set_pdl(1 if on else 0)
+
+
+if _os.environ.get("FOUNDRY_B200_PDL", "1") == "0":
+    set_dependent_launch(False)
 
 
 def gemm_tc_status():
@@ -393,16 +410,16 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         bn = 256 if N >= 256 else (128 if N > 64 else 64)
-        gemm_tc(x, w, out, out.stride(0), 1, bn)
+        gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2)
         return out
     bn, splits = _swapped_plan(M, N, K)
     if splits == 1:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        gemm_tc(w, x, out, 1, out.stride(0), bn)
+        gemm_tc(w, x, out, 1, out.stride(0), bn, constant_operand=1)
         return out
     planes = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
-    gemm_tc(w, x, planes, 1, N, bn, splits, M * N)
+    gemm_tc(w, x, planes, 1, N, bn, splits, M * N, constant_operand=1)
     if allow_planes and out is None:
         return Planes(planes)
     if out is None:
@@ -433,10 +450,10 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         return gemm_skinny(x, w_pairs, out, epilogue=1)
     if M > 128:
         bn = 256 if two_i >= 256 else (128 if two_i > 64 else 64)
-        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1)
+        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2)
     else:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-        gemm_tc(w_pairs, x, out, 1, out.stride(0), bn, epilogue=1)
+        gemm_tc(w_pairs, x, out, 1, out.stride(0), bn, epilogue=1, constant_operand=1)
     return out
 
 
