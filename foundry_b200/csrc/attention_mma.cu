@@ -6,8 +6,9 @@
 //   decode    one new token per sequence: the G query heads that share a
 //             key-value head form one 16-row tile (rows >= G are padding), the
 //             four warps own 16 keys of each page, the cache range is split
-//             over CTAs, and a second kernel merges the partial results. No
-//             kernel waits on another.
+//             over CTAs, and the CTA that delivers the last partial result of a
+//             (sequence, kv head) merges them all (it learns that it is the
+//             last from an atomic counter; nobody waits for anybody).
 //
 // Formulas are the reference's (src/nn/attention.rs:23-60: head a reads kv head
 // a / G; src/models/llama/attention.rs:56-58: scale 1/sqrt(D);
@@ -110,6 +111,7 @@ struct AttnParams {
   int splits;
   float* ws_o;   // [n_seqs, Kh, splits, 16, D]
   float* ws_ml;  // [n_seqs, Kh, splits, 16, 2]
+  int* counters; // [n_seqs, Kh]: splits that have delivered; zero between calls
 };
 
 // --------------------------------------------------------------------- prefill
@@ -285,6 +287,42 @@ attn_prefill_kernel(const AttnParams p) {
 }
 
 // ---------------------------------------------------------------------- decode
+// Called by every CTA of a (sequence, kv head) after it has written its partial
+// result. The CTA whose count completes the set reads all partial results and
+// writes the heads' outputs; it then puts the counter back to zero for the next
+// call. Publishing follows the usual pattern: writes, fence, barrier, one atomic
+// add; the reader fences after seeing the full count and reads around L1.
+template <int D>
+__device__ void merge_if_last(const AttnParams& p, int seq, int kvh, int token, int G) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int before = atomicAdd(&p.counters[seq * p.Kh + kvh], 1);
+    s_last = before == p.splits - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const size_t base = (size_t)(seq * p.Kh + kvh) * p.splits;
+  for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float M = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.ws_ml + (base + s) * 32 + 2 * row));
+    float L = 0.f, acc = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float ms = __ldcg(p.ws_ml + (base + s) * 32 + 2 * row);
+      if (ms == -INFINITY) continue;
+      const float f = exp2f(ms - M);
+      L += __ldcg(p.ws_ml + (base + s) * 32 + 2 * row + 1) * f;
+      acc += __ldcg(p.ws_o + ((base + s) * 16 + row) * D + d) * f;
+    }
+    p.out[(long long)token * p.out_stride + (long long)(kvh * G + row) * D + d] =
+        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+  if (threadIdx.x == 0) p.counters[seq * p.Kh + kvh] = 0;
+}
+
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const AttnParams p) {
@@ -310,6 +348,7 @@ attn_decode_kernel(const AttnParams p) {
   if (pg0 >= pg1) {  // nothing in this range (or a padding row: kv_len == 0)
     if (p.splits > 1) {
       for (int i = threadIdx.x; i < G; i += THREADS) { ws_ml[2 * i] = -INFINITY; ws_ml[2 * i + 1] = 0.f; }
+      merge_if_last<D>(p, seq, kvh, token, G);
     } else {
       for (int i = threadIdx.x; i < G * D; i += THREADS)
         p.out[(long long)token * p.out_stride + (long long)(kvh * G) * D + i] = __float2bfloat16_rn(0.f);
@@ -459,32 +498,7 @@ attn_decode_kernel(const AttnParams p) {
           __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
   }
-}
-
-// Merges the split results of one (sequence, head): grid (n_seqs, A), D threads.
-__global__ void attn_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
-                                  __nv_bfloat16* __restrict__ out, long long out_stride,
-                                  const int* __restrict__ cu_tokens, int A, int Kh, int D,
-                                  int splits) {
-  fb_pdl_wait();
-  const int seq = blockIdx.x, a = blockIdx.y;
-  const int G = A / Kh, kvh = a / G, row = a - kvh * G;
-  const size_t base = (size_t)(seq * Kh + kvh) * splits;
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, ws_ml[(base + s) * 32 + 2 * row]);
-  const int token = cu_tokens[seq];
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = ws_ml[(base + s) * 32 + 2 * row];
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - M);
-      L += ws_ml[(base + s) * 32 + 2 * row + 1] * f;
-      acc += ws_o[((base + s) * 16 + row) * D + d] * f;
-    }
-    out[(long long)token * out_stride + (long long)a * D + d] =
-        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
-  }
+  if (p.splits > 1) merge_if_last<D>(p, seq, kvh, token, G);
 }
 
 template <int D>
@@ -513,13 +527,8 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
     configured = true;
   }
-  fb_launch(attn_decode_kernel<D>, dim3(dim3(p.n_seqs, p.Kh, p.splits)), dim3(THREADS), bytes, stream, p);
-  int rc = fb_check_launch("attention_decode");
-  if (rc || p.splits == 1) return rc;
-  const int merge_threads = D > 32 ? D : 32;
-  fb_launch(attn_merge_kernel, dim3(dim3(p.n_seqs, p.A)), dim3(merge_threads), 0, stream, 
-      p.ws_o, p.ws_ml, p.out, p.out_stride, p.cu_tokens, p.A, p.Kh, D, p.splits);
-  return fb_check_launch("attention_merge");
+  fb_launch(attn_decode_kernel<D>, dim3(p.n_seqs, p.Kh, p.splits), dim3(THREADS), bytes, stream, p);
+  return fb_check_launch("attention_decode");
 }
 
 int check_common(const char* what, int n_seqs, int A, int Kh, int D, long long q_stride,
@@ -568,19 +577,21 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
 
 // One token per sequence. `splits` CTAs share each (sequence, kv head); with
 // splits > 1 the workspaces must hold n_seqs*Kh*splits*16*D and
-// n_seqs*Kh*splits*32 floats. A sequence with kv_lens == 0 is padding: its
-// output rows are zeros.
+// n_seqs*Kh*splits*32 floats, and `counters` n_seqs*Kh ints that are zero when
+// the call starts (the kernel leaves them zero again). A sequence with
+// kv_lens == 0 is padding: its output rows are zeros.
 FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                const int* cu_tokens, const int* kv_lens, const int* page_table,
                                int max_pages, const void* k_cache, const void* v_cache,
                                long long page_stride, long long head_stride, int n_seqs, int A,
                                int Kh, int D, float scale, int splits, float* ws_o, float* ws_ml,
-                               cudaStream_t stream) {
+                               int* counters, cudaStream_t stream) {
   int rc = check_common("attention_decode", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
                         v_cache, page_stride, head_stride);
   if (rc) return rc;
   FB_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: bad split count %d", splits);
-  FB_REQUIRE(splits == 1 || (ws_o && ws_ml), "attention_decode: split results need workspaces");
+  FB_REQUIRE(splits == 1 || (ws_o && ws_ml && counters),
+             "attention_decode: split results need workspaces and counters");
   AttnParams p{};
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
@@ -588,7 +599,7 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.page_stride = page_stride; p.head_stride = head_stride;
   p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E;
-  p.splits = splits; p.ws_o = ws_o; p.ws_ml = ws_ml;
+  p.splits = splits; p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
   switch (D) {
     case 16: return launch_decode<16>(p, stream);
     case 32: return launch_decode<32>(p, stream);
@@ -646,7 +657,7 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
              "attention_decode_static: bad sizes n_seqs=%d Kh=%d D=%d splits=%d", n_seqs, Kh, D,
              splits);
   const long long units = (long long)n_seqs * Kh * splits;
-  const long long need = units * (16LL * D + 32);
+  const long long need = units * (16LL * D + 32) + ((long long)n_seqs * Kh + 63) / 64 * 64;
   FB_REQUIRE(need <= (long long)FB_ATTENTION_STATIC_SCRATCH_FLOATS,
              "attention_decode_static: %d sequences x %d kv heads x %d splits at head size %d need "
              "%lld floats of scratch, the built-in array holds %d; use fewer splits or "
@@ -655,10 +666,16 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* scratch = nullptr;
   int rc = static_scratch(&scratch);
   if (rc) return rc;
-  // partial outputs first, then the (max, sum) pairs; every entry a call reads it has written
-  float* ws_o = scratch;
-  float* ws_ml = scratch + units * 16 * D;
+  // The arrival counters sit at the start of the array. They are the one part that
+  // must be zero when a call starts: the array is zero when the library is loaded,
+  // and the kernel puts every counter it used back to zero before it ends. Behind
+  // them come the partial outputs and the (max, sum) pairs, which a call writes
+  // before it reads them.
+  int* counters = reinterpret_cast<int*>(scratch);
+  const long long head = ((long long)n_seqs * Kh + 63) / 64 * 64;
+  float* ws_o = scratch + head;
+  float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, ws_o, ws_ml, stream);
+                             D, scale, splits, ws_o, ws_ml, counters, stream);
 }

@@ -28,16 +28,18 @@ extern "C" {
 // that no workspace is passed: partial results of the `splits` cache ranges go
 // to the library's own scratch array.
 //
-//   needs  n_seqs * Kh * splits * (16 * D + 32) <= FB_ATTENTION_STATIC_SCRATCH_FLOATS,
-//          else it returns non-zero with a message in fb_last_error() and
-//          launches nothing.
+//   needs  n_seqs * Kh * splits * (16 * D + 32) + n_seqs * Kh (rounded up to 64)
+//          <= FB_ATTENTION_STATIC_SCRATCH_FLOATS, else it returns non-zero with a
+//          message in fb_last_error() and launches nothing.
 //   calls  no cudaMalloc, cudaFree or any allocating routine.
 //   first call on a device: looks up the scratch array's device address (once
 //          per device, with that device current). Make this first call before
 //          any stream capture begins.
 //   shared state: every call on a device uses the same array, which keeps what
-//          the last call left. Nothing in it has to start at zero: each call
-//          writes every entry it later reads. Two calls that overlap on the GPU
+//          the last call left. Only the arrival counters at its start must be
+//          zero when a call begins: they are zero when the library is loaded and
+//          the kernel clears each one it used before it ends; everything else a
+//          call writes before it reads. Two calls that overlap on the GPU
 //          (different streams, no ordering between them) race on the array;
 //          order them, as calls on one stream are.
 int fb_attention_decode_static(const void* q, long long q_stride, void* out, long long out_stride,

@@ -48,7 +48,7 @@ _SIGNATURES = {
                              c_float, c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_void_p, c_void_p, c_void_p],
+                            c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
 }
@@ -473,15 +473,31 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
         return attention_simt(q, out, ctx.positions, ctx.seq_of_token, page_table, k_cache,
                               v_cache, num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
     if ctx.is_decode:
-        pairs = ctx.n_seqs * num_kv_heads
-        bound = max(1, (ctx.max_kv_len + PAGE - 1) // PAGE)
-        splits = max(1, min(bound, (4 * SM_COUNT + pairs - 1) // pairs))
+        splits = decode_splits(ctx.n_seqs * num_kv_heads, (ctx.max_kv_len + PAGE - 1) // PAGE)
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                                 num_heads, num_kv_heads, head_dim, scale, splits)
     blocks = sum((ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] + 63) // 64
                  for i in range(ctx.n_seqs))
     return attention_prefill(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
+
+
+DECODE_CTAS_PER_SM = 3  # what the decode attention kernel's shared memory allows at head size 128
+
+
+def decode_splits(pairs: int, pages: int) -> int:
+    """How many CTAs share one (sequence, kv head) in decode attention: the
+    count that minimises waves x (pages per CTA + a fixed cost of about two
+    pages), a wave being the CTAs the chip holds at once."""
+    slots = SM_COUNT * DECODE_CTAS_PER_SM
+    pages = max(1, pages)
+    best, best_cost = 1, None
+    for s in range(1, min(pages, 64) + 1):
+        waves = (pairs * s + slots - 1) // slots
+        cost = waves * ((pages + s - 1) // s + 2)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
@@ -501,23 +517,39 @@ def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, 
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
                      num_kv_heads, head_dim, scale, splits) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
-    over `splits` CTAs per (sequence, kv head); two launches when splits > 1."""
+    over `splits` CTAs per (sequence, kv head); the CTA that finishes a pair
+    last merges its partial results."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
     n = kv_lens.numel()
-    ws_o = ws_ml = None
+    ws_o = ws_ml = counters = None
     if splits > 1:
         ws_o = torch.empty(n * num_kv_heads * splits * 16 * head_dim, dtype=torch.float32,
                            device=q.device)
         ws_ml = torch.empty(n * num_kv_heads * splits * 32, dtype=torch.float32, device=q.device)
-        _COUNT[0] += 1  # the merge kernel
+        counters = _arrival_counters(q.device, n * num_kv_heads)
     _call("fb_attention_decode", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
           _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
           _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
           head_dim, float(scale), splits, 0 if ws_o is None else ws_o.data_ptr(),
-          0 if ws_ml is None else ws_ml.data_ptr(), _stream())
+          0 if ws_ml is None else ws_ml.data_ptr(),
+          0 if counters is None else counters.data_ptr(), _stream())
     return out
+
+
+_COUNTERS = {}
+
+
+def _arrival_counters(device, count: int) -> torch.Tensor:
+    """Zeroed int32 counters shared by all decode-attention calls on a device:
+    each call finds them zero and leaves them zero (calls on one stream follow
+    one another, so sharing is safe there)."""
+    held = _COUNTERS.get(device)
+    if held is None or held.numel() < count:
+        held = torch.zeros(max(65536, count), dtype=torch.int32, device=device)
+        _COUNTERS[device] = held
+    return held
 
 
 def attention_simt(q: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
