@@ -27,6 +27,7 @@
 namespace {
 
 constexpr int THREADS = 128;
+constexpr int DECODE_STAGES = 3;  // page buffers of the decode kernel
 constexpr float LOG2E = 1.4426950408889634f;
 
 // ------------------------------------------------------------- small PTX faces
@@ -128,7 +129,9 @@ attn_prefill_kernel(const AttnParams p) {
   __shared__ int s_info[2];
 
   if (threadIdx.x == 0) {
-    int b = blockIdx.x, s = 0;
+    // Later blocks of a sequence walk more pages: hand them out first, so that the
+    // long ones do not end up alone at the tail of the grid.
+    int b = (int)(gridDim.x - 1 - blockIdx.x), s = 0;
     for (; s < p.n_seqs; ++s) {
       const int nb = (p.cu_tokens[s + 1] - p.cu_tokens[s] + 63) / 64;
       if (b < nb) break;
@@ -329,9 +332,13 @@ attn_decode_kernel(const AttnParams p) {
   fb_pdl_wait();
   constexpr int KT = D / 16, NT = D / 8;
   extern __shared__ __align__(128) uint8_t smem[];
+  // Three page buffers: two pages are on their way while one is multiplied. A
+  // CTA's speed is pages in flight / memory latency, and the kernel has nothing
+  // else to hide that latency behind.
+  constexpr int ST = DECODE_STAGES;
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
-  __nv_bfloat16* sK = sQ + 16 * D;                              // [2][64][D]
-  __nv_bfloat16* sV = sK + 2 * 64 * D;                          // [2][64][D]
+  __nv_bfloat16* sK = sQ + 16 * D;                              // [ST][64][D]
+  __nv_bfloat16* sV = sK + ST * 64 * D;                         // [ST][64][D]
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int G = p.A / p.Kh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -361,12 +368,15 @@ attn_decode_kernel(const AttnParams p) {
 
   // rows 0..G-1 of the tile are this kv head's query heads, consecutive in q
   load_tile<D>(sQ, p.q + (long long)token * p.q_stride + (long long)(kvh * G) * D, D, 16, G);
-  {
-    const long long off = (long long)pages[pg0] * p.page_stride;
-    load_tile<D>(sK, kbase + off, D, 64, 64);
-    load_tile<D>(sV, vbase + off, D, 64, 64);
+#pragma unroll
+  for (int ahead = 0; ahead < ST - 1; ++ahead) {
+    if (pg0 + ahead < pg1) {
+      const long long off = (long long)pages[pg0 + ahead] * p.page_stride;
+      load_tile<D>(sK + ahead * 64 * D, kbase + off, D, 64, 64);
+      load_tile<D>(sV + ahead * 64 * D, vbase + off, D, 64, 64);
+    }
+    cp_async_commit();  // one group per page, empty when there is no page
   }
-  cp_async_commit();
 
   uint32_t qf[KT][4];
   float o[NT][4];
@@ -375,14 +385,15 @@ attn_decode_kernel(const AttnParams p) {
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   for (int pg = pg0; pg < pg1; ++pg) {
-    const int st = (pg - pg0) & 1;
-    if (pg + 1 < pg1) {
-      const long long off = (long long)pages[pg + 1] * p.page_stride;
-      load_tile<D>(sK + (st ^ 1) * 64 * D, kbase + off, D, 64, 64);
-      load_tile<D>(sV + (st ^ 1) * 64 * D, vbase + off, D, 64, 64);
+    const int st = (pg - pg0) % ST;
+    if (pg + ST - 1 < pg1) {  // refill the buffer that the previous iteration finished with
+      const int into = (pg - pg0 + ST - 1) % ST;
+      const long long off = (long long)pages[pg + ST - 1] * p.page_stride;
+      load_tile<D>(sK + into * 64 * D, kbase + off, D, 64, 64);
+      load_tile<D>(sV + into * 64 * D, vbase + off, D, 64, 64);
     }
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<ST - 1>();  // all but the newest ST - 1 groups: page `pg` has landed
     __syncthreads();
     if (pg == pg0) {
 #pragma unroll
@@ -463,8 +474,9 @@ attn_decode_kernel(const AttnParams p) {
   cp_async_wait<0>();
 
   // merge the four warps' (m, l, O) through shared memory (the page buffers are free now)
-  float* sO = reinterpret_cast<float*>(sK);   // [4][16][D]
-  float* sM = sO + 4 * 16 * D;                // [4][16]
+  constexpr int DP = D + 8;                   // padded row: fewer bank conflicts
+  float* sO = reinterpret_cast<float*>(sK);   // [4][16][DP]
+  float* sM = sO + 4 * 16 * DP;               // [4][16]
   float* sL = sM + 4 * 16;                    // [4][16]
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -472,8 +484,8 @@ attn_decode_kernel(const AttnParams p) {
     if (t == 0) { sM[warp * 16 + row] = m[r]; sL[warp * 16 + row] = l[r]; }
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-      sO[(warp * 16 + row) * D + n * 8 + 2 * t] = o[n][2 * r];
-      sO[(warp * 16 + row) * D + n * 8 + 2 * t + 1] = o[n][2 * r + 1];
+      *reinterpret_cast<float2*>(sO + (warp * 16 + row) * DP + n * 8 + 2 * t) =
+          make_float2(o[n][2 * r], o[n][2 * r + 1]);
     }
   }
   __syncthreads();
@@ -488,7 +500,7 @@ attn_decode_kernel(const AttnParams p) {
       const float mw = sM[w * 16 + row];
       const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
       L += sL[w * 16 + row] * f;
-      acc += sO[(w * 16 + row) * D + d] * f;
+      acc += sO[(w * 16 + row) * DP + d] * f;
     }
     if (p.splits > 1) {
       ws_o[row * D + d] = acc;
@@ -517,8 +529,8 @@ int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
 
 template <int D>
 int launch_decode(const AttnParams& p, cudaStream_t stream) {
-  int bytes = (16 + 4 * 64) * D * 2;
-  const int merge = 4 * 16 * D * 4 + 2 * 4 * 16 * 4 + 16 * D * 2;
+  int bytes = (16 + 2 * DECODE_STAGES * 64) * D * 2;
+  const int merge = 4 * 16 * (D + 8) * 4 + 2 * 4 * 16 * 4 + 16 * D * 2;
   if (merge > bytes) bytes = merge;
   static bool configured = false;
   if (!configured) {

@@ -32,6 +32,7 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
                                      long long page_stride, long long head_stride, int ring_pages,
                                      int A, int Kh, int D, int write_cache) {
   fb_pdl_wait();
+  __shared__ float s_cos[128], s_sin[128];  // rotary_dim / 2 <= 128 (head sizes up to 256)
   const int t = blockIdx.x;
   const int seq = seq_of_token[t];
   if (seq < 0) return;  // padding token
@@ -40,6 +41,12 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
   T* qrow = q_out + (size_t)t * q_stride;
   const int half = rotary_dim >> 1;
   const float fpos = (float)pos;
+  // the angles depend on the position only: computed once, used by every head
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = fpos * inv_freq[i];
+    sincosf(angle, &s_sin[i], &s_cos[i]);
+  }
+  __syncthreads();
   // sums the planes of two elements; the loads of a group of planes are issued together
   auto load2 = [&](int i0, int i1, float& a, float& b) {
     a = 0.f;
@@ -79,9 +86,8 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
        idx += gridDim.y * blockDim.x) {
     if (idx < n_rot) {
       const int h = idx / half, i = idx - h * half;
-      const float angle = fpos * inv_freq[i];
-      float s, c, x1, x2;
-      sincosf(angle, &s, &c);
+      const float s = s_sin[i], c = s_cos[i];
+      float x1, x2;
       load2(h * D + i, h * D + i + half, x1, x2);
       const float y1 = x1 * c - x2 * s;
       const float y2 = x2 * c + x1 * s;
@@ -141,7 +147,9 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   FB_REQUIRE(!write_cache || (k_cache && v_cache && page_table && max_pages > 0),
              "rope_kv_write: cache pointers missing");
   if (T == 0) return 0;
-  FB_REQUIRE(D % 2 == 0, "rope_kv_write: head_dim %d must be even", D);
+  FB_REQUIRE(D % 2 == 0 && rotary_dim <= 256,
+             "rope_kv_write: head_dim %d must be even and the rotary width %d at most 256", D,
+             rotary_dim);
   // few tokens: several blocks per token so that the step's latency is one round trip
   const int work = (A + 2 * Kh) * D / 2;
   int per_token = T >= 256 ? 1 : (work + 255) / 256;

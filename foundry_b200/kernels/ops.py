@@ -482,7 +482,7 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
 
 
-DECODE_CTAS_PER_SM = 3  # what the decode attention kernel's shared memory allows at head size 128
+DECODE_CTAS_PER_SM = 2  # what the decode attention kernel's shared memory allows at head size 128
 
 
 def decode_splits(pairs: int, pages: int) -> int:
