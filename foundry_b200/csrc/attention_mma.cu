@@ -27,7 +27,6 @@
 namespace {
 
 constexpr int THREADS = 128;
-constexpr int DECODE_STAGES = 3;  // page buffers of the decode kernel
 constexpr float LOG2E = 1.4426950408889634f;
 
 // ------------------------------------------------------------- small PTX faces
@@ -326,16 +325,15 @@ __device__ void merge_if_last(const AttnParams& p, int seq, int kvh, int token, 
   if (threadIdx.x == 0) p.counters[seq * p.Kh + kvh] = 0;
 }
 
-template <int D>
+template <int D, int ST>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const AttnParams p) {
   fb_pdl_wait();
   constexpr int KT = D / 16, NT = D / 8;
   extern __shared__ __align__(128) uint8_t smem[];
-  // Three page buffers: two pages are on their way while one is multiplied. A
+  // ST page buffers: ST - 1 pages are on their way while one is multiplied. A
   // CTA's speed is pages in flight / memory latency, and the kernel has nothing
-  // else to hide that latency behind.
-  constexpr int ST = DECODE_STAGES;
+  // else to hide that latency behind; more buffers mean fewer CTAs per SM.
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem);  // [16][D]
   __nv_bfloat16* sK = sQ + 16 * D;                              // [ST][64][D]
   __nv_bfloat16* sV = sK + ST * 64 * D;                         // [ST][64][D]
@@ -527,19 +525,19 @@ int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
   return fb_check_launch("attention_prefill");
 }
 
-template <int D>
+template <int D, int ST>
 int launch_decode(const AttnParams& p, cudaStream_t stream) {
-  int bytes = (16 + 2 * DECODE_STAGES * 64) * D * 2;
+  int bytes = (16 + 2 * ST * 64) * D * 2;
   const int merge = 4 * 16 * (D + 8) * 4 + 2 * 4 * 16 * 4 + 16 * D * 2;
   if (merge > bytes) bytes = merge;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, ST>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
     configured = true;
   }
-  fb_launch(attn_decode_kernel<D>, dim3(p.n_seqs, p.Kh, p.splits), dim3(THREADS), bytes, stream, p);
+  fb_launch(attn_decode_kernel<D, ST>, dim3(p.n_seqs, p.Kh, p.splits), dim3(THREADS), bytes, stream, p);
   return fb_check_launch("attention_decode");
 }
 
@@ -590,14 +588,15 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
 // One token per sequence. `splits` CTAs share each (sequence, kv head); with
 // splits > 1 the workspaces must hold n_seqs*Kh*splits*16*D and
 // n_seqs*Kh*splits*32 floats, and `counters` n_seqs*Kh ints that are zero when
-// the call starts (the kernel leaves them zero again). A sequence with
-// kv_lens == 0 is padding: its output rows are zeros.
+// the call starts (the kernel leaves them zero again). `stages` (2 or 3) is the
+// number of page buffers per CTA. A sequence with kv_lens == 0 is padding: its
+// output rows are zeros.
 FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                const int* cu_tokens, const int* kv_lens, const int* page_table,
                                int max_pages, const void* k_cache, const void* v_cache,
                                long long page_stride, long long head_stride, int n_seqs, int A,
-                               int Kh, int D, float scale, int splits, float* ws_o, float* ws_ml,
-                               int* counters, cudaStream_t stream) {
+                               int Kh, int D, float scale, int splits, int stages, float* ws_o,
+                               float* ws_ml, int* counters, cudaStream_t stream) {
   int rc = check_common("attention_decode", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
                         v_cache, page_stride, head_stride);
   if (rc) return rc;
@@ -612,11 +611,20 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.page_stride = page_stride; p.head_stride = head_stride;
   p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E;
   p.splits = splits; p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
+  FB_REQUIRE(stages == 2 || stages == 3, "attention_decode: %d page buffers (2 or 3)", stages);
+  if (stages == 2) {
+    switch (D) {
+      case 16: return launch_decode<16, 2>(p, stream);
+      case 32: return launch_decode<32, 2>(p, stream);
+      case 64: return launch_decode<64, 2>(p, stream);
+      default: return launch_decode<128, 2>(p, stream);
+    }
+  }
   switch (D) {
-    case 16: return launch_decode<16>(p, stream);
-    case 32: return launch_decode<32>(p, stream);
-    case 64: return launch_decode<64>(p, stream);
-    default: return launch_decode<128>(p, stream);
+    case 16: return launch_decode<16, 3>(p, stream);
+    case 32: return launch_decode<32, 3>(p, stream);
+    case 64: return launch_decode<64, 3>(p, stream);
+    default: return launch_decode<128, 3>(p, stream);
   }
 }
 
@@ -689,5 +697,5 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, ws_o, ws_ml, counters, stream);
+                             D, scale, splits, 3, ws_o, ws_ml, counters, stream);
 }

@@ -176,7 +176,10 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
                        plane_stride % 4 == 0;
   if (aligned && H <= 4 * 4 * 1024) {
     const int groups = H / 4;
-    const int threads = groups <= 128 ? 128 : groups <= 512 ? 256 : groups <= 1024 ? 512 : 1024;
+    // few rows: wide blocks make a row's latency short; many rows: narrower blocks
+    // with more loads in flight per thread keep more rows resident per SM
+    int threads = groups <= 128 ? 128 : groups <= 512 ? 256 : groups <= 1024 ? 512 : 1024;
+    if (T >= 512 && groups <= 1024) threads = groups <= 512 ? 128 : 256;
     const int items = (groups + threads - 1) / threads;
 #define FB_NORM_LAUNCH(N)                                                                     \
     FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (                     \

@@ -158,6 +158,100 @@ struct GemmParams {
   int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs
 };
 
+// Stores CHUNK consecutive accumulator columns (j0 .. j0 + CHUNK) of row
+// i_global, in the layout and with the epilogue the parameters name.
+template <int CHUNK>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v)[CHUNK],
+                                            long long i_global, long long j0, int lane,
+                                            float* out_f, __nv_bfloat16* out_h) {
+  if (p.epilogue == 1) {
+    // Feature rows come in (gate, up) pairs: 2f holds gate f, 2f+1 up f.
+    // out[token, f] = gate / (1 + exp(-gate)) * up, in 32-bit, stored bf16.
+    if (p.stride_b == 1) {
+      // features run along j: pairs sit in this thread's registers
+      if (i_global < p.rows_a) {
+        const long long base = i_global * p.stride_a + (j0 >> 1);
+        if (j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
+#pragma unroll
+          for (int e = 0; e < CHUNK; e += 16) {  // 8 results = 16 bytes per store
+            float r8[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float gate = v[e + 2 * q];
+              r8[q] = gate / (1.0f + __expf(-gate)) * v[e + 2 * q + 1];
+            }
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(r8[0], r8[1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(r8[2], r8[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(r8[4], r8[5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(r8[6], r8[7]);
+            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(out_h + base + (e >> 1)) = pk;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < CHUNK; e += 2) {
+            if (j0 + e + 1 < p.rows_b) {
+              const float gate = v[e];
+              out_h[base + (e >> 1)] =
+                  __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * v[e + 1]);
+            }
+          }
+        }
+      }
+    } else {
+      // features run along i (the lanes): the partner row is the next lane
+#pragma unroll
+      for (int e = 0; e < CHUNK; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[e], 1);
+        if ((lane & 1) == 0 && i_global + 1 < p.rows_a && j0 + e < p.rows_b) {
+          const float gate = v[e];
+          out_h[(i_global >> 1) + (j0 + e) * p.stride_b] =
+              __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * other);
+        }
+      }
+    }
+  } else if (i_global < p.rows_a) {
+    const long long base = i_global * p.stride_a + j0 * p.stride_b;
+    if (p.stride_b == 1 && j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
+      // this thread's elements are contiguous: vector stores
+      if (p.out_f32) {
+#pragma unroll
+        for (int e = 0; e < CHUNK; e += 4)
+          *reinterpret_cast<float4*>(out_f + base + e) =
+              make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < CHUNK; e += 8) {
+          uint4 pk;
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[e], v[e + 1]);
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(v[e + 2], v[e + 3]);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[e + 4], v[e + 5]);
+          __nv_bfloat162 h3 = __floats2bfloat162_rn(v[e + 6], v[e + 7]);
+          pk.x = *reinterpret_cast<uint32_t*>(&h0);
+          pk.y = *reinterpret_cast<uint32_t*>(&h1);
+          pk.z = *reinterpret_cast<uint32_t*>(&h2);
+          pk.w = *reinterpret_cast<uint32_t*>(&h3);
+          *reinterpret_cast<uint4*>(out_h + base + e) = pk;
+        }
+      }
+    } else {
+      // swapped form (stride_a == 1): for each j the warp's lanes are contiguous
+#pragma unroll
+      for (int e = 0; e < CHUNK; ++e) {
+        if (j0 + e < p.rows_b) {
+          const long long idx = base + (long long)e * p.stride_b;
+          if (p.out_f32) out_f[idx] = v[e];
+          else out_h[idx] = __float2bfloat16_rn(v[e]);
+        }
+      }
+    }
+  }
+}
+
 // Dynamic shared memory: [stages][A tile 128x64][B tile BNx64] bf16, 1024-aligned,
 // then the barriers.
 template <int BN>
@@ -307,95 +401,189 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < CHUNK; ++e) v[e] = 0.f;
         }
-        if (p.epilogue == 1) {
-          // Feature rows come in (gate, up) pairs: 2f holds gate f, 2f+1 up f.
-          // out[token, f] = gate / (1 + exp(-gate)) * up, in 32-bit, stored bf16.
-          const long long j0 = (long long)tile_b * BN + c;
-          if (p.stride_b == 1) {
-            // features run along j: pairs sit in this thread's registers
-            if (i_global < p.rows_a) {
-              const long long base = i_global * p.stride_a + (j0 >> 1);
-              if (j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
-#pragma unroll
-                for (int e = 0; e < CHUNK; e += 16) {  // 8 results = 16 bytes per store
-                  float r8[8];
-#pragma unroll
-                  for (int q = 0; q < 8; ++q) {
-                    const float gate = v[e + 2 * q];
-                    r8[q] = gate / (1.0f + __expf(-gate)) * v[e + 2 * q + 1];
-                  }
-                  uint4 pk;
-                  __nv_bfloat162 h0 = __floats2bfloat162_rn(r8[0], r8[1]);
-                  __nv_bfloat162 h1 = __floats2bfloat162_rn(r8[2], r8[3]);
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(r8[4], r8[5]);
-                  __nv_bfloat162 h3 = __floats2bfloat162_rn(r8[6], r8[7]);
-                  pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                  pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                  pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                  pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                  *reinterpret_cast<uint4*>(out_h + base + (e >> 1)) = pk;
-                }
-              } else {
-#pragma unroll
-                for (int e = 0; e < CHUNK; e += 2) {
-                  if (j0 + e + 1 < p.rows_b) {
-                    const float gate = v[e];
-                    out_h[base + (e >> 1)] =
-                        __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * v[e + 1]);
-                  }
-                }
-              }
-            }
-          } else {
-            // features run along i (the lanes): the partner row is the next lane
-#pragma unroll
-            for (int e = 0; e < CHUNK; ++e) {
-              const float other = __shfl_xor_sync(0xffffffffu, v[e], 1);
-              if ((lane & 1) == 0 && i_global + 1 < p.rows_a && j0 + e < p.rows_b) {
-                const float gate = v[e];
-                out_h[(i_global >> 1) + (j0 + e) * p.stride_b] =
-                    __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * other);
-              }
-            }
-          }
-        } else if (i_global < p.rows_a) {
-          const long long j0 = (long long)tile_b * BN + c;
-          const long long base = i_global * p.stride_a + j0 * p.stride_b;
-          if (p.stride_b == 1 && j0 + CHUNK <= p.rows_b && (base % 8) == 0) {
-            // this thread's elements are contiguous: vector stores
-            if (p.out_f32) {
-#pragma unroll
-              for (int e = 0; e < CHUNK; e += 4)
-                *reinterpret_cast<float4*>(out_f + base + e) =
-                    make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-            } else {
-#pragma unroll
-              for (int e = 0; e < CHUNK; e += 8) {
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[e], v[e + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[e + 2], v[e + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[e + 4], v[e + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[e + 6], v[e + 7]);
-                pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(out_h + base + e) = pk;
-              }
-            }
-          } else {
-            // swapped form (stride_a == 1): for each j the warp's lanes are contiguous
-#pragma unroll
-            for (int e = 0; e < CHUNK; ++e) {
-              if (j0 + e < p.rows_b) {
-                const long long idx = base + (long long)e * p.stride_b;
-                if (p.out_f32) out_f[idx] = v[e];
-                else out_h[idx] = __float2bfloat16_rn(v[e]);
-              }
-            }
-          }
-        }
+        store_chunk<CHUNK>(p, v, i_global, (long long)tile_b * BN + c, lane, out_f, out_h);
       }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ persistent
+// The same product for many token rows, as one CTA per SM that walks over
+// tiles (tile index = blockIdx.x, += gridDim.x; the A tile index runs fastest,
+// so the CTAs of a wave share weight tiles in L2). Two accumulators live in
+// tensor memory: while the epilogue warps read tile j out of one, the MMA warp
+// already fills the other with tile j + 1, and the TMA warp runs ahead of both
+// through the ring of shared-memory stages, across tile boundaries.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                          const __grid_constant__ CUtensorMap map_b, const GemmParams p,
+                          int tiles_a, int tiles_b) {
+  constexpr int STAGES = Smem<BN>::STAGES;
+  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * Smem<BN>::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = tiles_a * tiles_b;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;  // stage uses so far, across tiles
+      bool ok = true;
+      // the first tile's first stages: constants at once, the rest after the wait
+      const int first = (int)blockIdx.x;
+      const int early = (first < total_tiles) ? (nkb < STAGES ? nkb : STAGES) : 0;
+      const int fa = first % tiles_a, fb = first / tiles_a;
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a_dst = tiles + i * Smem<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+        mbar_expect_tx(&full[i], Smem<BN>::STAGE_BYTES);
+        if (p.constant_operand == 1) tma_load_2d(a_dst, &map_a, &full[i], i * BK, fa * BM);
+        if (p.constant_operand == 2) tma_load_2d(b_dst, &map_b, &full[i], i * BK, fb * BN);
+      }
+      fb_pdl_wait();
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a_dst = tiles + i * Smem<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+        if (p.constant_operand != 1) tma_load_2d(a_dst, &map_a, &full[i], i * BK, fa * BM);
+        if (p.constant_operand != 2) tma_load_2d(b_dst, &map_b, &full[i], i * BK, fb * BN);
+      }
+      for (int tile = first; tile < total_tiles && ok; tile += gridDim.x) {
+        const int ta = tile % tiles_a, tb = tile / tiles_a;
+        for (int kb = (tile == first ? early : 0); kb < nkb; ++kb) {
+          const int use = it + kb;
+          const int s = use % STAGES;
+          const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, kb)) { ok = false; break; }
+          uint8_t* a_dst = tiles + s * Smem<BN>::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + Smem<BN>::A_BYTES;
+          mbar_expect_tx(&full[s], Smem<BN>::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &full[s], kb * BK, ta * BM);
+          tma_load_2d(b_dst, &map_b, &full[s], kb * BK, tb * BN);
+        }
+        it += nkb;
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+        const int buf = j & 1;
+        // the epilogue must have emptied this accumulator (free at its first two uses)
+        ok = mbar_wait(&acc_empty[buf], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 4, j);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          const int use = it + kb;
+          const int s = use % STAGES;
+          const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
+          ok = mbar_wait(&full[s], phase, abort_flag, 2, kb);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * Smem<BN>::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + Smem<BN>::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma(d_tmem, make_desc(a_addr + k * UMMA_K * 2), make_desc(b_addr + k * UMMA_K * 2),
+                 idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(&empty[s]);
+        }
+        if (!ok) break;
+        tc_commit(&acc_full[buf]);
+        it += nkb;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    float* out_f = (float*)p.out;
+    __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
+    constexpr int CHUNK = BN < 32 ? 16 : 32;
+    fb_pdl_wait();
+    int j = 0;
+    bool ok = true;
+    for (int tile = (int)blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+      const int ta = tile % tiles_a, tb = tile / tiles_a;
+      const int buf = j & 1;
+      ok = mbar_wait(&acc_full[buf], (uint32_t)((j >> 1) & 1), abort_flag, 3, j);
+      if (!ok) break;
+      tc_fence_after();
+      const long long i_global = (long long)ta * BM + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CHUNK) {
+        float v[CHUNK];
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c);
+        if constexpr (CHUNK == 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+        } else {
+          uint32_t r[16];
+          tmem_ld16(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+        }
+        store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+      }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   // ------------------------------------------------------------------ teardown
@@ -492,6 +680,35 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
   return fb_check_launch("gemm_tc");
 }
 
+int sm_count() {
+  static int count = 0;
+  if (count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+template <int BN>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+                      int tiles_a, int tiles_b, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem<BN>::BYTES);
+    if (e != cudaSuccess) return fb_fail(2, "gemm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int total = tiles_a * tiles_b;
+  const int ctas = total < sm_count() ? total : sm_count();
+  fb_launch(gemm_tc_persistent_kernel<BN>, dim3(ctas), dim3(THREADS), Smem<BN>::BYTES, stream, ma,
+            mb, p, tiles_a, tiles_b);
+  return fb_check_launch("gemm_tc_persistent");
+}
+
 }  // namespace
 
 // out = A * B^T in the layout the strides give; see the file header.
@@ -502,13 +719,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 // that the caller sums.
 // constant_operand names the operand (1: a, 2: b, 0: none) that no earlier kernel
 // in the stream writes (weights); its first loads do not wait for that kernel.
+// persistent 1 runs one CTA per SM over all tiles with two accumulators in
+// tensor memory (for many token rows; one split).
 // epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
 // pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
 // dimension must be 1 and then indexes pairs.
 FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, long long ldb,
                       int rows_b, int K, void* out, long long stride_a, long long stride_b,
                       int out_f32, int bn, int splits, long long split_stride, int epilogue,
-                      int constant_operand, cudaStream_t stream) {
+                      int constant_operand, int persistent, cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, K);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
              "gemm_tc: K and the row strides must be multiples of 8 elements (16 bytes), got K=%d "
@@ -535,6 +754,15 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   if (rc) return rc;
   dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
   FB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
+  if (persistent) {
+    FB_REQUIRE(splits == 1 && (bn == 64 || bn == 128 || bn == 256),
+               "gemm_tc: the persistent form takes one split and tiles 64, 128 or 256 wide");
+    switch (bn) {
+      case 64: return launch_persistent<64>(ma, mb, p, grid.x, grid.y, stream);
+      case 128: return launch_persistent<128>(ma, mb, p, grid.x, grid.y, stream);
+      default: return launch_persistent<256>(ma, mb, p, grid.x, grid.y, stream);
+    }
+  }
   switch (bn) {
     case 16: return launch<16>(ma, mb, p, grid, stream);
     case 32: return launch<32>(ma, mb, p, grid, stream);

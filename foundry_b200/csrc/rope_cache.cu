@@ -126,6 +126,72 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
   }
 }
 
+// The common prompt case, vectorised: bfloat16 source rotated in place, no
+// planes, rotary width == head size, head size a multiple of 16. A thread moves
+// 8 consecutive elements of the first half and the 8 they pair with (16 bytes
+// each way), or 16 consecutive value elements.
+__global__ void rope_kv_write_bf16_kernel(__nv_bfloat16* __restrict__ qkv, long long stride,
+                                          const int* __restrict__ positions,
+                                          const int* __restrict__ seq_of_token,
+                                          const int* __restrict__ page_table, int max_pages,
+                                          const float* __restrict__ inv_freq,
+                                          __nv_bfloat16* __restrict__ k_cache,
+                                          __nv_bfloat16* __restrict__ v_cache,
+                                          long long page_stride, long long head_stride,
+                                          int ring_pages, int A, int Kh, int D, int write_cache) {
+  __shared__ float s_cos[128], s_sin[128];
+  fb_pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  if (seq < 0) return;
+  const int pos = positions[t];
+  const int half = D >> 1;
+  const float fpos = (float)pos;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(fpos * inv_freq[i], &s_sin[i], &s_cos[i]);
+  __syncthreads();
+  __nv_bfloat16* row = qkv + (size_t)t * stride;
+  long long cache_row = 0;
+  if (write_cache) {
+    int lp = pos / FB_PAGE;
+    if (ring_pages > 0) lp %= ring_pages;
+    const int page = page_table[(size_t)seq * max_pages + lp];
+    cache_row = (long long)page * page_stride + (long long)(pos % FB_PAGE) * D;
+  }
+  const int groups = half / 8;                       // 8-element groups per half head
+  const int n_rot = (A + (write_cache ? Kh : 0)) * groups;
+  const int n_val = write_cache ? Kh * (D / 8) : 0;  // 8-element groups of the value heads
+  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n_rot + n_val;
+       idx += gridDim.y * blockDim.x) {
+    if (idx < n_rot) {
+      const int h = idx / groups, i0 = (idx - h * groups) * 8;
+      __nv_bfloat16* x = row + (size_t)h * D + i0;
+      const uint4 lo = *reinterpret_cast<const uint4*>(x);
+      const uint4 hi = *reinterpret_cast<const uint4*>(x + half);
+      const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+      uint4 olo, ohi;
+      __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&olo);
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ohi);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = __bfloat1622float2(l2[e]), b = __bfloat1622float2(h2[e]);
+        const float c0 = s_cos[i0 + 2 * e], s0 = s_sin[i0 + 2 * e];
+        const float c1 = s_cos[i0 + 2 * e + 1], s1 = s_sin[i0 + 2 * e + 1];
+        ol[e] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+        oh[e] = __floats2bfloat162_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+      }
+      __nv_bfloat16* dst = h < A ? x : k_cache + cache_row + (long long)(h - A) * head_stride + i0;
+      *reinterpret_cast<uint4*>(dst) = olo;
+      *reinterpret_cast<uint4*>(dst + half) = ohi;
+    } else {
+      const int j = idx - n_rot;
+      const int h = j / (D / 8), i0 = (j - h * (D / 8)) * 8;
+      *reinterpret_cast<uint4*>(v_cache + cache_row + (long long)h * head_stride + i0) =
+          *reinterpret_cast<const uint4*>(row + (size_t)(A + Kh + h) * D + i0);
+    }
+  }
+}
+
 // src_dtype / planes: see the kernel. dtype is the element type of q_out and the cache.
 FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride, int planes,
                             long long plane_stride, void* q_out, int dtype, long long q_stride,
@@ -155,6 +221,19 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   int per_token = T >= 256 ? 1 : (work + 255) / 256;
   if (per_token > 16) per_token = 16;
   dim3 grid(T, per_token);
+  if (dtype == FB_BF16 && src_dtype == FB_BF16 && planes == 1 && src == q_out &&
+      rotary_dim == D && D % 16 == 0 && src_stride % 8 == 0 && ((uintptr_t)src % 16) == 0 &&
+      page_stride % 8 == 0 && head_stride % 8 == 0 && ((uintptr_t)k_cache % 16) == 0 &&
+      ((uintptr_t)v_cache % 16) == 0) {
+    const int vec_work = (A + 2 * Kh) * D / 16;
+    int blocks_y = T >= 256 ? 1 : (vec_work + 127) / 128;
+    if (blocks_y > 16) blocks_y = 16;
+    fb_launch(rope_kv_write_bf16_kernel, dim3(T, blocks_y), dim3(128), 0, stream,
+              (__nv_bfloat16*)q_out, src_stride, positions, seq_of_token, page_table, max_pages,
+              inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_stride,
+              head_stride, ring_pages, A, Kh, D, write_cache);
+    return fb_check_launch("rope_kv_write");
+  }
 #define FB_ROPE_LAUNCH(TS, TT)                                                                  \
   fb_launch(rope_kv_write_kernel<TS, TT>, dim3(grid), dim3(128), 0, stream,                                        \
       (const TS*)src, src_stride, planes, plane_stride, (TT*)q_out, q_stride, positions,        \

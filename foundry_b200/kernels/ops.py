@@ -10,6 +10,8 @@ from __future__ import annotations
 import ctypes
 from typing import Optional
 
+import os as _os
+
 import torch
 
 from . import library
@@ -39,7 +41,7 @@ _SIGNATURES = {
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
-                   c_int, c_int, c_ll, c_int, c_int, c_void_p],
+                   c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                        c_int, c_void_p],
@@ -48,7 +50,7 @@ _SIGNATURES = {
                              c_float, c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
 }
@@ -290,11 +292,13 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
 
 
 SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
+# many token rows: one CTA per SM walks the tiles, two accumulators in tensor memory
+PERSISTENT = _os.environ.get("FOUNDRY_B200_PERSISTENT", "1") != "0"
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
             bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0,
-            constant_operand: int = 0) -> None:
+            constant_operand: int = 0, persistent: bool = False) -> None:
     """Tensor-core product D[i,j] = sum_k a[i,k] b[j,k] written to
     out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu."""
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
@@ -305,7 +309,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
-          constant_operand, _stream())
+          constant_operand, 1 if persistent else 0, _stream())
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
@@ -323,8 +327,6 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
           _rows(out, "out"), 1 if out.dtype == torch.float32 else 0, M, N, K, epilogue, _stream())
     return out
 
-
-import os as _os
 
 # token rows up to which the weight-streaming kernel is used
 SKINNY_ROWS = int(_os.environ.get("FOUNDRY_B200_SKINNY_ROWS", "16"))
@@ -410,7 +412,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         bn = 256 if N >= 256 else (128 if N > 64 else 64)
-        gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2)
+        gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=PERSISTENT)
         return out
     bn, splits = _swapped_plan(M, N, K)
     if splits == 1:
@@ -450,7 +452,8 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         return gemm_skinny(x, w_pairs, out, epilogue=1)
     if M > 128:
         bn = 256 if two_i >= 256 else (128 if two_i > 64 else 64)
-        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2)
+        gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2,
+                persistent=PERSISTENT)
     else:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         gemm_tc(w_pairs, x, out, 1, out.stride(0), bn, epilogue=1, constant_operand=1)
@@ -473,31 +476,28 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
         return attention_simt(q, out, ctx.positions, ctx.seq_of_token, page_table, k_cache,
                               v_cache, num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
     if ctx.is_decode:
-        splits = decode_splits(ctx.n_seqs * num_kv_heads, (ctx.max_kv_len + PAGE - 1) // PAGE)
+        splits, stages = decode_plan(ctx.n_seqs * num_kv_heads,
+                                     (ctx.max_kv_len + PAGE - 1) // PAGE)
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
-                                num_heads, num_kv_heads, head_dim, scale, splits)
+                                num_heads, num_kv_heads, head_dim, scale, splits, stages)
     blocks = sum((ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] + 63) // 64
                  for i in range(ctx.n_seqs))
     return attention_prefill(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
 
 
-DECODE_CTAS_PER_SM = 2  # what the decode attention kernel's shared memory allows at head size 128
-
-
-def decode_splits(pairs: int, pages: int) -> int:
-    """How many CTAs share one (sequence, kv head) in decode attention: the
-    count that minimises waves x (pages per CTA + a fixed cost of about two
-    pages), a wave being the CTAs the chip holds at once."""
-    slots = SM_COUNT * DECODE_CTAS_PER_SM
-    pages = max(1, pages)
-    best, best_cost = 1, None
-    for s in range(1, min(pages, 64) + 1):
-        waves = (pairs * s + slots - 1) // slots
-        cost = waves * ((pages + s - 1) // s + 2)
-        if best_cost is None or cost < best_cost:
-            best, best_cost = s, cost
-    return best
+def decode_plan(pairs: int, pages: int):
+    """(splits, page buffers) of decode attention for `pairs` (sequence, kv head)
+    pairs of up to `pages` cache pages, as measured on B200 with head size 128
+    at 3,072 tokens of context: with two or more pairs per SM, whole ranges
+    and three page buffers per CTA (two CTAs per SM) stream at the memory's
+    rate; with fewer pairs the ranges are split until about 256 CTAs exist,
+    at most eightfold (every further split adds merge work), with two page
+    buffers so that three CTAs fit an SM."""
+    if pairs >= 2 * SM_COUNT:
+        return 1, 3
+    splits = max(1, min(8, pages, (256 + pairs // 2) // pairs))
+    return splits, 2
 
 
 def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
@@ -515,7 +515,7 @@ def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, 
 
 
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
-                     num_kv_heads, head_dim, scale, splits) -> torch.Tensor:
+                     num_kv_heads, head_dim, scale, splits, stages: int = 3) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
     over `splits` CTAs per (sequence, kv head); the CTA that finishes a pair
     last merges its partial results."""
@@ -532,7 +532,7 @@ def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, n
           _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
-          head_dim, float(scale), splits, 0 if ws_o is None else ws_o.data_ptr(),
+          head_dim, float(scale), splits, stages, 0 if ws_o is None else ws_o.data_ptr(),
           0 if ws_ml is None else ws_ml.data_ptr(),
           0 if counters is None else counters.data_ptr(), _stream())
     return out

@@ -271,11 +271,12 @@ def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, sp
     cu = torch.cat([case["cu"], case["cu"][-1:] + 1])
     q = torch.cat([case["q"], rnd(1, A * D, dtype=torch.bfloat16)])
     table = torch.cat([case["table"], torch.zeros_like(case["table"][:1])])
-    out = torch.full_like(q, 5.0)
-    ops.attention_decode(q, out, cu, kv, table, case["k"], case["v"], A, Kh, D,
-                         1.0 / math.sqrt(D), splits)
-    close(out[:-1], want, 3e-2, 1e-2)
-    assert float(out[-1].abs().max()) == 0.0
+    for stages in (2, 3):
+        out = torch.full_like(q, 5.0)
+        ops.attention_decode(q, out, cu, kv, table, case["k"], case["v"], A, Kh, D,
+                             1.0 / math.sqrt(D), splits, stages)
+        close(out[:-1], want, 3e-2, 1e-2)
+        assert float(out[-1].abs().max()) == 0.0
 
 
 def test_attention_picks_out_a_far_key(ops):
@@ -474,3 +475,22 @@ def test_gemm_skinny(ops, M, N, K):
     ops.gemm_skinny(wide_x[:, 8:8 + K], w, wide_out[:, :N])
     close(wide_out[:, :N], wide_x[:, 8:8 + K].double() @ w.double().T, 2e-4 * math.sqrt(K) + 1e-2, 8e-3)
     assert float(wide_out[:, N:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("rows_a,rows_b,K", [(300, 700, 264), (2048, 1024, 512), (130, 70, 64),
+                                              (1000, 5000, 72)])
+def test_gemm_tensor_core_persistent(ops, bn, rows_a, rows_b, K):
+    """One CTA per SM over many tiles, alternating accumulators: more tiles than
+    SMs, fewer tiles than SMs, ragged edges, short and long K loops; with and
+    without the SiLU-mul epilogue."""
+    a, b = rnd(rows_a, K, dtype=torch.bfloat16, scale=0.5), rnd(rows_b, K, dtype=torch.bfloat16, scale=0.5, seed=6)
+    want = a.double() @ b.double().T
+    out = torch.full((rows_a, rows_b), 3.0, device=DEV)
+    ops.gemm_tc(a, b, out, rows_b, 1, bn, persistent=True, constant_operand=2)
+    close(out, want, 2e-4 * math.sqrt(K), 1e-5)
+    act = torch.full((rows_a, rows_b // 2), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(a, b, act, rows_b // 2, 1, bn, epilogue=1, persistent=True, constant_operand=2)
+    g, u = want[:, 0::2], want[:, 1::2]
+    close(act, g / (1 + torch.exp(-g)) * u, 3e-2, 1e-2)
+    assert ops.gemm_tc_status() == 0
