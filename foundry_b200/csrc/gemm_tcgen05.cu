@@ -378,7 +378,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (ok) {
       float* out_f = (float*)p.out + (long long)split * p.split_stride;
       __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
-      constexpr int CHUNK = BN < 32 ? 16 : 32;
+      constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
 #pragma unroll 1
       for (int c = 0; c < BN; c += CHUNK) {
         float v[CHUNK];
@@ -433,7 +433,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_b, const GemmParams p,
                           int tiles_a, int tiles_b) {
   constexpr int STAGES = Smem<BN>::STAGES;
-  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(tiles + STAGES * Smem<BN>::STAGE_BYTES);
@@ -549,7 +549,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     const int quarter = warp & 3;
     float* out_f = (float*)p.out;
     __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
-    constexpr int CHUNK = BN < 32 ? 16 : 32;
+    constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
     fb_pdl_wait();
     int j = 0;
     bool ok = true;
@@ -755,12 +755,21 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
   FB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
   if (persistent) {
-    FB_REQUIRE(splits == 1 && (bn == 64 || bn == 128 || bn == 256),
-               "gemm_tc: the persistent form takes one split and tiles 64, 128 or 256 wide");
+    FB_REQUIRE(splits == 1, "gemm_tc: the persistent form takes one split");
     switch (bn) {
       case 64: return launch_persistent<64>(ma, mb, p, grid.x, grid.y, stream);
       case 128: return launch_persistent<128>(ma, mb, p, grid.x, grid.y, stream);
-      default: return launch_persistent<256>(ma, mb, p, grid.x, grid.y, stream);
+      case 144: return launch_persistent<144>(ma, mb, p, grid.x, grid.y, stream);
+      case 160: return launch_persistent<160>(ma, mb, p, grid.x, grid.y, stream);
+      case 176: return launch_persistent<176>(ma, mb, p, grid.x, grid.y, stream);
+      case 192: return launch_persistent<192>(ma, mb, p, grid.x, grid.y, stream);
+      case 208: return launch_persistent<208>(ma, mb, p, grid.x, grid.y, stream);
+      case 224: return launch_persistent<224>(ma, mb, p, grid.x, grid.y, stream);
+      case 240: return launch_persistent<240>(ma, mb, p, grid.x, grid.y, stream);
+      case 256: return launch_persistent<256>(ma, mb, p, grid.x, grid.y, stream);
+      default:
+        return fb_fail(1, "gemm_tc: the persistent form takes tiles 64 or 128..256 (steps of 16) "
+                          "wide, not %d", bn);
     }
   }
   switch (bn) {

@@ -380,6 +380,24 @@ def _swapped_plan(M: int, N: int, K: int):
     return bn, (kblocks + per - 1) // per  # no empty split
 
 
+def prompt_tile_width(M: int, N: int) -> int:
+    """Tile width (the weights' side) for many token rows: the width whose tile
+    count wastes least of the last round over the SMs (rounds x width is the
+    time in units of one 128 x 1 column strip); wider on ties."""
+    if N < 128:
+        return 64
+    if not PERSISTENT:
+        return 256 if N >= 256 else 128
+    tiles_a = (M + 127) // 128
+    best, best_cost = 256, None
+    for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
+        rounds = (tiles_a * ((N + bn - 1) // bn) + SM_COUNT - 1) // SM_COUNT
+        cost = rounds * (bn + 8)  # + a fixed cost per tile
+        if best_cost is None or cost < best_cost:
+            best, best_cost = bn, cost
+    return best
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
               out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
     """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
@@ -411,7 +429,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if M > 128:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        bn = 256 if N >= 256 else (128 if N > 64 else 64)
+        bn = prompt_tile_width(M, N)
         gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=PERSISTENT)
         return out
     bn, splits = _swapped_plan(M, N, K)
@@ -451,7 +469,7 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
     if M <= SKINNY_ROWS:
         return gemm_skinny(x, w_pairs, out, epilogue=1)
     if M > 128:
-        bn = 256 if two_i >= 256 else (128 if two_i > 64 else 64)
+        bn = prompt_tile_width(M, two_i)
         gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2,
                 persistent=PERSISTENT)
     else:

@@ -477,7 +477,7 @@ def test_gemm_skinny(ops, M, N, K):
     assert float(wide_out[:, N:].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("bn", [64, 128, 144, 176, 192, 208, 240, 256])
 @pytest.mark.parametrize("rows_a,rows_b,K", [(300, 700, 264), (2048, 1024, 512), (130, 70, 64),
                                               (1000, 5000, 72)])
 def test_gemm_tensor_core_persistent(ops, bn, rows_a, rows_b, K):
