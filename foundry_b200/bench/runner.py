@@ -18,6 +18,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..engine.context import SequenceStep
+from ..kernels import ops
 from ..sampling import SamplingParams
 from .rng import SplitMix64, token_rows
 from .stats import summarize
@@ -34,6 +35,7 @@ class BenchConfig:
     runs: int = 10
     batch_size: int = 1
     seed: int = 0
+    profile: Optional[str] = None  # "steps" | "kernels" (src/nn/profile.rs:7-13)
 
     def decode_step_count(self) -> int:
         # src/bench/mod.rs:72-77
@@ -51,6 +53,8 @@ def _one_run(engine, cfg: BenchConfig, depth_ids, prompt_ids, start_ids) -> Dict
             torch.cuda.synchronize()
 
         def timed(steps):
+            if cfg.profile:
+                ops.PROFILER.take()
             started = time.perf_counter_ns()
             logits = engine.step(steps)
             if cfg.timing_scope == "forward":
@@ -68,6 +72,8 @@ def _one_run(engine, cfg: BenchConfig, depth_ids, prompt_ids, start_ids) -> Dict
                                 for s, ids in zip(slots, prompt_ids)])
             sample["prompt_step_ns"] = ns
             sample["first_token_ns"] = time.perf_counter_ns() - run_started
+            if cfg.profile:
+                sample["prompt_profile"] = ops.PROFILER.take()
             for row, t in zip(sample["token_ids"], tokens):
                 row.append(t)
         else:
@@ -75,6 +81,8 @@ def _one_run(engine, cfg: BenchConfig, depth_ids, prompt_ids, start_ids) -> Dict
         for _ in range(cfg.decode_step_count()):
             tokens, ns = timed([SequenceStep(s, [t], [0]) for s, t in zip(slots, tokens)])
             sample["decode_step_ns"].append(ns)
+            if cfg.profile:
+                sample.setdefault("decode_profiles", []).append(ops.PROFILER.take())
             for row, t in zip(sample["token_ids"], tokens):
                 row.append(t)
         sample["generation_ns"] = time.perf_counter_ns() - run_started
@@ -88,6 +96,9 @@ def run_bench(engine, cfg: BenchConfig) -> Dict:
     if cfg.prompt_tokens == 0 and cfg.new_tokens == 0:
         raise ValueError("nothing to measure: prompt_tokens and new_tokens are both 0")
     vocab = engine.spec.vocab_size
+    ops.PROFILER.start(cfg.profile)
+    if cfg.profile == "kernels":
+        engine.use_graphs = False  # per-kernel times need one launch at a time
     rng = SplitMix64(cfg.seed)
     depth_ids = token_rows(rng, cfg.batch_size, cfg.depth, vocab)
     prompt_ids = token_rows(rng, cfg.batch_size, cfg.prompt_tokens, vocab)
@@ -109,6 +120,24 @@ def run_bench(engine, cfg: BenchConfig) -> Dict:
         s = summarize(values)
         return None if s is None else s.to_json()
 
+    ops.PROFILER.start(None)
+    decode_profiles = [p for r in runs for p in r.get("decode_profiles", [])]
+
+    def per_step(field):
+        return [sum(k.get(field, 0) for k in p["kernels"].values()) for p in decode_profiles]
+
+    profile_metrics = {}
+    if decode_profiles:
+        profile_metrics = {
+            "decode_dispatch_count": js(per_step("dispatch_count")),
+            "decode_allocation_count": js([p["allocation_count"] for p in decode_profiles]),
+            "decode_allocated_bytes": js([p["allocated_bytes"] for p in decode_profiles]),
+        }
+        if cfg.profile == "kernels":
+            profile_metrics["decode_gpu_busy_ns"] = js([p["gpu_busy_ns"] for p in decode_profiles])
+    # what a decode step has to read, and the share of the memory's rate it reached
+    step_bytes = engine.model.weight_bytes_read_per_step() + engine.cache.bytes_per_token() * \
+        cfg.batch_size * (cfg.depth + cfg.prompt_tokens + cfg.decode_step_count() / 2.0)
     return {
         "config": asdict(cfg),
         "depth_ids": depth_ids, "prompt_ids": prompt_ids, "start_ids": start_ids,
@@ -121,6 +150,12 @@ def run_bench(engine, cfg: BenchConfig) -> Dict:
             "prompt_tokens_per_s": js(prompt_rates),
             "decode_tokens_per_s": js(decode_rates),
             "output_tokens_per_s": js(output_rates),
+            **profile_metrics,
+        },
+        "decode_step_model": {
+            "bytes_read": step_bytes,
+            "achieved_gb_per_s": (step_bytes / (summarize([ns for r in runs for ns in r["decode_step_ns"]]).mean)
+                                  if any(r["decode_step_ns"] for r in runs) else None),
         },
         "peak_memory_bytes": torch.cuda.max_memory_allocated(),
         "peak_memory_source": "torch.cuda.max_memory_allocated",

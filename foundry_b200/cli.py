@@ -70,6 +70,10 @@ def build_parser() -> argparse.ArgumentParser:
                        help="Sequences generated together, each with its own random prompt of "
                             "the same length.")
     bench.add_argument("--seed", type=int, default=0, help="Seed of the random token IDs.")
+    bench.add_argument("--profile", choices=["steps", "kernels"], default=None,
+                       help="Record device dispatches, allocations and GPU busy time per step; "
+                            "steps keeps execution unchanged, kernels also times each kernel with "
+                            "one launch at a time (no graph replay), which slows wall times.")
     bench.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     bench.add_argument("--out", required=True, help="Directory that receives report.json.")
     return parser
@@ -127,7 +131,8 @@ def cmd_bench(args) -> int:
     from .engine import Engine
     from .weights import WeightFiles
     cfg = BenchConfig(args.prompt_tokens, args.new_tokens, args.timing_scope, args.depth,
-                      args.warmup_runs, args.warmup_ms, args.runs, args.batch_size, args.seed)
+                      args.warmup_runs, args.warmup_ms, args.runs, args.batch_size, args.seed,
+                      args.profile)
     per_seq = cfg.depth + cfg.prompt_tokens + cfg.decode_step_count()  # command.rs:152-169
     engine = Engine.from_folder(args.model, dtype=args.dtype,
                                 max_tokens=max(PAGE, pages_for(per_seq) * PAGE * cfg.batch_size),

@@ -75,6 +75,7 @@ class DecodeRunner:
         self.tokens_host = torch.zeros(b, dtype=torch.int32).pin_memory()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
+        self.kernel_histogram: Dict[str, int] = {}
         self.logits: Optional[torch.Tensor] = None
 
     def _body(self) -> None:
@@ -95,8 +96,12 @@ class DecodeRunner:
             # allocator and IS this call's step); then the same work is captured
             # for every later call. Capturing executes nothing.
             before = ops.launch_count()
+            counted = ops.PROFILER.snapshot_counts()
             self._body()
             self.kernels_per_step = ops.launch_count() - before
+            after = ops.PROFILER.snapshot_counts()
+            self.kernel_histogram = {k: n - counted.get(k, 0) for k, n in after.items()
+                                     if n != counted.get(k, 0)}
             plain_logits = self.logits
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -107,6 +112,8 @@ class DecodeRunner:
                                   capture_error_mode="relaxed"):
                 self._body()
             ops.add_launches(-self.kernels_per_step)  # recorded, not launched
+            if ops.PROFILER.mode is not None:
+                ops.PROFILER.add_counts({k: -n for k, n in self.kernel_histogram.items()})
             self.graph = graph
             # `self.logits` is now the graph's own buffer, which replays fill;
             # this call's logits are the plain run's
@@ -114,6 +121,8 @@ class DecodeRunner:
             return
         self.graph.replay()
         ops.add_launches(self.kernels_per_step)
+        if ops.PROFILER.mode is not None:
+            ops.PROFILER.add_counts(self.kernel_histogram)
 
 
 class DecodeSession:

@@ -79,6 +79,57 @@ def _fn(name: str):
 _COUNT = [0]
 
 
+class Profiler:
+    """Dispatch counts, and in `kernels` mode GPU time, per kernel: the
+    reference's `DeviceProfile` (src/nn/profile.rs:15-28). `steps` mode only
+    counts and leaves execution unchanged; `kernels` mode brackets every launch
+    with CUDA events, so it needs plain launches (no graph replay) and perturbs
+    wall times. Product kernels are keyed with their shape, as the reference
+    keys its matmul (src/metal/args.rs:196-204)."""
+
+    def __init__(self):
+        self.mode = None
+        self._counts = {}
+        self._events = []
+        self._alloc0 = None
+
+    def start(self, mode) -> None:
+        if mode not in (None, "steps", "kernels"):
+            raise ValueError(f"profile mode {mode!r}: choose steps or kernels")
+        self.mode = mode
+        self.take()
+
+    def count(self, key: str, times: int = 1) -> None:
+        self._counts[key] = self._counts.get(key, 0) + times
+
+    def snapshot_counts(self):
+        return dict(self._counts)
+
+    def add_counts(self, counts) -> None:
+        for key, n in counts.items():
+            self.count(key, n)
+
+    def take(self) -> dict:
+        """The profile since the last `take`, and a fresh start."""
+        kernels = {k: {"dispatch_count": n} for k, n in sorted(self._counts.items())}
+        if self._events:
+            torch.cuda.synchronize()
+            for key, a, b in self._events:
+                entry = kernels.setdefault(key, {"dispatch_count": 0})
+                entry["gpu_ns"] = entry.get("gpu_ns", 0.0) + a.elapsed_time(b) * 1e6
+        stats = torch.cuda.memory_stats() if torch.cuda.is_available() else {}
+        now = (stats.get("allocation.all.allocated", 0), stats.get("allocated_bytes.all.allocated", 0))
+        before = self._alloc0 or now
+        self._alloc0 = now
+        self._counts, self._events = {}, []
+        busy = sum(k["gpu_ns"] for k in kernels.values() if "gpu_ns" in k) if self.mode == "kernels" else None
+        return {"kernels": kernels, "allocation_count": now[0] - before[0],
+                "allocated_bytes": now[1] - before[1], "gpu_busy_ns": busy}
+
+
+PROFILER = Profiler()
+
+
 def launch_count() -> int:
     """Kernels of this library launched so far (graph replays included)."""
     return _COUNT[0]
@@ -91,8 +142,22 @@ def add_launches(n: int) -> None:
 add_graph_launches = add_launches
 
 
-def _call(name: str, *args) -> None:
+def _call(name: str, *args, tag: str = "") -> None:
     _COUNT[0] += 1
+    prof = PROFILER
+    if prof.mode is not None:
+        key = name[3:] + (" " + tag if tag else "")
+        prof.count(key)
+        if prof.mode == "kernels" and not torch.cuda.is_current_stream_capturing():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            code = _fn(name)(*args)
+            b.record()
+            prof._events.append((key, a, b))
+            if code != 0:
+                message = library.load().fb_last_error().decode(errors="replace")
+                raise KernelError(f"{name}: {message}")
+            return
     code = _fn(name)(*args)
     if code != 0:
         message = library.load().fb_last_error().decode(errors="replace")
@@ -287,7 +352,8 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
                           f"out {tuple(out.shape)}")
     _call("fb_gemm_simt", _dev(x, "x", contiguous=False), _dev(w, "w", contiguous=False),
           _dev(out, "out", contiguous=False), M, N, K, _rows(x, "x"), _rows(w, "w"),
-          _rows(out, "out"), code_of(x.dtype), code_of(out.dtype), _stream())
+          _rows(out, "out"), code_of(x.dtype), code_of(out.dtype), _stream(),
+          tag=f"m{M} k{K} n{N}")
     return out
 
 
@@ -309,7 +375,8 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
-          constant_operand, 1 if persistent else 0, _stream())
+          constant_operand, 1 if persistent else 0, _stream(),
+          tag=f"a{a.shape[0]} b{b.shape[0]} k{a.shape[1]} tile{bn} splits{splits}")
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
@@ -324,7 +391,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _call("fb_gemm_skinny", _dev(x, "x", contiguous=False), _rows(x, "x"),
           _dev(w, "w", contiguous=False), _rows(w, "w"), _dev(out, "out", contiguous=False),
-          _rows(out, "out"), 1 if out.dtype == torch.float32 else 0, M, N, K, epilogue, _stream())
+          _rows(out, "out"), 1 if out.dtype == torch.float32 else 0, M, N, K, epilogue, _stream(),
+          tag=f"m{M} k{K} n{N}")
     return out
 
 
