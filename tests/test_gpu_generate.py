@@ -230,3 +230,32 @@ def test_command_line_bench_writes_a_report(tiny_folders, tmp_path):
     assert report["runs"][0]["token_ids"] == report["runs"][1]["token_ids"]
     assert report["metrics"]["decode_tokens_per_s"]["count"] == 2
     assert report["metadata"]["model_parameter_count"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_a_page_table_growth(tmp_path, dtype):
+    """A sequence that grows from 8 to 9 pages while another stays short: the
+    decode graph is re-captured with a wider page table in the middle of the
+    run, and a far key (position 3) must still be found from position 530."""
+    import foundry_b200 as fb
+    from foundry_b200.config import LlamaConfig
+    from foundry_b200.engine import SequenceStep
+    cfg_doc = {**tiny.CONFIGS["tiny_a"], "max_position_embeddings": 1024}
+    folder = fb.write_model_folder(str(tmp_path / "long"), LlamaConfig.parse(cfg_doc), 3, std=tiny.STD)
+    cfg, w = plain.read_model(folder)
+    long_tokens = tiny.random_tokens(1, 540, cfg["vocab_size"])
+    short_tokens = tiny.random_tokens(2, 60, cfg["vocab_size"])
+    want_long = plain.forward(cfg, w, long_tokens).numpy()
+    want_short = plain.forward(cfg, w, short_tokens).numpy()
+    engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=2048, max_slots=2)
+    a, b = engine.open_sequence(), engine.open_sequence()
+    engine.step([SequenceStep(a, long_tokens[:500], []), SequenceStep(b, short_tokens[:20], [])])
+    rows_a, rows_b = [], []
+    for i in range(40):
+        out = engine.step([SequenceStep(a, [long_tokens[500 + i]], [0]),
+                           SequenceStep(b, [short_tokens[20 + i]], [0])]).cpu().numpy()
+        rows_a.append(out[0:1])
+        rows_b.append(out[1:2])
+    assert engine._session.runner.width == 16 and (2, 8) in engine._runners  # both graphs were used
+    tiny.assert_logits_close(np.concatenate(rows_a), want_long[500:540], dtype, "long sequence")
+    tiny.assert_logits_close(np.concatenate(rows_b), want_short[20:60], dtype, "short sequence")
