@@ -37,10 +37,11 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
 // calls `fb_pdl_wait()` before it reads anything an earlier kernel wrote and
 // before it writes anything an earlier kernel may still read (only constants
 // such as weights may be touched before; the products request their first
-// weight tiles there). No kernel triggers its successor early
-// (griddepcontrol.launch_dependents): measured on the 3B decode step, blocks
-// of later kernels that sit waiting on the SMs slowed the weight-streaming
-// product more than the earlier start gained. `fb_set_pdl(0)` switches the mark
+// weight tiles there). Only the short kernels of few blocks (norm, rotary)
+// trigger their successor early (griddepcontrol.launch_dependents). Measured on
+// the 3B decode step: when the long kernels triggered early too, blocks of later
+// kernels sat waiting on the SMs, held registers and shared memory that the
+// running kernel's next blocks needed, and the step took half as long again. `fb_set_pdl(0)` switches the mark
 // off: launches then serialise as usual and the device call does nothing.
 extern int g_fb_pdl;
 
@@ -62,6 +63,12 @@ inline cudaError_t fb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void fb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel's blocks be placed now. Only for short kernels of few
+// blocks (norm, rotary): the product or attention kernel that follows then sits
+// ready, its first weight tiles requested, when this kernel ends.
+__device__ __forceinline__ void fb_pdl_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 #endif
 
 // ---------------------------------------------------------------- device side

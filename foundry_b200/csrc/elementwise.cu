@@ -80,6 +80,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
                                        int planes, long long plane_stride,
                                        const float* __restrict__ weight, TO* __restrict__ out,
                                        int H, float eps, float inv_h) {
+  fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H;
@@ -132,6 +133,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
                                    int planes, long long plane_stride,
                                    const float* __restrict__ weight, TO* __restrict__ out, int H,
                                    float eps, float inv_h) {
+  fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float scratch[32];
   const size_t row = (size_t)blockIdx.x * H;

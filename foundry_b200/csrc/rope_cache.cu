@@ -31,6 +31,7 @@ __global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_s
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      long long page_stride, long long head_stride, int ring_pages,
                                      int A, int Kh, int D, int write_cache) {
+  fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float s_cos[128], s_sin[128];  // rotary_dim / 2 <= 128 (head sizes up to 256)
   const int t = blockIdx.x;
@@ -140,6 +141,7 @@ __global__ void rope_kv_write_bf16_kernel(__nv_bfloat16* __restrict__ qkv, long 
                                           long long page_stride, long long head_stride,
                                           int ring_pages, int A, int Kh, int D, int write_cache) {
   __shared__ float s_cos[128], s_sin[128];
+  fb_pdl_launch();
   fb_pdl_wait();
   const int t = blockIdx.x;
   const int seq = seq_of_token[t];
