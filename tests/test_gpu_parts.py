@@ -313,3 +313,132 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype)
     finally:
         unregister_architecture("ToyForCausalLM")
         MIXERS.unregister("toy_running_mean")
+
+
+def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_path):
+    """Two more parts defined here and plugged in by name: a position encoding
+    that rotates only half of each head with linearly scaled frequencies, and a
+    feed-forward with a squared-ReLU and two token-routed experts (routing in
+    32-bit). The attention part, the block and the engine are used unchanged."""
+    import foundry_b200 as fb
+    from foundry_b200.config import (Architecture, LlamaConfig, PartSpec, register_architecture,
+                                     unregister_architecture)
+    from foundry_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, Linear, Part,
+                                    register_feed_forward, register_position_encoding)
+    from foundry_b200.engine import SequenceStep
+    from dataclasses import replace
+
+    class HalfRotary(Part):
+        attention_factor = 1.0
+
+        def __init__(self, head_dim, theta, scale, *, dtype=None, device=None):
+            self.rotary_dim = head_dim // 2
+            inv = (1.0 / (theta ** (np.arange(0, self.rotary_dim, 2, dtype=np.float32) / self.rotary_dim))
+                   / np.float32(scale)).astype(np.float32)
+            self.inv_freq_host = inv
+            self.inv_freq = torch.from_numpy(inv).to(device)
+
+    class RoutedRelu2(Part):
+        """y = sum over the top-1 expert e of softmax(router x)[e] * W2_e relu(W1_e x)^2."""
+
+        def __init__(self, hidden_size, intermediate_size, experts, *, dtype, device):
+            self.h, self.i, self.n, self.dtype = hidden_size, intermediate_size, experts, dtype
+            self.router = Linear(hidden_size, [("router", experts)], dtype=dtype, device=device)
+            self.up = [Linear(hidden_size, [(f"experts.{e}.up", intermediate_size)], dtype=dtype, device=device)
+                       for e in range(experts)]
+            self.down = [Linear(intermediate_size, [(f"experts.{e}.down", hidden_size)], dtype=dtype, device=device)
+                         for e in range(experts)]
+
+        def expected_tensors(self, prefix):
+            out = dict(self.router.expected_tensors(prefix))
+            for lin in self.up + self.down:
+                out.update(lin.expected_tensors(prefix))
+            return out
+
+        def load(self, prefix, fetch):
+            for lin in [self.router] + self.up + self.down:
+                lin.load(prefix, fetch)
+
+        def forward(self, ctx, x):
+            gate = torch.softmax(self.router.forward(x, out_dtype=torch.float32), -1)  # 32-bit
+            choice = gate.argmax(-1)
+            y = torch.zeros(x.shape[0], self.h, dtype=torch.float32, device=x.device)
+            for e in range(self.n):  # every expert on every token, masked: a toy, not a fast path
+                hidden = torch.relu(self.up[e].forward(x).float()) ** 2
+                out = self.down[e].forward(hidden.to(self.dtype)).float()
+                y += out * (gate[:, e] * (choice == e)).unsqueeze(1)
+            return y.to(self.dtype)
+
+    register_position_encoding("toy_half_rotary", HalfRotary, replace=True)
+    register_feed_forward("toy_routed_relu2", RoutedRelu2, replace=True)
+
+    def build_spec(config):
+        from foundry_b200.models.llama import build_llama_spec
+        base = build_llama_spec(config)
+        layers = []
+        for layer in base.layers:
+            mixer = PartSpec("gqa_attention", {**layer.mixer.params, "position_encoding": PartSpec(
+                "toy_half_rotary", {"head_dim": config.head_dim, "theta": 10000.0, "scale": 2.0})})
+            ff = PartSpec("toy_routed_relu2", {"hidden_size": config.hidden_size,
+                                               "intermediate_size": 48, "experts": 2})
+            layers.append(replace(layer, mixer=mixer, feed_forward=ff))
+        return replace(base, architecture="Toy2ForCausalLM", layers=tuple(layers))
+
+    register_architecture(Architecture("Toy2ForCausalLM", "llama",
+                                       lambda d: LlamaConfig.parse({**d, "architectures": ["Toy2ForCausalLM"]}),
+                                       build_spec), replace=True)
+    try:
+        cfg_doc = {**tiny.CONFIGS["tiny_b"], "architectures": ["Toy2ForCausalLM"], "num_hidden_layers": 2}
+        folder = fb.write_model_folder(str(tmp_path / "toy2"), LlamaConfig.parse(cfg_doc), 8, std=0.1)
+        cfg, w = plain.read_model(folder)
+        assert "model.layers.0.mlp.experts.1.down.weight" in w and "model.layers.0.mlp.router.weight" in w
+
+        def plain_forward(tokens):
+            S, A, K, D = len(tokens), cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+            x = w["model.embed_tokens.weight"][torch.as_tensor(tokens)]
+            rot = D // 2
+            inv = (1.0 / (10000.0 ** (np.arange(0, rot, 2, dtype=np.float32) / rot)) / np.float32(2.0)).astype(np.float32)
+            ang = (np.arange(S, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float64)
+            cos, sin = torch.from_numpy(np.cos(ang)), torch.from_numpy(np.sin(ang))
+
+            def rope(t):  # [S, heads, D]: pairs (i, i + rot/2) inside the first `rot` elements
+                a, b = t[..., :rot // 2], t[..., rot // 2:rot]
+                return torch.cat([a * cos[:, None] - b * sin[:, None], b * cos[:, None] + a * sin[:, None],
+                                  t[..., rot:]], -1)
+            for i in range(2):
+                p = f"model.layers.{i}"
+                n = plain.rms_norm(x, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+                q = rope((n @ w[f"{p}.self_attn.q_proj.weight"].T).reshape(S, A, D))
+                k = rope((n @ w[f"{p}.self_attn.k_proj.weight"].T).reshape(S, K, D))
+                v = (n @ w[f"{p}.self_attn.v_proj.weight"].T).reshape(S, K, D)
+                att = torch.empty(S, A, D, dtype=torch.float64)
+                mask = torch.tril(torch.ones(S, S, dtype=torch.bool))
+                for a_ in range(A):
+                    s = (q[:, a_] @ k[:, a_ // (A // K)].T) / math.sqrt(D)
+                    att[:, a_] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, a_ // (A // K)]
+                h = x + att.reshape(S, A * D) @ w[f"{p}.self_attn.o_proj.weight"].T
+                n = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+                gate = torch.softmax(n @ w[f"{p}.mlp.router.weight"].T, -1)
+                choice = gate.argmax(-1)
+                y = torch.zeros_like(h)
+                for e in range(2):
+                    hid = torch.relu(n @ w[f"{p}.mlp.experts.{e}.up.weight"].T) ** 2
+                    y += (hid @ w[f"{p}.mlp.experts.{e}.down.weight"].T) * (gate[:, e] * (choice == e)).unsqueeze(1)
+                x = h + y
+            x = plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+            return (x @ w["lm_head.weight"].T).numpy()
+
+        engine = fb.Engine.from_folder(folder, dtype="float32", max_tokens=512, max_slots=2)
+        tokens = tiny.random_tokens(77, 50, cfg["vocab_size"])
+        want = plain_forward(tokens)
+        slot = engine.open_sequence()
+        got = [engine.step([SequenceStep(slot, tokens[:45], list(range(45)))]).cpu().numpy()]
+        for t in tokens[45:]:
+            got.append(engine.step([SequenceStep(slot, [t], [0])]).cpu().numpy())
+        engine.close_sequence(slot)
+        got = np.concatenate(got)
+        tiny.assert_logits_close(got, want, "float32", "toy position encoding and feed-forward")
+    finally:
+        unregister_architecture("Toy2ForCausalLM")
+        POSITION_ENCODINGS.unregister("toy_half_rotary")
+        FEED_FORWARDS.unregister("toy_routed_relu2")
