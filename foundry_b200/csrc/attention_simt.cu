@@ -46,10 +46,10 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
 
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
-attention_simt_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out,
+attention_simt_kernel(const T* q, long long q_stride, T* __restrict__ out,
                       long long out_stride, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_token, const int* __restrict__ page_table,
-                      int max_pages, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                      int max_pages, const T* k_cache, const T* v_cache,
                       long long page_stride, long long head_stride, int ring_pages, int window,
                       int A, int Kh, int D, float scale) {
   fb_pdl_wait();

@@ -41,7 +41,12 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
 // trigger their successor early (griddepcontrol.launch_dependents). Measured on
 // the 3B decode step: when the long kernels triggered early too, blocks of later
 // kernels sat waiting on the SMs, held registers and shared memory that the
-// running kernel's next blocks needed, and the step took half as long again. `fb_set_pdl(0)` switches the mark
+// running kernel's next blocks needed, and the step took half as long again.
+// A kernel that can follow an early trigger reads what its predecessor wrote
+// with ordinary (coherent) loads only: pointers to such data carry no
+// `__restrict__` read-only promise and no `ld.global.nc`, because the writer
+// may still have been running when the reader's blocks were placed, and a
+// non-coherent load was seen to return the address's previous contents then. `fb_set_pdl(0)` switches the mark
 // off: launches then serialise as usual and the device call does nothing.
 extern int g_fb_pdl;
 

@@ -14,7 +14,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
-gemm_simt_kernel(const TI* __restrict__ x, const TI* __restrict__ w, TO* __restrict__ out, int M,
+gemm_simt_kernel(const TI* x /* written by the kernel before: no read-only promise */,
+                 const TI* __restrict__ w, TO* __restrict__ out, int M,
                  int N, int K, long long ldx, long long ldw, long long ldo) {
   fb_pdl_wait();
   __shared__ float xs[BK][BM + 4];

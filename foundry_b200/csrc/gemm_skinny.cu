@@ -29,7 +29,10 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 }
 __device__ __forceinline__ uint4 ld_cached(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+  // Not the non-coherent path: the kernel that writes x may still have been
+  // running when this kernel's blocks were placed (dependent launch), and a
+  // non-coherent load may then return what the address held before.
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
@@ -49,7 +52,7 @@ constexpr int CHUNK = 64;   // K elements per step of a warp
 // UNROLL: chunks whose loads are in flight together.
 template <int NT, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
-gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
                    const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
                    long long ldo, int out_f32, int T, int N, int K, int epilogue) {
   __shared__ float red[WARPS][16][8 * NT + 1];

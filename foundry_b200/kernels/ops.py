@@ -48,6 +48,10 @@ _SIGNATURES = {
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
+    "fb_attention_prefill_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p,
+                                c_int, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int,
+                                c_int, c_int, c_float, c_void_p],
+    "fb_attention_tc_status": [c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -413,11 +417,14 @@ if _os.environ.get("FOUNDRY_B200_PDL", "1") == "0":
 
 
 def gemm_tc_status():
-    """0 when no bounded wait of the tensor-core kernels ever ran out, else
-    (role, block, k-block). Synchronises the device."""
-    detail = (ctypes.c_int * 3)()
-    code = _fn("fb_gemm_tc_status")(ctypes.cast(detail, ctypes.c_void_p))
-    return 0 if code == 0 else (code, detail[1], detail[2])
+    """0 when no bounded wait of the tcgen05 kernels (products and prompt
+    attention) ever ran out, else (role, block, step). Synchronises the device."""
+    for name in ("fb_gemm_tc_status", "fb_attention_tc_status"):
+        detail = (ctypes.c_int * 3)()
+        code = _fn(name)(ctypes.cast(detail, ctypes.c_void_p))
+        if code != 0:
+            return (code, detail[1], detail[2])
+    return 0
 
 
 def sum_planes(planes: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -566,8 +573,12 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
                                      (ctx.max_kv_len + PAGE - 1) // PAGE)
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                                 num_heads, num_kv_heads, head_dim, scale, splits, stages)
-    blocks = sum((ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] + 63) // 64
-                 for i in range(ctx.n_seqs))
+    lens = [ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] for i in range(ctx.n_seqs)]
+    if head_dim in TC_HEAD_DIMS and PREFILL_TC and max(lens) >= 64 and _tc_attention_ok(q, out):
+        return attention_prefill_tc(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache,
+                                    v_cache, num_heads, num_kv_heads, head_dim, scale,
+                                    sum((n + 127) // 128 for n in lens))
+    blocks = sum((n + 63) // 64 for n in lens)
     return attention_prefill(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
 
@@ -584,6 +595,29 @@ def decode_plan(pairs: int, pages: int):
         return 1, 3
     splits = max(1, min(8, pages, (256 + pairs // 2) // pairs))
     return splits, 2
+
+
+TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prompt-attention kernel
+PREFILL_TC = _os.environ.get("FOUNDRY_B200_PREFILL_TC", "1") != "0"
+
+
+def _tc_attention_ok(q: torch.Tensor, out: torch.Tensor) -> bool:
+    return (q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and out.data_ptr() % 16 == 0 and q.stride(1) == 1 and out.stride(1) == 1)
+
+
+def attention_prefill_tc(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
+                         num_kv_heads, head_dim, scale, q_blocks) -> torch.Tensor:
+    """Prompt attention on tcgen05 (csrc/attention_tcgen05.cu); `q_blocks` is the
+    sum over sequences of ceil(tokens / 128)."""
+    _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
+    _call("fb_attention_prefill_tc", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
+          q.shape[0], _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
+          _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
+          v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), k_cache.shape[0],
+          kv_lens.numel(), q_blocks, num_heads, num_kv_heads, head_dim, float(scale), _stream())
+    return out
 
 
 def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,

@@ -261,6 +261,30 @@ def test_attention_tensor_cores_any_token_counts(ops, lens_q, lens_kv, A, Kh, D)
     close(out, want, 3e-2, 1e-2)
 
 
+TC_ATT_CASES = [c for c in ATT_CASES if c[4] in (64, 128)] + [
+    ([128, 129, 1], [128, 129, 400], 4, 2, 64),
+    ([700, 64], [700, 1000], 6, 2, 128),
+    ([256], [2000], 2, 1, 128),
+]
+
+
+@pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", TC_ATT_CASES)
+def test_attention_tcgen05_any_token_counts(ops, lens_q, lens_kv, A, Kh, D):
+    """The tcgen05 prompt kernel: whole prompts, continued prompts (keys before
+    the first query), blocks of exactly and just over 128 rows, single tokens far
+    into a sequence, a far key that stands out; q read as a strided view."""
+    case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, torch.bfloat16, seed=4, sharp=True)
+    T = sum(lens_q)
+    wide = torch.zeros(T, A * D + 2 * 8 * D, dtype=torch.bfloat16, device=DEV)
+    wide[:, :A * D] = case["q"]
+    out = torch.full_like(case["q"], 5.0)
+    blocks = sum((x + 127) // 128 for x in lens_q)
+    ops.attention_prefill_tc(wide[:, :A * D], out, case["cu"], case["kv"], case["table"], case["k"],
+                             case["v"], A, Kh, D, 1.0 / math.sqrt(D), blocks + 1)
+    assert ops.gemm_tc_status() == 0
+    close(out, want, 3e-2, 1e-2)
+
+
 @pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", [c for c in ATT_CASES if max(c[0]) == 1])
 @pytest.mark.parametrize("splits", [1, 2, 7])
 def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, splits):

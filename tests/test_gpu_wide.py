@@ -92,3 +92,25 @@ def test_benchmark_widths_on_an_unequal_batch(wide, dtype):
             assert err <= 5e-2 * scale, f"sequence {i}: max |diff| {err:.3e} (scale {scale:.2f})"
     from foundry_b200.kernels import ops
     assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replayed_steps_equal_plainly_launched_steps(wide, dtype):
+    """Single-token steps replayed as a graph run their kernels back to back, so
+    that dependent launches really overlap; launched one by one they do not.
+    Both must give the same logits, bit for bit, step after step."""
+    import foundry_b200 as fb
+    from foundry_b200.engine import SequenceStep
+    folder, seqs, _, _ = wide
+    results = []
+    for graphs in (True, False):
+        engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=4096, max_slots=4)
+        engine.use_graphs = graphs
+        slots = [engine.open_sequence() for _ in seqs]
+        engine.step([SequenceStep(s, q[:40], []) for s, q in zip(slots, seqs)])
+        rows = []
+        for i in range(8):
+            rows.append(engine.step([SequenceStep(s, [q[40 + i]], [0])
+                                     for s, q in zip(slots, seqs)]).clone())
+        results.append(torch.stack(rows))
+    assert torch.equal(results[0], results[1])
