@@ -17,6 +17,8 @@
 // [lo, p] of its own sequence, lo = max(0, p - window + 1) when the layer group
 // has a window. Each lane scores one key of a chunk; for the weighted sum the
 // lanes own head elements lane, lane+32, ...
+// Queries, keys and values are read with coherent (L2) loads: the kernel that
+// wrote this step's rows may have overlapped this kernel's start.
 #include "common.cuh"
 
 namespace {
@@ -27,14 +29,14 @@ template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
 template <>
 __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
-  const float4 a = *reinterpret_cast<const float4*>(p);
-  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  const float4 a = __ldcg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldcg(reinterpret_cast<const float4*>(p + 4));
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
   v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 template <>
 __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
-  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(p));
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -67,7 +69,7 @@ attention_simt_kernel(const T* q, long long q_stride, T* __restrict__ out,
   const int pos = positions[t];
   const int kvh = a / (A / Kh);
   const T* qrow = q + (size_t)t * q_stride + (size_t)a * D;
-  for (int d = lane; d < D; d += 32) qs[warp][d] = fb_to_float<T>(qrow[d]);
+  for (int d = lane; d < D; d += 32) qs[warp][d] = fb_load_coherent<T>(qrow + d);
   __syncwarp();
 
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
@@ -113,7 +115,7 @@ attention_simt_kernel(const T* q, long long q_stride, T* __restrict__ out,
 #pragma unroll
       for (int i = 0; i < MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < D) acc[i] = fmaf(pj, fb_to_float<T>(vrow[d]), acc[i]);
+        if (d < D) acc[i] = fmaf(pj, fb_load_coherent<T>(vrow + d), acc[i]);
       }
     }
   }

@@ -86,6 +86,17 @@ __device__ __forceinline__ float fb_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
   return __bfloat162float(v);
 }
 
+// A load that is never served by the non-coherent path: for data that the
+// kernel before this one wrote (see the launching notes above).
+template <typename T>
+__device__ __forceinline__ float fb_load_coherent(const T* p);
+template <>
+__device__ __forceinline__ float fb_load_coherent<float>(const float* p) { return __ldcg(p); }
+template <>
+__device__ __forceinline__ float fb_load_coherent<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(__ldcg(p));
+}
+
 template <typename T>
 __device__ __forceinline__ T fb_from_float(float v);
 template <>

@@ -36,7 +36,7 @@ gemm_simt_kernel(const TI* x /* written by the kernel before: no read-only promi
     for (int j = 0; j < 4; ++j) {
       const int k = k0 + lc + j;
       const int m = m0 + lr, n = n0 + lr;
-      xs[lc + j][lr] = (m < M && k < K) ? fb_to_float<TI>(x[(size_t)m * ldx + k]) : 0.f;
+      xs[lc + j][lr] = (m < M && k < K) ? fb_load_coherent<TI>(x + (size_t)m * ldx + k) : 0.f;
       ws[lc + j][lr] = (n < N && k < K) ? fb_to_float<TI>(w[(size_t)n * ldw + k]) : 0.f;
     }
     __syncthreads();

@@ -102,6 +102,7 @@ def test_replayed_steps_equal_plainly_launched_steps(wide, dtype):
     import foundry_b200 as fb
     from foundry_b200.engine import SequenceStep
     folder, seqs, _, _ = wide
+    seqs = [seqs[1], seqs[2], seqs[2][100:]]  # three streams of at least 48 tokens
     results = []
     for graphs in (True, False):
         engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=4096, max_slots=4)
