@@ -52,6 +52,12 @@ struct FaParams {
   float scale_log2;
 };
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 struct FaSmem {
   static constexpr int Q_BYTES = BQ * D * 2;
@@ -237,14 +243,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
       const int key0 = j * FB_PAGE;
       const bool diagonal = key0 + FB_PAGE - 1 > pos0 + quarter * 32;  // some key may be masked
-      float mx = -INFINITY;
+      if (diagonal) {
 #pragma unroll
-      for (int e = 0; e < FB_PAGE; ++e) {
-        float v = sc[e] * p.scale_log2;
-        if (diagonal && key0 + e > qpos) v = -INFINITY;
-        sc[e] = v;
-        mx = fmaxf(mx, v);
+        for (int e = 0; e < FB_PAGE; ++e)
+          if (key0 + e > qpos) sc[e] = -INFINITY;
       }
+      // the row maximum of the raw scores, by four independent chains; the scale is
+      // positive, so it can be applied to the maximum afterwards
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int e = 0; e < FB_PAGE; e += 4) {
+        mx4[0] = fmaxf(mx4[0], sc[e]);
+        mx4[1] = fmaxf(mx4[1], sc[e + 1]);
+        mx4[2] = fmaxf(mx4[2], sc[e + 2]);
+        mx4[3] = fmaxf(mx4[3], sc[e + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
       // P[b] was read by the product of page j - 2; after this wait at most one
       // product (page j - 1) is still running
       ok = mbar_wait(&p_empty[b], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 17, j);
@@ -274,14 +288,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       // probabilities against the reference maximum (at most 2^8), as a K-major tile
       // with the 128-byte swizzle: 16-byte chunk c of row r lands at chunk c ^ (r & 7)
       uint8_t* prow = sP + b * FaSmem<D>::P_BYTES + row * 128;
-      float sum = 0.f;
+      const float neg_ref = -m_ref;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         float pv[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          pv[e] = exp2f(sc[c * 8 + e] - m_ref);
-          sum += pv[e];
+          // 2^(s * scale - m_ref): one multiply-add and one ex2; the result is at most 2^8
+          // and is rounded to bfloat16 next, so the approximate ex2 costs no accuracy
+          pv[e] = fast_exp2(fmaf(sc[c * 8 + e], p.scale_log2, neg_ref));
+          sum4[e & 3] += pv[e];
         }
         uint4 pk;
         __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]);
@@ -294,6 +311,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         pk.w = *reinterpret_cast<uint32_t*>(&h3);
         *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = pk;
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
       fence_async_smem();
       tc_fence_before();
