@@ -112,6 +112,8 @@ struct AttnParams {
   float* ws_o;   // [n_seqs, Kh, splits, 16, D]
   float* ws_ml;  // [n_seqs, Kh, splits, 16, 2]
   int* counters; // [n_seqs, Kh]: splits that have delivered; zero between calls
+  const void* next;      // constant data to bring into L2 for the kernel after this one
+  long long next_bytes;  // 0 = none
 };
 
 // --------------------------------------------------------------------- prefill
@@ -351,6 +353,7 @@ attn_decode_kernel(const AttnParams p) {
   float* ws_o = p.ws_o + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * D;
   float* ws_ml = p.ws_ml + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * 2;
   if (pg0 >= pg1) {  // nothing in this range (or a padding row: kv_len == 0)
+    fb_prefetch_l2_slice(p.next, p.next_bytes);
     if (p.splits > 1) {
       for (int i = threadIdx.x; i < G; i += THREADS) { ws_ml[2 * i] = -INFINITY; ws_ml[2 * i + 1] = 0.f; }
       merge_if_last<D>(p, seq, kvh, token, G);
@@ -470,6 +473,7 @@ attn_decode_kernel(const AttnParams p) {
     __syncthreads();
   }
   cp_async_wait<0>();
+  fb_prefetch_l2_slice(p.next, p.next_bytes);
 
   // merge the four warps' (m, l, O) through shared memory (the page buffers are free now)
   constexpr int DP = D + 8;                   // padded row: fewer bank conflicts
@@ -596,7 +600,10 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
                                int max_pages, const void* k_cache, const void* v_cache,
                                long long page_stride, long long head_stride, int n_seqs, int A,
                                int Kh, int D, float scale, int splits, int stages, float* ws_o,
-                               float* ws_ml, int* counters, cudaStream_t stream) {
+                               float* ws_ml, int* counters, const void* next,
+                               long long next_bytes, cudaStream_t stream) {
+  FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
+             "attention_decode: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
   int rc = check_common("attention_decode", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
                         v_cache, page_stride, head_stride);
   if (rc) return rc;
@@ -697,5 +704,5 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, 3, ws_o, ws_ml, counters, stream);
+                             D, scale, splits, 3, ws_o, ws_ml, counters, nullptr, 0, stream);
 }

@@ -74,6 +74,26 @@ __device__ __forceinline__ void fb_pdl_wait() { asm volatile("griddepcontrol.wai
 __device__ __forceinline__ void fb_pdl_launch() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+
+// Asks the memory system to bring [p, p + bytes) into L2; nothing waits for it.
+// The blocks of a grid share the range in pieces, each block's first warp asks
+// for its pieces. A kernel calls this once its own loads are issued, with the
+// constant data (weights) that the NEXT kernel streams first: DRAM then keeps
+// working through this kernel's tail and the next one's start.
+// p must be 16-byte aligned and bytes a multiple of 16.
+__device__ __forceinline__ void fb_prefetch_l2_slice(const void* p, long long bytes) {
+  constexpr long long PIECE = 8192;
+  if (bytes <= 0 || threadIdx.x >= 32) return;
+  const long long nblk = (long long)gridDim.x * gridDim.y * gridDim.z;
+  const long long bid = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+  const long long pieces = (bytes + PIECE - 1) / PIECE;
+  for (long long i = bid + nblk * threadIdx.x; i < pieces; i += nblk * 32) {
+    const long long left = bytes - i * PIECE;
+    const unsigned size = (unsigned)(left < PIECE ? left : PIECE);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;"
+                 :: "l"(reinterpret_cast<const char*>(p) + i * PIECE), "r"(size) : "memory");
+  }
+}
 #endif
 
 // ---------------------------------------------------------------- device side

@@ -54,15 +54,19 @@ template <int NT, int WARPS, int UNROLL>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
                    const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
-                   long long ldo, int out_f32, int T, int N, int K, int epilogue) {
+                   long long ldo, int out_f32, int T, int N, int K, int epilogue,
+                   const void* next, long long next_bytes, long long plane_stride) {
   __shared__ float red[WARPS][16][8 * NT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);  // rows past N are discarded
+  // gridDim.y CTAs share a row group's K; each writes its own float32 plane
   const int chunks = (K + CHUNK - 1) / CHUNK;
-  const int per = (chunks + WARPS - 1) / WARPS;
-  const int c0 = warp * per, c1 = min(chunks, c0 + per);
+  const int share = (chunks + (int)gridDim.y - 1) / (int)gridDim.y;
+  const int s0 = blockIdx.y * share, s1 = min(chunks, s0 + share);
+  const int per = (max(s1 - s0, 0) + WARPS - 1) / WARPS;
+  const int c0 = s0 + warp * per, c1 = min(s1, c0 + per);
 
   // A thread's 16 elements of a 64-element chunk are [8t, 8t+8) and [32+8t, 32+8t+8):
   // the four threads of a row group read 64 contiguous bytes per load instruction.
@@ -149,6 +153,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
     }
     multiply(a, b);
   }
+  // this block's weights are in; the kernel after this one can have its own on the way
+  fb_prefetch_l2_slice(next, next_bytes);
   // acc[j][0..1]: row g, tokens j*8 + 2t, 2t+1; acc[j][2..3]: row g + 8
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
@@ -158,7 +164,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
     red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
   }
   __syncthreads();
-  float* out_f = reinterpret_cast<float*>(out);
+  float* out_f = reinterpret_cast<float*>(out) + (size_t)blockIdx.y * plane_stride;
   __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(out);
   if (epilogue == 0) {
     for (int idx = threadIdx.x; idx < 16 * T; idx += WARPS * 32) {
@@ -193,28 +199,45 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
 // x: [T, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), T <= 16.
 // epilogue 0: out[T, N] (bf16 or float32, row stride ldo).
 // epilogue 1: w's rows are (gate, up) pairs; out[T, N / 2] bf16 = SiLU(gate) * up.
+// next / next_bytes: optional constant data (the next kernel's weights) to be
+// brought into L2 as this kernel's blocks finish their own loads; 0 bytes = none.
+// ksplit > 1: K is shared by ksplit CTAs per row group and out is ksplit float32
+// planes [T, N], plane_stride elements apart, for a consumer that sums them
+// (epilogue 0 only). warps: 4, 8 or 16 per CTA, or 0 to have it chosen here.
 FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long ldw, void* out,
                           long long ldo, int out_f32, int T, int N, int K, int epilogue,
-                          cudaStream_t stream) {
+                          const void* next, long long next_bytes, int ksplit,
+                          long long plane_stride, int warps, cudaStream_t stream) {
+  FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
+             "gemm_skinny: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
   FB_REQUIRE(T > 0 && T <= 16 && N > 0 && K > 0, "gemm_skinny: bad sizes T=%d N=%d K=%d", T, N, K);
   FB_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)x % 16) == 0 &&
                  ((uintptr_t)w % 16) == 0,
              "gemm_skinny: K, the row strides and the pointers must keep 16-byte alignment");
   FB_REQUIRE(epilogue == 0 || (epilogue == 1 && !out_f32 && N % 2 == 0),
              "gemm_skinny: the SiLU-mul epilogue needs a bf16 output and an even row count");
+  FB_REQUIRE(ksplit >= 1 && ksplit <= 64 && (ksplit == 1 || (out_f32 && epilogue == 0 &&
+                                                             plane_stride >= (long long)T * ldo)),
+             "gemm_skinny: %d K shares need float32 planes and the plain epilogue", ksplit);
+  FB_REQUIRE(warps == 0 || warps == 4 || warps == 8 || warps == 16,
+             "gemm_skinny: %d warps per CTA (4, 8 or 16)", warps);
   const int blocks = (N + 15) / 16;
-  // Warps per CTA: enough warps on the chip to cover the memory latency (about
-  // 16 per SM), at least two chunks of K each.
-  const int chunks = (K + CHUNK - 1) / CHUNK;
-  int warps = (148 * 16 + blocks - 1) / blocks;
-  warps = warps <= 4 ? 4 : warps <= 8 ? 8 : 16;
-  while (warps > 4 && chunks / warps < 2) warps /= 2;
+  // Warps per CTA: as many as still let every CTA of the grid be resident at
+  // once (one CTA of 16 warps, two of 8 or five of 4 fit an SM). A second, thin
+  // round of CTAs costs a whole round's latency: measured on the 3B decode step,
+  // 192 CTAs of 16 warps (148 + 44) were 4 us a call slower than 192 of 8.
+  const int chunks = ((K + CHUNK - 1) / CHUNK + ksplit - 1) / ksplit;
+  if (warps == 0) {
+    const long long ctas = (long long)blocks * ksplit;
+    warps = ctas <= 148 ? 16 : ctas <= 296 ? 8 : 4;
+    while (warps > 4 && chunks / warps < 2) warps /= 2;
+  }
   const int per = (chunks + warps - 1) / warps;
   const int unroll = per >= 4 ? 4 : per >= 3 ? 3 : 2;
 #define FB_SKINNY(NT, W, U)                                                                   \
-  fb_launch(gemm_skinny_kernel<NT, W, U>, dim3(blocks), dim3(W * 32), 0, stream,               \
+  fb_launch(gemm_skinny_kernel<NT, W, U>, dim3(blocks, ksplit), dim3(W * 32), 0, stream,       \
             (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw, out, ldo, out_f32, T, N, \
-            K, epilogue)
+            K, epilogue, next, next_bytes, plane_stride)
 #define FB_SKINNY_U(NT, W)                                    \
   do {                                                        \
     if (unroll == 4) FB_SKINNY(NT, W, 4);                     \

@@ -46,6 +46,9 @@ class StepContext:
     max_q_len: int
     max_kv_len: int
     _tables: Dict[int, torch.Tensor] = field(default_factory=dict)
+    # The weight that the step streams after the part being run (a prefetch
+    # hint, set by the model and the blocks as they go; None = unknown).
+    reads_after_part: Optional[torch.Tensor] = None
 
     def page_table(self, group: KVGroup) -> torch.Tensor:
         """int32 [n_seqs, width]: the pages of each sequence in `group`."""

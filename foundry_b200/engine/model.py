@@ -16,6 +16,7 @@ from ..cache.store import CacheRequest, SequenceCache
 from ..config.spec import ModelSpec
 from ..kernels import ops
 from ..parts import BLOCKS, NORMS
+from ..parts.base import first_weight_of
 from ..parts.linear import matmul_nt
 from ..weights.loader import ExpectedTensor, check_against, load_tensor
 from ..weights.safetensors_io import WeightFiles
@@ -125,9 +126,14 @@ class Model:
                             device=self.device)
         ops.embed_gather(self.embedding, ctx.token_ids, resid)
         delta = None
-        for entry in spec.schedule:
+        for i, entry in enumerate(spec.schedule):
             block = self.blocks[entry.layer]
+            follower = (self.blocks[spec.schedule[i + 1].layer] if i + 1 < len(spec.schedule)
+                        else None)
+            ctx.reads_after_part = (first_weight_of(follower) if follower is not None
+                                    else self.output_head if ctx.n_want else None)
             delta = block.forward(ctx, resid, delta, cache.view(entry.cache, entry.writes_cache))
+        ctx.reads_after_part = None
         n = ctx.n_want
         logits = torch.empty((n, spec.vocab_size), dtype=torch.float32, device=self.device)
         if n == 0:

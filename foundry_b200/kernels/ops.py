@@ -44,7 +44,7 @@ _SIGNATURES = {
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
-                       c_int, c_void_p],
+                       c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
@@ -54,7 +54,7 @@ _SIGNATURES = {
     "fb_attention_tc_status": [c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
 }
@@ -383,21 +383,76 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           tag=f"a{a.shape[0]} b{b.shape[0]} k{a.shape[1]} tile{bn} splits{splits}")
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0) -> torch.Tensor:
+# Bytes of the next kernel's weights that a single-token-step kernel asks into
+# L2 while it finishes (0 switches the hints off).
+L2_PREFETCH_BYTES = int(float(_os.environ.get("FOUNDRY_B200_L2_PREFETCH_MB", "8")) * (1 << 20))
+
+
+def _prefetch_range(then_reads: Optional[torch.Tensor]):
+    """(address, bytes) of the start of `then_reads` to bring into L2, or (0, 0)."""
+    if then_reads is None or L2_PREFETCH_BYTES <= 0 or not then_reads.is_cuda:
+        return 0, 0
+    size = min(then_reads.numel() * then_reads.element_size(), L2_PREFETCH_BYTES) // 16 * 16
+    if not then_reads.is_contiguous() or then_reads.data_ptr() % 16 or size <= 0:
+        return 0, 0
+    return then_reads.data_ptr(), size
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 0,
+                then_reads: Optional[torch.Tensor] = None, ksplit: int = 1,
+                warps: int = 0) -> torch.Tensor:
     """Up to 16 token rows: the weight-streaming kernel (csrc/gemm_skinny.cu).
-    epilogue 1: `w` rows are (gate, up) pairs and out is [M, N/2] = SiLU(gate)*up."""
+    epilogue 1: `w` rows are (gate, up) pairs and out is [M, N/2] = SiLU(gate)*up.
+    `then_reads`: the weights the step streams after this product; the kernel's
+    blocks ask for their start to be brought into L2 as they finish.
+    `ksplit` > 1: K is shared by that many CTAs per row group and `out` is
+    float32 planes [ksplit, M, N]. `warps`: 4, 8 or 16 per CTA (0: the
+    launcher's choice)."""
     M, K = x.shape
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_skinny takes bfloat16 operands")
     want = (M, N // 2) if epilogue else (M, N)
+    if ksplit > 1:
+        want = (ksplit, *want)
+        if out.dtype != torch.float32 or not out.is_contiguous():
+            raise KernelError("gemm_skinny: K shares are written as contiguous float32 planes")
     if tuple(out.shape) != want or w.shape[1] != K:
         raise KernelError(f"gemm_skinny: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _call("fb_gemm_skinny", _dev(x, "x", contiguous=False), _rows(x, "x"),
           _dev(w, "w", contiguous=False), _rows(w, "w"), _dev(out, "out", contiguous=False),
-          _rows(out, "out"), 1 if out.dtype == torch.float32 else 0, M, N, K, epilogue, _stream(),
+          _rows(out, "out") if ksplit == 1 else N, 1 if out.dtype == torch.float32 else 0,
+          M, N, K, epilogue,
+          *_prefetch_range(then_reads), ksplit, M * N if ksplit > 1 else 0, warps, _stream(),
           tag=f"m{M} k{K} n{N}")
     return out
+
+
+def skinny_plan(N: int, K: int, planes_ok: bool):
+    """(K shares, warps per CTA; 0 = the launcher's rule) of the weight-streaming
+    product for N weight rows. A CTA owns 16 rows. With fewer row groups than
+    SMs, K is shared among CTAs (float32 planes for the consumer to sum) until
+    the grid covers the SMs, each share keeping at least 8 chunks of 64.
+    Measured on the 3B decode step, sharing K did not pay once the row groups
+    alone covered the SMs."""
+    override = _SKINNY_PLANS.get(N * 1000003 + K)
+    if override:
+        return override if planes_ok else (1, override[1])
+    groups = (N + 15) // 16
+    if planes_ok and groups < SM_COUNT:
+        return max(1, min(SM_COUNT // groups, (K + 63) // 64 // 8)), 0
+    return 1, 0
+
+
+def _parse_plans(text: str):
+    plans = {}
+    for item in filter(None, text.split(",")):
+        n, k, ks, wp = (int(v) for v in item.split(":"))
+        plans[n * 1000003 + k] = (ks, wp)
+    return plans
+
+
+_SKINNY_PLANS = _parse_plans(_os.environ.get("FOUNDRY_B200_SKINNY_PLANS", ""))
 
 
 # token rows up to which the weight-streaming kernel is used
@@ -474,7 +529,8 @@ def prompt_tile_width(M: int, N: int) -> int:
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-              out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
+              out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
+              then_reads: Optional[torch.Tensor] = None):
     """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
 
     Up to 16 rows: the weight-streaming kernel. More than 128 rows: token rows
@@ -498,9 +554,14 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_simt(x, w, out)
     if M <= SKINNY_ROWS:
+        ksplit, warps = skinny_plan(N, K, allow_planes and out is None)
+        if ksplit > 1:
+            planes = torch.empty((ksplit, M, N), dtype=torch.float32, device=x.device)
+            gemm_skinny(x, w, planes, then_reads=then_reads, ksplit=ksplit, warps=warps)
+            return Planes(planes)
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        return gemm_skinny(x, w, out)
+        return gemm_skinny(x, w, out, then_reads=then_reads, warps=warps)
     if M > 128:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
@@ -527,7 +588,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
-def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,
+                       then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[M, I] = silu(x @ gate^T) * (x @ up^T) with `w_pairs` [2I, K] holding
     gate i in row 2i and up i in row 2i+1; the activation runs in the product's
     epilogue, so the [M, 2I] intermediate never reaches memory."""
@@ -542,7 +604,8 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         gemm_simt(x, w_pairs, tmp)
         return silu_mul(tmp, out, interleaved=True)
     if M <= SKINNY_ROWS:
-        return gemm_skinny(x, w_pairs, out, epilogue=1)
+        return gemm_skinny(x, w_pairs, out, epilogue=1, then_reads=then_reads,
+                           warps=skinny_plan(two_i, K, False)[1])
     if M > 128:
         bn = prompt_tile_width(M, two_i)
         gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2,
@@ -558,7 +621,8 @@ FAST_HEAD_DIMS = (16, 32, 64, 128)  # head sizes of the tensor-core attention ke
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
               k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int,
-              head_dim: int, scale: float, window: int = 0, ring_pages: int = 0) -> torch.Tensor:
+              head_dim: int, scale: float, window: int = 0, ring_pages: int = 0,
+              then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of a step's tokens over the cache: the kernel that fits the
     element type and the step. bfloat16 with a built head size runs on the
     tensor cores (one kernel for single-token steps, one for prompts); float32,
@@ -572,7 +636,8 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
         splits, stages = decode_plan(ctx.n_seqs * num_kv_heads,
                                      (ctx.max_kv_len + PAGE - 1) // PAGE)
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
-                                num_heads, num_kv_heads, head_dim, scale, splits, stages)
+                                num_heads, num_kv_heads, head_dim, scale, splits, stages,
+                                then_reads=then_reads)
     lens = [ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] for i in range(ctx.n_seqs)]
     if head_dim in TC_HEAD_DIMS and PREFILL_TC and max(lens) >= 64 and _tc_attention_ok(q, out):
         return attention_prefill_tc(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache,
@@ -635,10 +700,12 @@ def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, 
 
 
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
-                     num_kv_heads, head_dim, scale, splits, stages: int = 3) -> torch.Tensor:
+                     num_kv_heads, head_dim, scale, splits, stages: int = 3,
+                     then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
     over `splits` CTAs per (sequence, kv head); the CTA that finishes a pair
-    last merges its partial results."""
+    last merges its partial results. `then_reads`: weights to ask into L2 for
+    the kernel that follows (see `gemm_skinny`)."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
     n = kv_lens.numel()
     ws_o = ws_ml = counters = None
@@ -654,7 +721,8 @@ def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, n
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
           head_dim, float(scale), splits, stages, 0 if ws_o is None else ws_o.data_ptr(),
           0 if ws_ml is None else ws_ml.data_ptr(),
-          0 if counters is None else counters.data_ptr(), _stream())
+          0 if counters is None else counters.data_ptr(), *_prefetch_range(then_reads),
+          _stream())
     return out
 
 

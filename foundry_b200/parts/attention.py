@@ -64,6 +64,9 @@ class GQAAttention(Part):
     def cache_request(self) -> KVRequest:
         return KVRequest(self.num_kv_heads, self.head_dim, self.window)
 
+    def first_weight(self):
+        return self.qkv.weight
+
     # ------------------------------------------------------------------- run
     def forward(self, ctx, x: torch.Tensor, cache: KVView):
         qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
@@ -76,5 +79,6 @@ class GQAAttention(Part):
         attn = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(ctx, q, attn, table, cache.k, cache.v, self.num_heads, self.num_kv_heads,
                       self.head_dim, self.scale, window=cache.group.window,
-                      ring_pages=cache.group.ring_pages)
-        return self.o.forward(attn, allow_planes=True)
+                      ring_pages=cache.group.ring_pages, then_reads=self.o.weight)
+        return self.o.forward(attn, allow_planes=True,
+                        then_reads=getattr(ctx, "reads_after_part", None))

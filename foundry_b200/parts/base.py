@@ -23,6 +23,13 @@ FeedForward
     forward(ctx, x) -> y
 Block
     forward(ctx, resid, delta, cache_view) -> new delta (not yet added to resid)
+Optional, any part
+    first_weight() -> the weight tensor its forward streams first, or None.
+    `ctx.reads_after_part` holds the first weight of whatever runs after the
+    part being called (the block sets it for its mixer and feed-forward, the
+    model for the block); a part may hand it to its last product as
+    `then_reads`, which single-token steps turn into an L2 prefetch. A part
+    that ignores both is still correct.
 
 A new part is a class with these methods plus one `register_*` call; the
 engine builds it from `PartSpec(kind, params)` as `cls(**params, dtype=...,
@@ -48,6 +55,15 @@ class Part:
 
     def load(self, prefix: str, fetch: Fetch) -> None:
         return None
+
+    def first_weight(self) -> Optional[torch.Tensor]:
+        return None
+
+
+def first_weight_of(part) -> Optional[torch.Tensor]:
+    """`part.first_weight()` where the part offers it."""
+    probe = getattr(part, "first_weight", None)
+    return probe() if callable(probe) else None
 
 
 class Registry:

@@ -17,7 +17,8 @@ import torch
 
 from ..config.spec import LayerSpec
 from ..weights.loader import ExpectedTensor
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Fetch, Part, register_block
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Fetch, Part, first_weight_of,
+                   register_block)
 
 
 @register_block("pre_norm_residual")
@@ -51,8 +52,14 @@ class PreNormResidualBlock(Part):
     def cache_request(self):
         return self.mixer.cache_request()
 
+    def first_weight(self):
+        return first_weight_of(self.mixer)
+
     def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], cache):
+        after_block = getattr(ctx, "reads_after_part", None)  # what follows this block
         normed = self.mixer_norm.add_norm(resid, delta)
+        ctx.reads_after_part = first_weight_of(self.feed_forward)
         mixed = self.mixer.forward(ctx, normed, cache)
         normed = self.feed_forward_norm.add_norm(resid, mixed)
+        ctx.reads_after_part = after_block
         return self.feed_forward.forward(ctx, normed)

@@ -17,11 +17,13 @@ from .base import Fetch, Part
 
 
 def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-              out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
+              out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
+              then_reads: Optional[torch.Tensor] = None):
     """out[M,N] = x[M,K] @ w[N,K]^T, accumulated in 32-bit, by the kernel that
     fits the element type and the shape. With `allow_planes` a split-K product
     may come back as `ops.Planes` (float32 partial results) for a consumer that
-    sums them while it reads."""
+    sums them while it reads. `then_reads` names the weights the step streams
+    next, a hint that the single-token kernel turns into an L2 prefetch."""
     M, N = x.shape[0], w.shape[0]
     if x.dtype != w.dtype:
         raise ops.KernelError(
@@ -31,7 +33,7 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
         return ops.gemm_simt(x, w, out)
-    return ops.gemm_bf16(x, w, out, out_dtype, allow_planes)
+    return ops.gemm_bf16(x, w, out, out_dtype, allow_planes, then_reads)
 
 
 class Linear(Part):
@@ -57,5 +59,6 @@ class Linear(Part):
         self.weight = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, 0).contiguous()
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False):
-        return matmul_nt(x, self.weight, out, out_dtype, allow_planes)
+                out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
+                then_reads: Optional[torch.Tensor] = None):
+        return matmul_nt(x, self.weight, out, out_dtype, allow_planes, then_reads)

@@ -39,10 +39,15 @@ class SwiGLU(Part):
                                                           self.hidden_size).contiguous()
         self.down.load(prefix, fetch)
 
+    def first_weight(self):
+        return self.gate_up
+
     def forward(self, ctx, x: torch.Tensor):
         hidden = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16:
-            ops.gemm_bf16_silu_mul(x, self.gate_up, hidden)  # activation in the epilogue
+            ops.gemm_bf16_silu_mul(x, self.gate_up, hidden,  # activation in the epilogue
+                                   then_reads=self.down.weight)
         else:
             ops.silu_mul(matmul_nt(x, self.gate_up), hidden, interleaved=True)
-        return self.down.forward(hidden, allow_planes=True)
+        return self.down.forward(hidden, allow_planes=True,
+                        then_reads=getattr(ctx, "reads_after_part", None))

@@ -501,6 +501,41 @@ def test_gemm_skinny(ops, M, N, K):
     assert float(wide_out[:, N:].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("warps", [4, 8, 16])
+@pytest.mark.parametrize("M,N,K,ksplit", [(3, 100, 72, 2), (8, 384, 8192, 5), (16, 50, 4104, 3),
+                                          (9, 16, 64, 4), (1, 130, 200, 1)])
+def test_gemm_skinny_shared_k(ops, M, N, K, ksplit, warps):
+    """K shared among CTAs: float32 planes whose sum is the product (shares that
+    hold no chunk write zeros); every warp count; a weight range handed over
+    for prefetching changes nothing."""
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=9)
+    want = x.double() @ w.double().T
+    later = rnd(64, 256, dtype=torch.bfloat16, seed=3)
+    if ksplit == 1:
+        out = torch.full((M, N), 7.0, device=DEV)
+        ops.gemm_skinny(x, w, out, warps=warps, then_reads=later)
+        close(out, want, 2e-4 * math.sqrt(K), 1e-5)
+        return
+    planes = torch.full((ksplit, M, N), 7.0, device=DEV)
+    ops.gemm_skinny(x, w, planes, ksplit=ksplit, warps=warps, then_reads=later)
+    close(planes.sum(0), want, 2e-4 * math.sqrt(K), 1e-5)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny(x, w, torch.zeros(ksplit, M, N, dtype=torch.bfloat16, device=DEV), ksplit=ksplit)
+
+
+def test_gemm_bf16_few_rows_few_features_shares_k(ops):
+    """Fewer row groups than SMs: the dispatcher shares K and hands planes to a
+    consumer that allows them, a tensor to one that does not."""
+    x, w = rnd(4, 2048, dtype=torch.bfloat16), rnd(256, 2048, dtype=torch.bfloat16, seed=2)
+    want = x.double() @ w.double().T
+    got = ops.gemm_bf16(x, w, allow_planes=True)
+    assert isinstance(got, ops.Planes) and got.count > 1
+    close(got.tensor.sum(0), want, 2e-4 * math.sqrt(2048), 1e-5)
+    plain = ops.gemm_bf16(x, w)
+    assert isinstance(plain, torch.Tensor)
+    close(plain, want, 2e-4 * math.sqrt(2048) + 1e-2, 8e-3)
+
+
 @pytest.mark.parametrize("bn", [64, 128, 144, 176, 192, 208, 240, 256])
 @pytest.mark.parametrize("rows_a,rows_b,K", [(300, 700, 264), (2048, 1024, 512), (130, 70, 64),
                                               (1000, 5000, 72)])
