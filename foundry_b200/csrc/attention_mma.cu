@@ -327,10 +327,70 @@ __device__ void merge_if_last(const AttnParams& p, int seq, int kvh, int token, 
   if (threadIdx.x == 0) p.counters[seq * p.Kh + kvh] = 0;
 }
 
-template <int D, int ST>
+// ---- the same merge inside a thread-block cluster: the CTAs of a (sequence,
+// kv head) form one cluster, each leaves its partial (max, sum, output) in its
+// own shared memory, and after a cluster barrier every CTA reads its peers'
+// shared memory for its share of the output elements. No workspace in global
+// memory, no counters. Every CTA of the cluster calls this exactly once (also
+// one whose range is empty): the two barriers need all of them.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer(const float* mine, unsigned rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(mine)), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+constexpr int MAX_CLUSTER = 8;  // portable cluster size
+
+// cO [16][D], cM [16], cL [16]: this CTA's partial result, at the same shared
+// memory offset in every CTA of the cluster.
+template <int D>
+__device__ void merge_in_cluster(const AttnParams& p, const float* cO, const float* cM,
+                                 const float* cL, int kvh, int token, int G) {
+  unsigned rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  __syncthreads();
+  cluster_sync_all();
+  const int S = p.splits;
+  const int total = G * D, share = (total + S - 1) / S;
+  const int end = min(total, (int)(rank + 1) * share);
+  for (int idx = rank * share + threadIdx.x; idx < end; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
+#pragma unroll
+    for (int s = 0; s < MAX_CLUSTER; ++s) {
+      ms[s] = -INFINITY; ls[s] = 0.f; os[s] = 0.f;
+      if (s < S) {
+        ms[s] = ld_peer(cM + row, s);
+        ls[s] = ld_peer(cL + row, s);
+        // an empty range left no output behind; its sum is zero
+        os[s] = ms[s] == -INFINITY ? 0.f : ld_peer(cO + row * D + d, s);
+      }
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < MAX_CLUSTER; ++s) M = fmaxf(M, ms[s]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int s = 0; s < MAX_CLUSTER; ++s) {
+      if (ms[s] == -INFINITY) continue;
+      const float f = exp2f(ms[s] - M);
+      L += ls[s] * f;
+      acc += os[s] * f;
+    }
+    p.out[(long long)token * p.out_stride + (long long)(kvh * G + row) * D + d] =
+        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+  }
+  cluster_sync_all();  // peers may have been reading this CTA's memory until here
+}
+
+template <int D, int ST, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const AttnParams p) {
-  fb_pdl_wait();
   constexpr int KT = D / 16, NT = D / 8;
   extern __shared__ __align__(128) uint8_t smem[];
   // ST page buffers: ST - 1 pages are on their way while one is multiplied. A
@@ -343,18 +403,31 @@ attn_decode_kernel(const AttnParams p) {
   const int G = p.A / p.Kh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  // The step's description (token offsets, lengths, page table) is uploaded
+  // before the step's first kernel, so it is read before the wait for the
+  // previous kernel; so are cache pages that were full before this step: the
+  // step's own keys lie in the pages from `fresh` on.
   const int token = p.cu_tokens[seq];
   const int kv_len = p.kv_lens[seq];
   const int n_pages = (kv_len + FB_PAGE - 1) / FB_PAGE;
   const int per = (n_pages + p.splits - 1) / p.splits;
   const int pg0 = split * per;
   const int pg1 = min(n_pages, pg0 + per);
+  const int fresh = max(kv_len - (p.cu_tokens[seq + 1] - token), 0) / FB_PAGE;
 
   float* ws_o = p.ws_o + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * D;
   float* ws_ml = p.ws_ml + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * 2;
+  constexpr int DP = D + 8;                                     // padded row of the warps' merge
+  float* cO = reinterpret_cast<float*>(sK) + 4 * 16 * DP + 128;  // [16][D] (cluster merge)
+  float* cM = cO + 16 * D;                                      // [16]
+  float* cL = cM + 16;                                          // [16]
   if (pg0 >= pg1) {  // nothing in this range (or a padding row: kv_len == 0)
+    fb_pdl_wait();
     fb_prefetch_l2_slice(p.next, p.next_bytes);
-    if (p.splits > 1) {
+    if (CLUSTER) {
+      for (int i = threadIdx.x; i < 16; i += THREADS) { cM[i] = -INFINITY; cL[i] = 0.f; }
+      merge_in_cluster<D>(p, cO, cM, cL, kvh, token, G);
+    } else if (p.splits > 1) {
       for (int i = threadIdx.x; i < G; i += THREADS) { ws_ml[2 * i] = -INFINITY; ws_ml[2 * i + 1] = 0.f; }
       merge_if_last<D>(p, seq, kvh, token, G);
     } else {
@@ -367,15 +440,21 @@ attn_decode_kernel(const AttnParams p) {
   const __nv_bfloat16* kbase = p.k_cache + (long long)kvh * p.head_stride;
   const __nv_bfloat16* vbase = p.v_cache + (long long)kvh * p.head_stride;
 
+  auto load_page = [&](int ahead) {
+    const long long off = (long long)pages[pg0 + ahead] * p.page_stride;
+    load_tile<D>(sK + ahead * 64 * D, kbase + off, D, 64, 64);
+    load_tile<D>(sV + ahead * 64 * D, vbase + off, D, 64, 64);
+  };
+  // old pages of the first ST - 1 go out now; they complete with the first group
+#pragma unroll
+  for (int ahead = 0; ahead < ST - 1; ++ahead)
+    if (pg0 + ahead < min(pg1, fresh)) load_page(ahead);
+  fb_pdl_wait();
   // rows 0..G-1 of the tile are this kv head's query heads, consecutive in q
   load_tile<D>(sQ, p.q + (long long)token * p.q_stride + (long long)(kvh * G) * D, D, 16, G);
 #pragma unroll
   for (int ahead = 0; ahead < ST - 1; ++ahead) {
-    if (pg0 + ahead < pg1) {
-      const long long off = (long long)pages[pg0 + ahead] * p.page_stride;
-      load_tile<D>(sK + ahead * 64 * D, kbase + off, D, 64, 64);
-      load_tile<D>(sV + ahead * 64 * D, vbase + off, D, 64, 64);
-    }
+    if (pg0 + ahead < pg1 && pg0 + ahead >= fresh) load_page(ahead);
     cp_async_commit();  // one group per page, empty when there is no page
   }
 
@@ -476,8 +555,7 @@ attn_decode_kernel(const AttnParams p) {
   fb_prefetch_l2_slice(p.next, p.next_bytes);
 
   // merge the four warps' (m, l, O) through shared memory (the page buffers are free now)
-  constexpr int DP = D + 8;                   // padded row: fewer bank conflicts
-  float* sO = reinterpret_cast<float*>(sK);   // [4][16][DP]
+  float* sO = reinterpret_cast<float*>(sK);   // [4][16][DP], rows padded: fewer bank conflicts
   float* sM = sO + 4 * 16 * DP;               // [4][16]
   float* sL = sM + 4 * 16;                    // [4][16]
 #pragma unroll
@@ -504,7 +582,10 @@ attn_decode_kernel(const AttnParams p) {
       L += sL[w * 16 + row] * f;
       acc += sO[(w * 16 + row) * DP + d] * f;
     }
-    if (p.splits > 1) {
+    if (CLUSTER) {
+      cO[row * D + d] = acc;
+      if (d == 0) { cM[row] = M; cL[row] = L; }
+    } else if (p.splits > 1) {
       ws_o[row * D + d] = acc;
       if (d == 0) { ws_ml[2 * row] = M; ws_ml[2 * row + 1] = L; }
     } else {
@@ -512,7 +593,8 @@ attn_decode_kernel(const AttnParams p) {
           __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
   }
-  if (p.splits > 1) merge_if_last<D>(p, seq, kvh, token, G);
+  if (CLUSTER) merge_in_cluster<D>(p, cO, cM, cL, kvh, token, G);
+  else if (p.splits > 1) merge_if_last<D>(p, seq, kvh, token, G);
 }
 
 template <int D>
@@ -529,20 +611,35 @@ int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
   return fb_check_launch("attention_prefill");
 }
 
-template <int D, int ST>
-int launch_decode(const AttnParams& p, cudaStream_t stream) {
+template <int D, int ST, bool CLUSTER>
+int launch_decode_as(const AttnParams& p, cudaStream_t stream) {
   int bytes = (16 + 2 * ST * 64) * D * 2;
-  const int merge = 4 * 16 * (D + 8) * 4 + 2 * 4 * 16 * 4 + 16 * D * 2;
+  // the merge reuses the page buffers: four warps' outputs, their (max, sum),
+  // and the CTA's own partial result for its cluster
+  const int merge = 16 * D * 2 + (4 * 16 * (D + 8) + 128 + 16 * D + 32) * 4;
   if (merge > bytes) bytes = merge;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, ST>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, ST, CLUSTER>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
     configured = true;
   }
-  fb_launch(attn_decode_kernel<D, ST>, dim3(p.n_seqs, p.Kh, p.splits), dim3(THREADS), bytes, stream, p);
+  const dim3 grid(p.n_seqs, p.Kh, p.splits);
+  if (CLUSTER)
+    fb_launch_cluster(attn_decode_kernel<D, ST, CLUSTER>, grid, dim3(THREADS), bytes, stream,
+                      (unsigned)p.splits, p);
+  else
+    fb_launch(attn_decode_kernel<D, ST, CLUSTER>, grid, dim3(THREADS), bytes, stream, p);
   return fb_check_launch("attention_decode");
+}
+
+// Several CTAs per (sequence, kv head) merge inside a cluster when the caller
+// gave no workspace, else through the workspace and the arrival counters.
+template <int D, int ST>
+int launch_decode(const AttnParams& p, cudaStream_t stream) {
+  if (p.splits > 1 && p.ws_o == nullptr) return launch_decode_as<D, ST, true>(p, stream);
+  return launch_decode_as<D, ST, false>(p, stream);
 }
 
 int check_common(const char* what, int n_seqs, int A, int Kh, int D, long long q_stride,
@@ -589,8 +686,10 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
   }
 }
 
-// One token per sequence. `splits` CTAs share each (sequence, kv head); with
-// splits > 1 the workspaces must hold n_seqs*Kh*splits*16*D and
+// One token per sequence. `splits` CTAs share each (sequence, kv head). Up to
+// 8 of them merge their partial results inside a thread-block cluster when no
+// workspace is given (ws_o, ws_ml, counters all null). With workspaces (any
+// split count) they must hold n_seqs*Kh*splits*16*D and
 // n_seqs*Kh*splits*32 floats, and `counters` n_seqs*Kh ints that are zero when
 // the call starts (the kernel leaves them zero again). `stages` (2 or 3) is the
 // number of page buffers per CTA. A sequence with kv_lens == 0 is padding: its
@@ -608,8 +707,10 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
                         v_cache, page_stride, head_stride);
   if (rc) return rc;
   FB_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: bad split count %d", splits);
-  FB_REQUIRE(splits == 1 || (ws_o && ws_ml && counters),
-             "attention_decode: split results need workspaces and counters");
+  FB_REQUIRE(splits == 1 || (ws_o && ws_ml && counters) ||
+                 (!ws_o && !ws_ml && !counters && splits <= MAX_CLUSTER),
+             "attention_decode: %d split results need workspaces and counters (up to %d merge "
+             "in a cluster without)", splits, MAX_CLUSTER);
   AttnParams p{};
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
@@ -618,6 +719,7 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.page_stride = page_stride; p.head_stride = head_stride;
   p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E;
   p.splits = splits; p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
+  p.next = next; p.next_bytes = next_bytes;
   FB_REQUIRE(stages == 2 || stages == 3, "attention_decode: %d page buffers (2 or 3)", stages);
   if (stages == 2) {
     switch (D) {

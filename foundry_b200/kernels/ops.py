@@ -699,17 +699,24 @@ def attention_prefill(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, 
     return out
 
 
+# Up to this many CTAs of a (sequence, kv head) merge their partial results
+# through distributed shared memory; more go through a workspace in global memory.
+DECODE_CLUSTER_MAX = 8
+DECODE_CLUSTER = _os.environ.get("FOUNDRY_B200_DECODE_CLUSTER", "1") != "0"
+
+
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
                      num_kv_heads, head_dim, scale, splits, stages: int = 3,
                      then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
-    over `splits` CTAs per (sequence, kv head); the CTA that finishes a pair
-    last merges its partial results. `then_reads`: weights to ask into L2 for
+    over `splits` CTAs per (sequence, kv head). Up to 8 form a thread-block
+    cluster and merge their partial results through each other's shared memory;
+    more write them to a workspace, and the CTA that finishes a pair last merges. `then_reads`: weights to ask into L2 for
     the kernel that follows (see `gemm_skinny`)."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
     n = kv_lens.numel()
     ws_o = ws_ml = counters = None
-    if splits > 1:
+    if splits > DECODE_CLUSTER_MAX or (splits > 1 and not DECODE_CLUSTER):
         ws_o = torch.empty(n * num_kv_heads * splits * 16 * head_dim, dtype=torch.float32,
                            device=q.device)
         ws_ml = torch.empty(n * num_kv_heads * splits * 32, dtype=torch.float32, device=q.device)
