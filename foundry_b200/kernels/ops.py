@@ -651,15 +651,11 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
 def decode_plan(pairs: int, pages: int):
     """(splits, page buffers) of decode attention for `pairs` (sequence, kv head)
     pairs of up to `pages` cache pages, as measured on B200 with head size 128
-    at 3,072 tokens of context: with two or more pairs per SM, whole ranges
-    and three page buffers per CTA (two CTAs per SM) stream at the memory's
-    rate; with fewer pairs the ranges are split until about 256 CTAs exist,
-    at most eightfold (every further split adds merge work), with two page
-    buffers so that three CTAs fit an SM."""
-    if pairs >= 2 * SM_COUNT:
-        return 1, 3
-    splits = max(1, min(8, pages, (256 + pairs // 2) // pairs))
-    return splits, 2
+    at 3,072 tokens of context. Three page buffers per CTA (two pages on their
+    way while one is multiplied), of which two CTAs fit an SM; ranges are split
+    while all CTAs stay resident at once (a second round of CTAs cost 10 us a
+    call), at most eightfold (one cluster)."""
+    return max(1, min(DECODE_CLUSTER_MAX, pages, 2 * SM_COUNT // max(pairs, 1))), 3
 
 
 TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prompt-attention kernel
