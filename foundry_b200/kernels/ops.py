@@ -45,6 +45,10 @@ _SIGNATURES = {
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                        c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
+    "fb_gemm_skinny_rope": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p,
+                            c_void_p, c_int, c_void_p, c_int, c_void_p, c_ll, c_void_p, c_void_p,
+                            c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int,
+                            c_void_p],
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
@@ -426,6 +430,57 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
           *_prefetch_range(then_reads), ksplit, M * N if ksplit > 1 else 0, warps, _stream(),
           tag=f"m{M} k{K} n{N}")
     return out
+
+
+def qkv_rope_fusable(x: torch.Tensor, w: torch.Tensor, rotary_dim: int, head_dim: int,
+                     k_cache: Optional[torch.Tensor]) -> bool:
+    """Whether `gemm_skinny_rope` takes this projection: bfloat16, few token
+    rows, and a rotation whose pairs fall into the kernel's 8-row halves."""
+    return (FUSE_QKV_ROPE and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and 0 < x.shape[0] <= SKINNY_ROWS and _tc_usable(x, w, x)
+            and rotary_dim % 16 == 0 and head_dim % 16 == 0
+            and (k_cache is None or k_cache.dtype == torch.bfloat16))
+
+
+def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
+                     seq_of_token: torch.Tensor, page_table: torch.Tensor, inv_freq: torch.Tensor,
+                     rotary_dim: int, k_cache: Optional[torch.Tensor],
+                     v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
+                     head_dim: int, ring_pages: int = 0, write_cache: bool = True,
+                     then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The fused q/k/v projection of up to 16 tokens, rotated and stored by the
+    product's epilogue: returns the rotated queries [T, heads * head_dim]; the
+    rotated keys and the values go into the cache pages (`rope_kv_write` has
+    the meaning of the arguments). `w` is [(heads + 2 kv_heads) * head_dim, K]."""
+    T, K = x.shape
+    if w.shape != ((num_heads + 2 * num_kv_heads) * head_dim, K):
+        raise KernelError(f"gemm_skinny_rope: w is {tuple(w.shape)} for {num_heads}+2x{num_kv_heads} "
+                          f"heads of {head_dim} and K={K}")
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_skinny_rope takes bfloat16 operands")
+    if positions.numel() != T or seq_of_token.numel() != T:
+        raise KernelError("gemm_skinny_rope: positions / seq_of_token do not cover the tokens")
+    if inv_freq.numel() * 2 != rotary_dim:
+        raise KernelError("gemm_skinny_rope: inv_freq does not hold rotary_dim / 2 entries")
+    q_out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    page_stride = head_stride = kp = vp = 0
+    if write_cache:
+        _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
+        page_stride, head_stride = k_cache.stride(0), k_cache.stride(1)
+        kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
+    _call("fb_gemm_skinny_rope", _dev(x, "x", contiguous=False), _rows(x, "x"),
+          _dev(w, "w", contiguous=False), _rows(w, "w"), T, K,
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+          _dev(inv_freq, "inv_freq", torch.float32) if rotary_dim else 0, rotary_dim,
+          q_out.data_ptr(), q_out.stride(0), kp, vp, page_stride, head_stride, ring_pages,
+          num_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
+          *_prefetch_range(then_reads), skinny_plan(w.shape[0], K, False)[1], _stream(),
+          tag=f"m{T} k{K} n{w.shape[0]}")
+    return q_out
+
+
+FUSE_QKV_ROPE = _os.environ.get("FOUNDRY_B200_FUSE_QKV_ROPE", "1") != "0"
 
 
 def skinny_plan(N: int, K: int, planes_ok: bool):

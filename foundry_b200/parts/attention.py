@@ -69,13 +69,20 @@ class GQAAttention(Part):
 
     # ------------------------------------------------------------------- run
     def forward(self, ctx, x: torch.Tensor, cache: KVView):
-        qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
         table = ctx.page_table(cache.group)
-        q = ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
-                              self.rotary_dim, cache.k, cache.v, self.num_heads,
-                              self.num_kv_heads, self.head_dim,
-                              ring_pages=cache.group.ring_pages, write_cache=cache.writes,
-                              dtype=x.dtype)
+        if ops.qkv_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k):
+            # a handful of tokens: projection, rotation and cache write in one kernel
+            q = ops.gemm_skinny_rope(x, self.qkv.weight, ctx.positions, ctx.seq_of_token, table,
+                                     self.inv_freq, self.rotary_dim, cache.k, cache.v,
+                                     self.num_heads, self.num_kv_heads, self.head_dim,
+                                     ring_pages=cache.group.ring_pages, write_cache=cache.writes)
+        else:
+            qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
+            q = ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
+                                  self.rotary_dim, cache.k, cache.v, self.num_heads,
+                                  self.num_kv_heads, self.head_dim,
+                                  ring_pages=cache.group.ring_pages, write_cache=cache.writes,
+                                  dtype=x.dtype)
         attn = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(ctx, q, attn, table, cache.k, cache.v, self.num_heads, self.num_kv_heads,
                       self.head_dim, self.scale, window=cache.group.window,

@@ -431,6 +431,81 @@ def test_rope_kv_write(ops, dtype, A, Kh, D, rot, source):
     assert float(k_cache.float().abs().sum(dim=(1, 3)).cpu()[mask].max()) == 0.0
 
 
+@pytest.mark.parametrize("A,Kh,D,rot", [(4, 2, 16, 16), (6, 3, 32, 32), (3, 1, 48, 32), (8, 2, 128, 128),
+                                        (2, 2, 64, 0), (5, 1, 80, 48)])
+@pytest.mark.parametrize("T", [6, 13])
+def test_gemm_skinny_rope(ops, A, Kh, D, rot, T):
+    """Projection, rotation and cache write in one kernel against the plain
+    formulas: far positions, a padding token, scattered pages, partial and
+    absent rotation; without cache writes only the queries appear."""
+    K = 264
+    positions = ([0, 1, 63, 64, 100000, 7] + list(range(200, 200 + T)))[:T]
+    seqs = ([0, 0, 1, 1, 2, -1] + [0] * T)[:T]
+    width = (A + 2 * Kh) * D
+    n_pages = 1600
+    table = torch.zeros(3, 1563, dtype=torch.int32)
+    table[0, 0], table[1, 0], table[1, 1], table[2, 100000 // 64] = 5, 9, 2, 11
+    table[0, 3] = 17  # positions 200.. of sequence 0
+    inv_freq = (10000.0 ** (-np.arange(0, rot, 2, dtype=np.float32) / max(rot, 1))).astype(np.float32)
+    x, w = rnd(T, K, dtype=torch.bfloat16), rnd(width, K, dtype=torch.bfloat16, scale=0.1, seed=4)
+    ref = (x.double() @ w.double().T).cpu()
+    k_cache = torch.zeros(n_pages, Kh, 64, D, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    args = (torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(seqs, dtype=torch.int32, device=DEV), table.to(DEV),
+            torch.from_numpy(inv_freq).to(DEV), rot)
+    q = ops.gemm_skinny_rope(x, w, *args, k_cache, v_cache, A, Kh, D,
+                             then_reads=rnd(8, 64, dtype=torch.bfloat16))
+    a, r = 2e-2, 8e-3
+    written = set()
+    for t in range(T):
+        if seqs[t] < 0:
+            continue
+        row = ref[t].view(A + 2 * Kh, D)
+        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot), a, r)
+        page = int(table[seqs[t], positions[t] // 64])
+        written.add((page, positions[t] % 64))
+        close(k_cache[page, :, positions[t] % 64], plain_rope(row[A:A + Kh], positions[t], inv_freq, rot), a, r)
+        close(v_cache[page, :, positions[t] % 64], row[A + Kh:], a, r)
+    mask = torch.ones(n_pages, 64, dtype=torch.bool)
+    for p, rr in written:
+        mask[p, rr] = False
+    for cache in (k_cache, v_cache):
+        assert float(cache.float().abs().sum(dim=(1, 3)).cpu()[mask].max()) == 0.0
+    # agrees with the two separate kernels to the rounding of their intermediate
+    qkv = torch.empty(T, width, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(x, w, qkv)
+    k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    q2 = ops.rope_kv_write(qkv, *args, k2, v2, A, Kh, D)
+    live = [t for t in range(T) if seqs[t] >= 0]
+    close(q[live], q2[live].double(), a, r)
+    close(k_cache, k2.double(), a, r)
+    close(v_cache, v2.double(), a, r)
+    # reading another layer's cache: no key or value is computed or stored
+    k_cache.zero_(), v_cache.zero_()
+    q3 = ops.gemm_skinny_rope(x, w, *args, k_cache, v_cache, A, Kh, D, write_cache=False)
+    assert torch.equal(q3[live], q[live])
+    assert float(k_cache.float().abs().max()) == 0.0 and float(v_cache.float().abs().max()) == 0.0
+
+
+def test_gemm_skinny_rope_ring_pages(ops):
+    """A windowed group's pages are a ring: position p lands in page slot (p / 64) % ring."""
+    A, Kh, D, K, ring = 2, 1, 32, 64, 3
+    positions, seqs = [64 * 7 + 5], [0]
+    table = torch.tensor([[4, 8, 6]], dtype=torch.int32, device=DEV)
+    inv_freq = torch.from_numpy((10000.0 ** (-np.arange(0, D, 2, dtype=np.float32) / D)).astype(np.float32)).to(DEV)
+    x, w = rnd(1, K, dtype=torch.bfloat16), rnd((A + 2 * Kh) * D, K, dtype=torch.bfloat16, scale=0.2, seed=4)
+    k_cache = torch.zeros(10, Kh, 64, D, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    ops.gemm_skinny_rope(x, w, torch.tensor(positions, dtype=torch.int32, device=DEV),
+                         torch.tensor(seqs, dtype=torch.int32, device=DEV), table, inv_freq, D,
+                         k_cache, v_cache, A, Kh, D, ring_pages=ring)
+    ref = (x.double() @ w.double().T).cpu().view(A + 2 * Kh, D)
+    page = int(table[0, 7 % ring])
+    close(v_cache[page, :, 5], ref[A + Kh:], 2e-2, 8e-3)
+    assert float(v_cache.float().abs().sum()) == pytest.approx(float(v_cache[page, :, 5].float().abs().sum()))
+
+
 # ------------------------------------------------------------------ sampling
 @pytest.mark.parametrize("V", [384, 5001, 128256])
 def test_select_tokens_greedy_first_index_wins(ops, V):
