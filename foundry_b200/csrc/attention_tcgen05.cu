@@ -12,7 +12,8 @@
 //
 // Roles of a CTA (192 threads):
 //   warp 0     one lane issues TMA loads: the query tile once, then a ring of
-//              three (K page, V page) stages;
+//              two K pages and a ring of two V pages (a K page is free again
+//              when its scores are computed, a V page one product later);
 //   warp 1     allocates tensor memory; one lane issues S = Q K^T (M 128, N 64)
 //              into one of two score buffers and O += P V (M 128, N D, V read
 //              MN-major straight from its [key, d] page) one page behind, so
@@ -26,6 +27,12 @@
 //              accumulator read back, rescaled and stored again.
 //   At the end the softmax warps read O, divide by the row sums and store.
 //
+// Shared memory (112 KB at head size 128) and tensor memory (256 columns) are
+// sized so that two CTAs share an SM: a row's softmax is one long dependent
+// chain per thread, and with a single CTA each scheduler has one softmax warp
+// and the tensor pipe idles four fifths of the time; the second CTA's warps
+// fill those gaps.
+//
 // Every wait on an mbarrier is bounded; a wait that runs out raises the CTA's
 // abort flag, all roles run out, tensor memory is freed, and the host can read
 // the place from `fb_attention_tc_status`.
@@ -37,7 +44,7 @@
 namespace {
 
 constexpr int BQ = 128;        // query rows per CTA = lanes of tensor memory
-constexpr int ST = 3;          // (K page, V page) stages
+constexpr int ST = 2;          // K stages, and V stages
 constexpr int THREADS = 192;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;  // the reference maximum moves in steps of 2^8 at least
@@ -63,11 +70,14 @@ struct FaSmem {
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int PAGE_BYTES = FB_PAGE * D * 2;       // one K or V page of one head
   static constexpr int P_BYTES = BQ * FB_PAGE * 2;
-  static constexpr int BYTES = Q_BYTES + 2 * ST * PAGE_BYTES + 2 * P_BYTES + 1024 + 256;
+  static constexpr int USED = Q_BYTES + 2 * ST * PAGE_BYTES + P_BYTES + 256;
+  // never three CTAs on an SM: they would need more tensor memory than it has
+  static constexpr int BYTES = USED > 77 * 1024 ? USED : 77 * 1024;
+  static_assert(BYTES <= (233472 - 2 * 1024) / 2, "two CTAs must fit an SM");
 };
 
 template <int D>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const FaParams p) {
@@ -76,21 +86,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   constexpr int KV_SUB = FB_PAGE * 128;        // bytes of one K or V sub-tile
   constexpr int TMEM_COLS = 256;               // 2 x 64 score columns + D output columns
   constexpr uint32_t O_COL = 128;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];  // swizzled tiles start on 1,024 bytes
+  uint8_t* base = smem_raw;
   uint8_t* sQ = base;
   uint8_t* sK = sQ + FaSmem<D>::Q_BYTES;                 // [ST][SUB][64 keys][64]
   uint8_t* sV = sK + ST * FaSmem<D>::PAGE_BYTES;         // [ST][SUB][64 keys][64]
-  uint8_t* sP = sV + ST * FaSmem<D>::PAGE_BYTES;         // [2][128 rows][64 keys]
-  uint64_t* bars = (uint64_t*)(sP + 2 * FaSmem<D>::P_BYTES);
+  uint8_t* sP = sV + ST * FaSmem<D>::PAGE_BYTES;         // [128 rows][64 keys]
+  uint64_t* bars = (uint64_t*)(sP + FaSmem<D>::P_BYTES);
   uint64_t* q_full = bars;
-  uint64_t* kv_full = bars + 1;        // [ST]
-  uint64_t* kv_empty = kv_full + ST;   // [ST]
-  uint64_t* s_full = kv_empty + ST;    // [2]
+  uint64_t* k_full = bars + 1;         // [ST]
+  uint64_t* v_full = k_full + ST;      // [ST]
+  uint64_t* k_empty = v_full + ST;     // [ST]
+  uint64_t* v_empty = k_empty + ST;    // [ST]
+  uint64_t* s_full = v_empty + ST;     // [2]
   uint64_t* s_empty = s_full + 2;      // [2]
-  uint64_t* p_full = s_empty + 2;      // [2]
-  uint64_t* p_empty = p_full + 2;      // [2]
-  uint64_t* pv_done = p_empty + 2;     // completes once per P.V product
+  uint64_t* p_full = s_empty + 2;      // completes once per page
+  uint64_t* pv_done = p_full + 1;      // completes once per P.V product
   uint64_t* o_final = pv_done + 1;     // completes once, after the last one
   uint32_t* tmem_slot = (uint32_t*)(o_final + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -98,8 +109,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    // later blocks of a sequence walk more pages: they are handed out first
-    int b = (int)(gridDim.x - 1 - blockIdx.x), s = 0;
+    // Later blocks of a sequence walk more pages: they are handed out first, and
+    // the heads are the fast grid index, so that the long blocks of every head
+    // start before any short one.
+    int b = (int)(gridDim.y - 1 - blockIdx.y), s = 0;
     for (; s < p.n_seqs; ++s) {
       const int nb = (p.cu_tokens[s + 1] - p.cu_tokens[s] + BQ - 1) / BQ;
       if (b < nb) break;
@@ -108,13 +121,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     s_info[0] = s < p.n_seqs ? s : -1;
     s_info[1] = b;
     mbar_init(q_full, 1);
-    for (int i = 0; i < ST; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+    for (int i = 0; i < ST; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+    }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);  // one arrival per softmax warp
-      mbar_init(&p_full[i], 4);
-      mbar_init(&p_empty[i], 1);
     }
+    mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     mbar_init(o_final, 1);
     *abort_flag = 0;
@@ -124,6 +139,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   const int seq = s_info[0];
   if (seq < 0) return;  // a block beyond the real count: nothing allocated yet
+  if (smem_u32(base) & 1023u) {  // the tiles' swizzle pattern assumes this alignment
+    if (threadIdx.x == 0 && atomicCAS(&g_status[0], 0, 1) == 0) {
+      g_status[1] = 20;
+      g_status[2] = (int)(blockIdx.x + gridDim.x * blockIdx.y);
+      g_status[3] = (int)(smem_u32(base) & 1023u);
+    }
+    return;
+  }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
@@ -137,7 +160,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const uint32_t tmem_base = *tmem_slot;
 
   const int row0 = s_info[1] * BQ;
-  const int head = blockIdx.y, kvh = head / (p.A / p.Kh);
+  const int head = blockIdx.x, kvh = head / (p.A / p.Kh);
   const int tok0 = p.cu_tokens[seq], q_len = p.cu_tokens[seq + 1] - tok0;
   const int kv_len = p.kv_lens[seq];
   const int pos0 = kv_len - q_len + row0;  // position of this block's first query
@@ -155,16 +178,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         tma_load_2d(sQ + sb * Q_SUB, &map_q, q_full, head * D + sb * 64, tok0 + row0);
       for (int j = 0; j < n_pages; ++j) {
         const int s = j % ST;
-        if (!mbar_wait(&kv_empty[s], (uint32_t)((j / ST) & 1) ^ 1u, abort_flag, 11, j)) break;
-        mbar_expect_tx(&kv_full[s], 2 * FaSmem<D>::PAGE_BYTES);
+        const uint32_t parity = (uint32_t)((j / ST) & 1) ^ 1u;
         const int page = pages[j];
+        if (!mbar_wait(&k_empty[s], parity, abort_flag, 11, j)) break;
+        mbar_expect_tx(&k_full[s], FaSmem<D>::PAGE_BYTES);
 #pragma unroll
-        for (int sb = 0; sb < SUB; ++sb) {
-          tma_load_3d(sK + s * FaSmem<D>::PAGE_BYTES + sb * KV_SUB, &map_k, &kv_full[s], sb * 64,
+        for (int sb = 0; sb < SUB; ++sb)
+          tma_load_3d(sK + s * FaSmem<D>::PAGE_BYTES + sb * KV_SUB, &map_k, &k_full[s], sb * 64,
                       kvh * FB_PAGE, page);
-          tma_load_3d(sV + s * FaSmem<D>::PAGE_BYTES + sb * KV_SUB, &map_v, &kv_full[s], sb * 64,
+        if (!mbar_wait(&v_empty[s], parity, abort_flag, 10, j)) break;
+        mbar_expect_tx(&v_full[s], FaSmem<D>::PAGE_BYTES);
+#pragma unroll
+        for (int sb = 0; sb < SUB; ++sb)
+          tma_load_3d(sV + s * FaSmem<D>::PAGE_BYTES + sb * KV_SUB, &map_v, &v_full[s], sb * 64,
                       kvh * FB_PAGE, page);
-        }
       }
     }
   } else if (warp == 1) {
@@ -177,7 +204,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         if (j < n_pages) {
           // S[j & 1] = Q K_j^T
           const int s = j % ST, b = j & 1;
-          ok = mbar_wait(&kv_full[s], (uint32_t)((j / ST) & 1), abort_flag, 13, j) &&
+          ok = mbar_wait(&k_full[s], (uint32_t)((j / ST) & 1), abort_flag, 13, j) &&
                mbar_wait(&s_empty[b], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 14, j);
           if (!ok) break;
           tc_fence_after();
@@ -190,21 +217,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
               umma(tmem_base + (uint32_t)(b * FB_PAGE), make_desc(q_addr + sb * Q_SUB + k * 32),
                    make_desc(k_addr + sb * KV_SUB + k * 32), idesc_qk, (sb | k) != 0 ? 1u : 0u);
           tc_commit(&s_full[b]);
+          tc_commit(&k_empty[s]);
         }
         if (j >= 1) {
           // O += P_{j-1} V_{j-1}, one page behind the scores
-          const int jj = j - 1, s = jj % ST, b = jj & 1;
-          ok = mbar_wait(&p_full[b], (uint32_t)((jj >> 1) & 1), abort_flag, 15, jj);
+          const int jj = j - 1, s = jj % ST;
+          ok = mbar_wait(p_full, (uint32_t)(jj & 1), abort_flag, 15, jj) &&
+               mbar_wait(&v_full[s], (uint32_t)((jj / ST) & 1), abort_flag, 9, jj);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t p_addr = smem_u32(sP + b * FaSmem<D>::P_BYTES);
+          const uint32_t p_addr = smem_u32(sP);
           const uint32_t v_addr = smem_u32(sV + s * FaSmem<D>::PAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // 16 keys per instruction: 32 bytes of P, 16 rows of V
             umma(tmem_base + O_COL, make_desc(p_addr + k * 32),
                  make_desc_mn(v_addr + k * 16 * 128, KV_SUB), idesc_pv, (jj | k) != 0 ? 1u : 0u);
-          tc_commit(&kv_empty[s]);
-          tc_commit(&p_empty[b]);
+          tc_commit(&v_empty[s]);
           tc_commit(pv_done);
           if (jj == n_pages - 1) tc_commit(o_final);
         }
@@ -259,17 +287,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         mx4[3] = fmaxf(mx4[3], sc[e + 3]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-      // P[b] was read by the product of page j - 2; after this wait at most one
-      // product (page j - 1) is still running
-      ok = mbar_wait(&p_empty[b], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 17, j);
+      // P was read by the product of page j - 1, which ran while this page's scores
+      // were fetched and their maximum taken
+      ok = mbar_wait(pv_done, (uint32_t)(j & 1) ^ 1u, abort_flag, 17, j);
       if (!ok) break;
       const bool grow = mx > m_ref + RESCALE_STEP;  // also the first page (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float corr = grow ? exp2f(m_ref - mx) : 1.0f;  // 0 on the first page
         if (j > 0) {
-          // the accumulator must be at rest: wait for the product of page j - 1
-          ok = mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, 18, j);
-          if (!ok) break;
+          // the accumulator is at rest: the product of page j - 1 is complete
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
@@ -287,7 +313,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       // probabilities against the reference maximum (at most 2^8), as a K-major tile
       // with the 128-byte swizzle: 16-byte chunk c of row r lands at chunk c ^ (r & 7)
-      uint8_t* prow = sP + b * FaSmem<D>::P_BYTES + row * 128;
+      uint8_t* prow = sP + row * 128;
       const float neg_ref = -m_ref;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -316,7 +342,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       fence_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[b]);
+      if (lane == 0) mbar_arrive(p_full);
     }
     // O / l
     if (ok) ok = mbar_wait(o_final, 0, abort_flag, 19, n_pages);
@@ -405,7 +431,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     if (e != cudaSuccess) return fb_fail(2, "attention_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  fb_launch(attn_prefill_tc_kernel<D>, dim3(q_blocks, p.A), dim3(THREADS), FaSmem<D>::BYTES, stream,
+  fb_launch(attn_prefill_tc_kernel<D>, dim3(p.A, q_blocks), dim3(THREADS), FaSmem<D>::BYTES, stream,
             mq, mk, mv, p);
   return fb_check_launch("attention_prefill_tc");
 }
