@@ -560,7 +560,7 @@ def _swapped_plan(M: int, N: int, K: int):
     bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     tiles = (N + 127) // 128
     kblocks = (K + 63) // 64
-    splits = max(1, min(kblocks // 4, (SM_COUNT + tiles // 2) // tiles))
+    splits = max(1, min(kblocks // 4, SM_COUNT // tiles))  # one CTA per SM: never a second round
     per = (kblocks + splits - 1) // splits
     return bn, (kblocks + per - 1) // per  # no empty split
 
