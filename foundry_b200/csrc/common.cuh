@@ -42,12 +42,17 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
 // the 3B decode step: when the long kernels triggered early too, blocks of later
 // kernels sat waiting on the SMs, held registers and shared memory that the
 // running kernel's next blocks needed, and the step took half as long again.
-// A kernel that can follow an early trigger reads what its predecessor wrote
-// with ordinary (coherent) loads only: pointers to such data carry no
-// `__restrict__` read-only promise and no `ld.global.nc`, because the writer
-// may still have been running when the reader's blocks were placed, and a
-// non-coherent load was seen to return the address's previous contents then. `fb_set_pdl(0)` switches the mark
-// off: launches then serialise as usual and the device call does nothing.
+// The prompt step lost too: with the persistent product or the prompt attention
+// triggering early, 12.1 ms became 13.0 to 13.8 ms (the successors' blocks wait
+// on the SMs beside the running kernel and slow it).
+// Every kernel reads what an earlier kernel wrote with ordinary (coherent)
+// loads only: pointers to such data carry no `__restrict__` read-only promise
+// and no `ld.global.nc`, because after an early trigger the writer may still
+// have been running when the reader's blocks were placed, and a non-coherent
+// load was seen to return the address's previous contents then. Only weights
+// and the step's description, which no kernel writes, keep the promise.
+// `fb_set_pdl(0)` switches the mark off: launches then serialise as usual and
+// the device calls do nothing.
 extern int g_fb_pdl;
 
 template <typename... KArgs, typename... Args>

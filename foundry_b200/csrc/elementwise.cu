@@ -76,7 +76,7 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v
 }
 
 template <typename TD, typename TO, int ITEMS>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* delta,
                                        int planes, long long plane_stride,
                                        const float* __restrict__ weight, TO* __restrict__ out,
                                        int H, float eps, float inv_h) {
@@ -129,7 +129,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
 }
 
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* delta,
                                    int planes, long long plane_stride,
                                    const float* __restrict__ weight, TO* __restrict__ out, int H,
                                    float eps, float inv_h) {
@@ -205,7 +205,7 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
 // up projection. Interleaved layout: column 2i holds gate i, column 2i+1 up i
 // (the layout the fused product epilogue uses).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I,
+__global__ void silu_mul_kernel(const T* gate_up, T* __restrict__ out, int I,
                                 size_t total, int interleaved) {
   fb_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -236,7 +236,7 @@ FB_API int fb_silu_mul(const void* gate_up, void* out, int dtype, int T, int I, 
 // ---------------------------------------------------------------- row gather
 // dst[r,:] = src[rows[r],:]; a negative row index gives a zero row.
 template <typename T>
-__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
+__global__ void gather_rows_kernel(const T* src, const int* __restrict__ rows,
                                    T* __restrict__ dst, int H) {
   fb_pdl_wait();
   const int r = blockIdx.x;
@@ -261,7 +261,7 @@ FB_API int fb_gather_rows(const void* src, int dtype, const int* rows, void* dst
 
 // ----------------------------------------------------------------------- cast
 template <typename TI, typename TO>
-__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+__global__ void cast_kernel(const TI* in, TO* __restrict__ out, size_t n) {
   fb_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
@@ -283,7 +283,7 @@ FB_API int fb_cast(const void* in, int in_dtype, void* out, int out_dtype, long 
 // out[i] = sum_s planes[s * plane_stride + i], planes in float32, summed in
 // plane order (a fixed order: the result does not depend on timing).
 template <typename TO>
-__global__ void sum_planes_kernel(const float* __restrict__ planes, int S, long long n,
+__global__ void sum_planes_kernel(const float* planes, int S, long long n,
                                   long long plane_stride, TO* __restrict__ out) {
   fb_pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;

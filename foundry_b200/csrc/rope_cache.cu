@@ -22,7 +22,7 @@
 // Rotated queries go to `q_out` (row stride q_stride), which may be `src`
 // itself when the types agree.
 template <typename TS, typename T>
-__global__ void rope_kv_write_kernel(const TS* __restrict__ src, long long src_stride, int planes,
+__global__ void rope_kv_write_kernel(const TS* src, long long src_stride, int planes,
                                      long long plane_stride, T* __restrict__ q_out,
                                      long long q_stride, const int* __restrict__ positions,
                                      const int* __restrict__ seq_of_token,

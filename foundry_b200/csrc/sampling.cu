@@ -31,7 +31,7 @@ __device__ __forceinline__ float uniform24(unsigned long long stream, unsigned l
 // temperature is 0. Block (r, c) scans chunk c of row r and leaves its best
 // (score, index); with one chunk per row it writes the token itself.
 __global__ void __launch_bounds__(1024)
-select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int V, int chunk,
+select_tokens_kernel(const float* logits, long long row_stride, int V, int chunk,
                      const float* __restrict__ temperature,
                      const long long* __restrict__ streams, const long long* __restrict__ steps,
                      float* __restrict__ part_val, int* __restrict__ part_idx,
@@ -95,8 +95,8 @@ select_tokens_kernel(const float* __restrict__ logits, long long row_stride, int
 }
 
 // One warp per row merges the chunk results (chunks <= 1024).
-__global__ void select_merge_kernel(const float* __restrict__ part_val,
-                                    const int* __restrict__ part_idx, int chunks,
+__global__ void select_merge_kernel(const float* part_val,
+                                    const int* part_idx, int chunks,
                                     int* __restrict__ out) {
   fb_pdl_wait();
   const int r = blockIdx.x, lane = threadIdx.x;
