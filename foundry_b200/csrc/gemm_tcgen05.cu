@@ -477,6 +477,297 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
+// ------------------------------------------------------------------------ pairs
+// The persistent product with two SMs on one tile (tcgen05 cta_group::2): a
+// cluster of two CTAs owns a 256 x BN tile. Each CTA loads its own 128 token
+// rows of A and its own half (BN / 2 weight rows) of B; one thread of the
+// first CTA (the leader) issues the MMAs for both, the hardware reads A and B
+// from both CTAs' shared memory and writes each CTA's 128 rows of D into that
+// CTA's tensor memory. What it buys: per 64-wide K step a CTA takes
+// (128 + BN / 2) x 128 bytes from L2 instead of (128 + BN) x 128 for BN x 2
+// tensor-core cycles, and the L2 -> SM rate (about 60 bytes per cycle and SM)
+// is what caps the one-CTA form.
+//
+// Protocol. Both CTAs' TMA loads of a stage complete on the LEADER's full
+// barrier (cp.async.bulk.tensor.cta_group::2 may name the peer's barrier;
+// no multicast), which the leader arms with the bytes of both. The leader's
+// commits arrive on both CTAs' barriers (tcgen05.commit ... multicast::cluster):
+// `empty` frees a stage in both, `acc_full` hands each CTA's epilogue its
+// accumulator. The epilogue warps of both CTAs arrive on the leader's
+// `acc_empty` (8 arrivals; the peer's through its cluster address). Tensor
+// memory is allocated per CTA, all 512 columns, so both bases are 0. Every wait
+// is bounded as elsewhere; both CTAs pass the same two cluster barriers on every
+// path, the second one before either frees its tensor memory or exits.
+
+template <int BN>
+struct SmemPair {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // All the shared memory a CTA can have (227 KB): the bytes a CTA has on their
+  // way from L2, over the latency of that way, is its intake, and the intake is
+  // what bounds these kernels.
+  static constexpr int BUDGET = 227 * 1024 - 1024 - 256;
+  static constexpr int STAGES = BUDGET / STAGE_BYTES > 12 ? 12 : BUDGET / STAGE_BYTES;
+  static constexpr int BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256;
+};
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster's shared-memory window, of `local` in CTA `rank`.
+__device__ __forceinline__ uint32_t cluster_address(const void* local, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(local)), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A tile load whose completion is counted on a barrier of the CTA pair (its
+// address in the cluster window), not necessarily this CTA's own.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map,
+                                                 uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives, when the MMAs issued so far are complete, on the barrier at this
+// shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster)
+               : "memory");
+}
+// mbar_wait for a barrier that the peer CTA arrives on: acquire at cluster scope.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag, int where, int kb) {
+  for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((spin & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (atomicCAS(&g_status[0], 0, 1) == 0) {
+    g_status[1] = where;
+    g_status[2] = (int)blockIdx.x;
+    g_status[3] = kb;
+  }
+  return false;
+}
+
+// tiles_a counts 256-row blocks of A. gridDim.x is even: CTAs 2c and 2c + 1 are
+// cluster c, which walks tiles c, c + clusters, ...
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, const GemmParams p, int tiles_a,
+                    int tiles_b) {
+  constexpr int STAGES = SmemPair<BN>::STAGES;
+  constexpr int TMEM_COLS = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + STAGES * SmemPair<BN>::STAGE_BYTES);  // used in the leader
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2], used in the leader
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const int cluster = (int)(blockIdx.x >> 1), clusters = (int)(gridDim.x >> 1);
+  const int total_tiles = tiles_a * tiles_b;
+  const int nkb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);  // the four epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_barrier();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint32_t full_leader = cluster_address(&full[0], 0);
+      // The first tile's first stages (all empty at the start): the operand that
+      // holds constants (weights) is requested before this kernel waits for the
+      // one before it, the other operand after.
+      const int early = (cluster < total_tiles) ? (nkb < STAGES ? nkb : STAGES) : 0;
+      const int fa = cluster % tiles_a, fb = cluster / tiles_a;
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a_dst = tiles + i * SmemPair<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + SmemPair<BN>::A_BYTES;
+        if (leader) mbar_expect_tx(&full[i], 2 * SmemPair<BN>::STAGE_BYTES);
+        const uint32_t bar = full_leader + (uint32_t)(i * 8);
+        if (p.constant_operand == 1)
+          tma_load_2d_pair(a_dst, &map_a, bar, i * BK, fa * 2 * BM + (int)rank * BM);
+        if (p.constant_operand == 2)
+          tma_load_2d_pair(b_dst, &map_b, bar, i * BK, fb * BN + (int)rank * (BN / 2));
+      }
+      fb_pdl_wait();
+      for (int i = 0; i < early; ++i) {
+        uint8_t* a_dst = tiles + i * SmemPair<BN>::STAGE_BYTES;
+        uint8_t* b_dst = a_dst + SmemPair<BN>::A_BYTES;
+        const uint32_t bar = full_leader + (uint32_t)(i * 8);
+        if (p.constant_operand != 1)
+          tma_load_2d_pair(a_dst, &map_a, bar, i * BK, fa * 2 * BM + (int)rank * BM);
+        if (p.constant_operand != 2)
+          tma_load_2d_pair(b_dst, &map_b, bar, i * BK, fb * BN + (int)rank * (BN / 2));
+      }
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster; tile < total_tiles && ok; tile += clusters) {
+        const int ta = tile % tiles_a, tb = tile / tiles_a;
+        for (int kb = (tile == cluster ? early : 0); kb < nkb; ++kb) {
+          const int use = it + kb;
+          const int s = use % STAGES;
+          const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, kb)) { ok = false; break; }
+          uint8_t* a_dst = tiles + s * SmemPair<BN>::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + SmemPair<BN>::A_BYTES;
+          if (leader) mbar_expect_tx(&full[s], 2 * SmemPair<BN>::STAGE_BYTES);
+          const uint32_t bar = full_leader + (uint32_t)(s * 8);
+          tma_load_2d_pair(a_dst, &map_a, bar, kb * BK, ta * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(b_dst, &map_b, bar, kb * BK, tb * BN + (int)rank * (BN / 2));
+        }
+        it += nkb;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc(2 * BM, BN);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int tile = cluster; tile < total_tiles && ok; tile += clusters, ++j) {
+        const int buf = j & 1;
+        ok = mbar_wait_cluster(&acc_empty[buf], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 4, j);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          const int use = it + kb;
+          const int s = use % STAGES;
+          const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
+          ok = mbar_wait_cluster(&full[s], phase, abort_flag, 2, kb);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * SmemPair<BN>::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + SmemPair<BN>::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_pair(d_tmem, make_desc(a_addr + k * UMMA_K * 2),
+                      make_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit_pair(&empty[s]);
+        }
+        if (!ok) break;
+        tc_commit_pair(&acc_full[buf]);
+        it += nkb;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    float* out_f = (float*)p.out;
+    __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
+    constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
+    const uint32_t acc_empty_leader = cluster_address(&acc_empty[0], 0);
+    fb_pdl_wait();
+    int j = 0;
+    bool ok = true;
+    for (int tile = cluster; tile < total_tiles && ok; tile += clusters, ++j) {
+      const int ta = tile % tiles_a, tb = tile / tiles_a;
+      const int buf = j & 1;
+      ok = mbar_wait(&acc_full[buf], (uint32_t)((j >> 1) & 1), abort_flag, 3, j);
+      if (!ok) break;
+      tc_fence_after();
+      const long long i_global = (long long)ta * 2 * BM + (long long)rank * BM + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += CHUNK) {
+        float v[CHUNK];
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c);
+        if constexpr (CHUNK == 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+        } else {
+          uint32_t r[16];
+          tmem_ld16(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
+        }
+        store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+      }
+      // this warp has read its lanes of the accumulator: tell the leader's MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader + (uint32_t)(buf * 8));
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  cluster_barrier();  // nothing of the peer's may still be on its way to this CTA
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------- host: tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -589,6 +880,44 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
   return fb_check_launch("gemm_tc_persistent");
 }
 
+template <int BN>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_a,
+                int tiles_b, cudaStream_t stream) {
+  static int clusters_max = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SmemPair<BN>::BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  if (clusters_max == 0) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemPair<BN>::BYTES);
+    if (e != cudaSuccess) return fb_fail(2, "gemm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
+    cfg.gridDim = dim3(sm_count() / 2 * 2);
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<BN>, &cfg);
+    if (e != cudaSuccess || n <= 0)
+      return fb_fail(2, "gemm_tc: no CTA pair of this kernel fits the device (%s)",
+                     cudaGetErrorString(e));
+    clusters_max = n;
+  }
+  const int total = tiles_a * tiles_b;
+  const int clusters = total < clusters_max ? total : clusters_max;
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.numAttrs = g_fb_pdl ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN>, ma, mb, p, tiles_a, tiles_b);
+  return fb_check_launch("gemm_tc_pair");
+}
+
 }  // namespace
 
 // out = A * B^T in the layout the strides give; see the file header.
@@ -600,7 +929,8 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 // constant_operand names the operand (1: a, 2: b, 0: none) that no earlier kernel
 // in the stream writes (weights); its first loads do not wait for that kernel.
 // persistent 1 runs one CTA per SM over all tiles with two accumulators in
-// tensor memory (for many token rows; one split).
+// tensor memory (for many token rows; one split); persistent 2 does the same
+// with two SMs on each 256 x bn tile (cta_group::2).
 // epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
 // pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
 // dimension must be 1 and then indexes pairs.
@@ -634,6 +964,27 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   if (rc) return rc;
   dim3 grid((rows_a + BM - 1) / BM, (rows_b + bn - 1) / bn, splits);
   FB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid too large");
+  if (persistent == 2) {
+    // two SMs per tile: A in blocks of 256 rows, each CTA loads half of a B tile
+    FB_REQUIRE(splits == 1, "gemm_tc: the paired form takes one split");
+    rc = make_map(&mb, b, rows_b, K, ldb, bn / 2);
+    if (rc) return rc;
+    const int pairs_a = (rows_a + 2 * BM - 1) / (2 * BM);
+    switch (bn) {
+      case 128: return launch_pair<128>(ma, mb, p, pairs_a, grid.y, stream);
+      case 144: return launch_pair<144>(ma, mb, p, pairs_a, grid.y, stream);
+      case 160: return launch_pair<160>(ma, mb, p, pairs_a, grid.y, stream);
+      case 176: return launch_pair<176>(ma, mb, p, pairs_a, grid.y, stream);
+      case 192: return launch_pair<192>(ma, mb, p, pairs_a, grid.y, stream);
+      case 208: return launch_pair<208>(ma, mb, p, pairs_a, grid.y, stream);
+      case 224: return launch_pair<224>(ma, mb, p, pairs_a, grid.y, stream);
+      case 240: return launch_pair<240>(ma, mb, p, pairs_a, grid.y, stream);
+      case 256: return launch_pair<256>(ma, mb, p, pairs_a, grid.y, stream);
+      default:
+        return fb_fail(1, "gemm_tc: the paired form takes tiles 128..256 (steps of 16) wide, "
+                          "not %d", bn);
+    }
+  }
   if (persistent) {
     FB_REQUIRE(splits == 1, "gemm_tc: the persistent form takes one split");
     switch (bn) {

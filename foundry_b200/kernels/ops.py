@@ -368,11 +368,13 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
 SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
 # many token rows: one CTA per SM walks the tiles, two accumulators in tensor memory
 PERSISTENT = _os.environ.get("FOUNDRY_B200_PERSISTENT", "1") != "0"
+# two SMs on one 256-row tile (tcgen05 cta_group::2) for more than 128 token rows
+PAIRED = _os.environ.get("FOUNDRY_B200_PAIRED", "1") != "0"
 
 
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
             bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0,
-            constant_operand: int = 0, persistent: bool = False) -> None:
+            constant_operand: int = 0, persistent: int = 0) -> None:
     """Tensor-core product D[i,j] = sum_k a[i,k] b[j,k] written to
     out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu."""
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
@@ -383,7 +385,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
-          constant_operand, 1 if persistent else 0, _stream(),
+          constant_operand, int(persistent), _stream(),
           tag=f"a{a.shape[0]} b{b.shape[0]} k{a.shape[1]} tile{bn} splits{splits}")
 
 
@@ -583,13 +585,33 @@ def prompt_tile_width(M: int, N: int) -> int:
     return best
 
 
+def prompt_plan(M: int, N: int):
+    """(tile width, form) of the product for more than 128 token rows: form 2
+    pairs two SMs on tiles of 256 token rows (a CTA then takes half of each
+    weight tile from L2), form 1 runs one CTA per SM on 128-row tiles, form 0
+    one CTA per tile. Paired: the widest tile among those with the fewest
+    rounds over the 74 CTA pairs (measured at 2,048 rows, the time of a round
+    hardly depends on the width between 176 and 256)."""
+    if PAIRED and PERSISTENT and N >= 128:
+        blocks = (M + 255) // 256
+        pairs = SM_COUNT // 2
+        best, best_rounds = 256, None
+        for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
+            rounds = (blocks * ((N + bn - 1) // bn) + pairs - 1) // pairs
+            if best_rounds is None or rounds < best_rounds:
+                best, best_rounds = bn, rounds
+        return best, 2
+    return prompt_tile_width(M, N), 1 if PERSISTENT else 0
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
               out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
               then_reads: Optional[torch.Tensor] = None):
     """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
 
     Up to 16 rows: the weight-streaming kernel. More than 128 rows: token rows
-    fill the 128-row operand, weights the other (256 wide). In between: swapped, the weights fill the 128-row operand and
+    fill the 128-row operand (256 rows over a pair of SMs), weights the other
+    (up to 256 wide), see `prompt_plan`. In between: swapped, the weights fill the 128-row operand and
     stream through once, the tokens are the narrow operand; K is split over
     CTAs until the grid covers the SMs, each split writing a float32 plane.
     With `allow_planes` the planes are returned as `Planes` for a consumer that
@@ -620,8 +642,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if M > 128:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        bn = prompt_tile_width(M, N)
-        gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=PERSISTENT)
+        bn, form = prompt_plan(M, N)
+        gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=form)
         return out
     bn, splits = _swapped_plan(M, N, K)
     if splits == 1:
@@ -662,9 +684,9 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         return gemm_skinny(x, w_pairs, out, epilogue=1, then_reads=then_reads,
                            warps=skinny_plan(two_i, K, False)[1])
     if M > 128:
-        bn = prompt_tile_width(M, two_i)
+        bn, form = prompt_plan(M, two_i)
         gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2,
-                persistent=PERSISTENT)
+                persistent=form)
     else:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         gemm_tc(w_pairs, x, out, 1, out.stride(0), bn, epilogue=1, constant_operand=1)

@@ -611,6 +611,25 @@ def test_gemm_bf16_few_rows_few_features_shares_k(ops):
     close(plain, want, 2e-4 * math.sqrt(2048) + 1e-2, 8e-3)
 
 
+@pytest.mark.parametrize("bn", [128, 144, 160, 176, 192, 208, 224, 240, 256])
+@pytest.mark.parametrize("rows_a,rows_b,K", [(300, 700, 264), (2048, 1024, 512), (130, 70, 64),
+                                              (1000, 5000, 72), (257, 130, 4104)])
+def test_gemm_tensor_core_paired(ops, bn, rows_a, rows_b, K):
+    """Two SMs on one 256-row tile (cta_group::2): more tiles than CTA pairs and
+    fewer, a second CTA whose rows or weight half lie wholly outside, ragged
+    edges, short and long K loops; with and without the SiLU-mul epilogue."""
+    a, b = rnd(rows_a, K, dtype=torch.bfloat16, scale=0.5), rnd(rows_b, K, dtype=torch.bfloat16, scale=0.5, seed=6)
+    want = a.double() @ b.double().T
+    out = torch.full((rows_a, rows_b), 3.0, device=DEV)
+    ops.gemm_tc(a, b, out, rows_b, 1, bn, persistent=2, constant_operand=2)
+    close(out, want, 2e-4 * math.sqrt(K), 1e-5)
+    act = torch.full((rows_a, rows_b // 2), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(a, b, act, rows_b // 2, 1, bn, epilogue=1, persistent=2, constant_operand=2)
+    g, u = want[:, 0::2], want[:, 1::2]
+    close(act, g / (1 + torch.exp(-g)) * u, 3e-2, 1e-2)
+    assert ops.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("bn", [64, 128, 144, 176, 192, 208, 240, 256])
 @pytest.mark.parametrize("rows_a,rows_b,K", [(300, 700, 264), (2048, 1024, 512), (130, 70, 64),
                                               (1000, 5000, 72)])
