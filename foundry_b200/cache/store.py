@@ -51,6 +51,7 @@ class KVGroup:
         self.storage = torch.zeros(
             (len(entries), page_count, 2, request.kv_heads, PAGE, request.head_dim),
             dtype=dtype, device=device)
+        self._views: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     @property
     def ring_pages(self) -> int:
@@ -61,8 +62,11 @@ class KVGroup:
         return self.request.window or 0
 
     def kv(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        block = self.storage[self.index_of[entry]]
-        return block[:, 0], block[:, 1]
+        views = self._views.get(entry)
+        if views is None:  # the views never change: made once per entry
+            block = self.storage[self.index_of[entry]]
+            views = self._views[entry] = (block[:, 0], block[:, 1])
+        return views
 
     def bytes_per_token(self) -> int:
         r = self.request
