@@ -14,7 +14,6 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..cache.pages import PAGE, pages_for
 from ..cache.store import KVGroup, SequenceCache
 
 

@@ -22,7 +22,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..cache.pages import PAGE, pages_for
+from ..cache.pages import PAGE
 from ..kernels import ops
 from ..sampling.params import SamplingParams
 from .context import StepContext

@@ -9,8 +9,7 @@ lengths and one shared position.
 """
 from __future__ import annotations
 
-import os
-from typing import Dict, List, Optional, Sequence, Union
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -20,7 +19,7 @@ from ..config.spec import ModelSpec
 from ..sampling import Sampler, SamplingParams
 from ..weights.safetensors_io import WeightFiles
 from . import generate as loop
-from .context import SequenceStep, StepContext, build_context
+from .context import SequenceStep, build_context
 from .decode import DecodeRunner, DecodeSession
 from .model import Model
 

@@ -8,7 +8,7 @@ names no separate head, model.rs:62). The residual stream is float32.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Mapping, Optional
+from typing import Dict, Mapping, Optional
 
 import torch
 

@@ -17,7 +17,7 @@ import torch
 
 from ..config.spec import LayerSpec
 from ..weights.loader import ExpectedTensor
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Fetch, Part, first_weight_of,
+from .base import (FEED_FORWARDS, MIXERS, NORMS, Fetch, Part, first_weight_of,
                    register_block)
 
 

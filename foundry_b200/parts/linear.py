@@ -7,7 +7,7 @@ them; the tensor names in the files stay the separate Hugging Face ones.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 

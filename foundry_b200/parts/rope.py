@@ -17,7 +17,6 @@ ones by `factor`, and blends between the two bands:
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import numpy as np
 import torch

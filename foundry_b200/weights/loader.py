@@ -15,8 +15,8 @@ float32, which is exact for bfloat16 values.
 from __future__ import annotations
 
 import fnmatch
-from dataclasses import dataclass, field
-from typing import Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import List, Mapping, Sequence, Tuple
 
 import torch
 

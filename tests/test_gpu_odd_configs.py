@@ -4,7 +4,6 @@ attention does not build (48, 80, 96), one kv head for all heads, as many kv
 heads as heads, widths, feed-forward widths and vocabularies that are odd or
 no multiple of 8 (which sends products to the CUDA-core kernel), a single
 layer, a large eps, partial last pages."""
-import numpy as np
 import pytest
 
 import plain_llama as plain

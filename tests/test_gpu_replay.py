@@ -11,7 +11,6 @@ import sys
 
 import numpy as np
 import pytest
-import torch
 
 import plain_llama as plain
 import tiny

@@ -13,7 +13,7 @@ import tiny
 from foundry_b200.config import LlamaConfig
 from foundry_b200.engine.model import expected_tensors
 from foundry_b200.models.llama import build_llama_spec
-from foundry_b200.weights import (ExpectedTensor, WeightFiles, WeightsMismatch, check_against,
+from foundry_b200.weights import (WeightFiles, WeightsMismatch, check_against,
                                   save_file, stored_to_run_dtype, write_model_folder)
 from foundry_b200.weights import safetensors_io as sio
 from foundry_b200.weights.random_init import random_tensors

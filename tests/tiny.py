@@ -5,9 +5,6 @@ count and grouping, head size, feed-forward width (176 is no power of two),
 vocabulary, eps, theta, frequency scaling, tied or separate output head.
 Tiny B's 16 frequencies fall into all three bands of the llama3 scaling.
 """
-import json
-import os
-
 import numpy as np
 import torch
 
