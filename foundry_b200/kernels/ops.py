@@ -150,11 +150,13 @@ def add_launches(n: int) -> None:
 add_graph_launches = add_launches
 
 
-def _call(name: str, *args, tag: str = "") -> None:
+def _call(name: str, *args, tag=None) -> None:
+    """Launch `name`. `tag` is (format, values...) naming the shape for the
+    profiler; it is formatted only when a profile is being taken."""
     _COUNT[0] += 1
     prof = PROFILER
     if prof.mode is not None:
-        key = name[3:] + (" " + tag if tag else "")
+        key = name[3:] + (" " + tag[0].format(*tag[1:]) if tag else "")
         prof.count(key)
         if prof.mode == "kernels" and not torch.cuda.is_current_stream_capturing():
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -368,7 +370,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
     _call("fb_gemm_simt", _dev(x, "x", contiguous=False), _dev(w, "w", contiguous=False),
           _dev(out, "out", contiguous=False), M, N, K, _rows(x, "x"), _rows(w, "w"),
           _rows(out, "out"), code_of(x.dtype), code_of(out.dtype), _stream(),
-          tag=f"m{M} k{K} n{N}")
+          tag=("m{} k{} n{}", M, K, N))
     return out
 
 
@@ -393,7 +395,7 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           _dev(out, "out", contiguous=False), stride_a, stride_b,
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
           constant_operand, int(persistent), _stream(),
-          tag=f"a{a.shape[0]} b{b.shape[0]} k{a.shape[1]} tile{bn} splits{splits}")
+          tag=("a{} b{} k{} tile{} splits{}", a.shape[0], b.shape[0], a.shape[1], bn, splits))
 
 
 # Bytes of the next kernel's weights that a single-token-step kernel asks into
@@ -437,7 +439,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
           _rows(out, "out") if ksplit == 1 else N, 1 if out.dtype == torch.float32 else 0,
           M, N, K, epilogue,
           *_prefetch_range(then_reads), ksplit, M * N if ksplit > 1 else 0, warps, _stream(),
-          tag=f"m{M} k{K} n{N}")
+          tag=("m{} k{} n{}", M, K, N))
     return out
 
 
@@ -485,7 +487,7 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
           q_out.data_ptr(), q_out.stride(0), kp, vp, page_stride, head_stride, ring_pages,
           num_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
           *_prefetch_range(then_reads), skinny_plan(w.shape[0], K, False)[1], _stream(),
-          tag=f"m{T} k{K} n{w.shape[0]}")
+          tag=("m{} k{} n{}", T, K, w.shape[0]))
     return q_out
 
 
