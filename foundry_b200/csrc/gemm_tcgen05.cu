@@ -39,6 +39,12 @@ struct GemmParams {
   int out_f32;                // 1: float32 output, 0: bfloat16
   int constant_operand;       // 1: A holds constants (weights), 2: B does, 0: neither
   int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs
+  // paired form only: the tiles of the last, partly filled round are shared along K
+  int full_tiles;             // tiles [0, full_tiles) are computed whole
+  int tail_splits;            // K shares of every later tile (1: whole too)
+  int tail_kblocks;           // K blocks per share
+  float* partial;             // float32 partial sums of the shares (layout: see the kernel)
+  int* tail_counters;         // [tail tile][8]: shares delivered per (CTA of the pair, epilogue warp)
 };
 
 // Stores CHUNK consecutive accumulator columns (j0 .. j0 + CHUNK) of row
@@ -582,8 +588,36 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   return false;
 }
 
+constexpr int MAX_TAIL_SHARES = 4;
+
+// One piece of work of a CTA pair: a tile, whole (share < 0) or one share of its K.
+struct PairUnit {
+  int ta, tb, kb0, kb1, share, tail_tile;
+};
+__device__ __forceinline__ PairUnit pair_unit(const GemmParams& p, int u, int tiles_a, int nkb) {
+  PairUnit w;
+  int tile = u;
+  w.share = -1; w.tail_tile = 0; w.kb0 = 0; w.kb1 = nkb;
+  if (u >= p.full_tiles && p.tail_splits > 1) {
+    const int v = u - p.full_tiles;
+    w.tail_tile = v / p.tail_splits;
+    w.share = v - w.tail_tile * p.tail_splits;
+    tile = p.full_tiles + w.tail_tile;
+    w.kb0 = w.share * p.tail_kblocks;
+    w.kb1 = min(nkb, w.kb0 + p.tail_kblocks);
+  }
+  w.ta = tile % tiles_a;
+  w.tb = tile / tiles_a;
+  return w;
+}
+
 // tiles_a counts 256-row blocks of A. gridDim.x is even: CTAs 2c and 2c + 1 are
-// cluster c, which walks tiles c, c + clusters, ...
+// cluster c, which walks the units c, c + clusters, ... A unit is a whole tile,
+// or, for the tiles of the last round when they would leave most pairs idle, one
+// of `tail_splits` shares of a tile's K. A share's accumulator goes to the
+// float32 workspace; the epilogue warp that delivers a tile's last share (an
+// atomic counter per tile, CTA and warp, no waiting) sums the shares in share
+// order and runs the usual epilogue on the sum.
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -604,8 +638,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t rank = cluster_cta_rank();
   const bool leader = rank == 0;
   const int cluster = (int)(blockIdx.x >> 1), clusters = (int)(gridDim.x >> 1);
-  const int total_tiles = tiles_a * tiles_b;
   const int nkb = (p.K + BK - 1) / BK;
+  const int n_tiles = tiles_a * tiles_b;
+  const int total_units =
+      p.tail_splits > 1 ? p.full_tiles + (n_tiles - p.full_tiles) * p.tail_splits : n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -640,34 +676,37 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       // The first tile's first stages (all empty at the start): the operand that
       // holds constants (weights) is requested before this kernel waits for the
       // one before it, the other operand after.
-      const int early = (cluster < total_tiles) ? (nkb < STAGES ? nkb : STAGES) : 0;
-      const int fa = cluster % tiles_a, fb = cluster / tiles_a;
+      const PairUnit first = pair_unit(p, cluster < total_units ? cluster : 0, tiles_a, nkb);
+      const int first_kb = first.kb1 - first.kb0;
+      const int early = (cluster < total_units) ? (first_kb < STAGES ? first_kb : STAGES) : 0;
       for (int i = 0; i < early; ++i) {
         uint8_t* a_dst = tiles + i * SmemPair<BN>::STAGE_BYTES;
         uint8_t* b_dst = a_dst + SmemPair<BN>::A_BYTES;
         if (leader) mbar_expect_tx(&full[i], 2 * SmemPair<BN>::STAGE_BYTES);
         const uint32_t bar = full_leader + (uint32_t)(i * 8);
+        const int k = (first.kb0 + i) * BK;
         if (p.constant_operand == 1)
-          tma_load_2d_pair(a_dst, &map_a, bar, i * BK, fa * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(a_dst, &map_a, bar, k, first.ta * 2 * BM + (int)rank * BM);
         if (p.constant_operand == 2)
-          tma_load_2d_pair(b_dst, &map_b, bar, i * BK, fb * BN + (int)rank * (BN / 2));
+          tma_load_2d_pair(b_dst, &map_b, bar, k, first.tb * BN + (int)rank * (BN / 2));
       }
       fb_pdl_wait();
       for (int i = 0; i < early; ++i) {
         uint8_t* a_dst = tiles + i * SmemPair<BN>::STAGE_BYTES;
         uint8_t* b_dst = a_dst + SmemPair<BN>::A_BYTES;
         const uint32_t bar = full_leader + (uint32_t)(i * 8);
+        const int k = (first.kb0 + i) * BK;
         if (p.constant_operand != 1)
-          tma_load_2d_pair(a_dst, &map_a, bar, i * BK, fa * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(a_dst, &map_a, bar, k, first.ta * 2 * BM + (int)rank * BM);
         if (p.constant_operand != 2)
-          tma_load_2d_pair(b_dst, &map_b, bar, i * BK, fb * BN + (int)rank * (BN / 2));
+          tma_load_2d_pair(b_dst, &map_b, bar, k, first.tb * BN + (int)rank * (BN / 2));
       }
       int it = 0;
       bool ok = true;
-      for (int tile = cluster; tile < total_tiles && ok; tile += clusters) {
-        const int ta = tile % tiles_a, tb = tile / tiles_a;
-        for (int kb = (tile == cluster ? early : 0); kb < nkb; ++kb) {
-          const int use = it + kb;
+      for (int u = cluster; u < total_units && ok; u += clusters) {
+        const PairUnit w = pair_unit(p, u, tiles_a, nkb);
+        for (int kb = w.kb0 + (u == cluster ? early : 0); kb < w.kb1; ++kb) {
+          const int use = it + (kb - w.kb0);
           const int s = use % STAGES;
           const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
           if (!mbar_wait(&empty[s], phase ^ 1u, abort_flag, 1, kb)) { ok = false; break; }
@@ -675,10 +714,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           uint8_t* b_dst = a_dst + SmemPair<BN>::A_BYTES;
           if (leader) mbar_expect_tx(&full[s], 2 * SmemPair<BN>::STAGE_BYTES);
           const uint32_t bar = full_leader + (uint32_t)(s * 8);
-          tma_load_2d_pair(a_dst, &map_a, bar, kb * BK, ta * 2 * BM + (int)rank * BM);
-          tma_load_2d_pair(b_dst, &map_b, bar, kb * BK, tb * BN + (int)rank * (BN / 2));
+          tma_load_2d_pair(a_dst, &map_a, bar, kb * BK, w.ta * 2 * BM + (int)rank * BM);
+          tma_load_2d_pair(b_dst, &map_b, bar, kb * BK, w.tb * BN + (int)rank * (BN / 2));
         }
-        it += nkb;
+        it += w.kb1 - w.kb0;
       }
     }
   } else if (warp == 1) {
@@ -687,14 +726,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       constexpr uint32_t idesc = make_idesc(2 * BM, BN);
       int it = 0, j = 0;
       bool ok = true;
-      for (int tile = cluster; tile < total_tiles && ok; tile += clusters, ++j) {
+      for (int u = cluster; u < total_units && ok; u += clusters, ++j) {
+        const PairUnit w = pair_unit(p, u, tiles_a, nkb);
         const int buf = j & 1;
         ok = mbar_wait_cluster(&acc_empty[buf], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 4, j);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < nkb; ++kb) {
-          const int use = it + kb;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          const int use = it + (kb - w.kb0);
           const int s = use % STAGES;
           const uint32_t phase = (uint32_t)(use / STAGES) & 1u;
           ok = mbar_wait_cluster(&full[s], phase, abort_flag, 2, kb);
@@ -705,12 +745,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_pair(d_tmem, make_desc(a_addr + k * UMMA_K * 2),
-                      make_desc(b_addr + k * UMMA_K * 2), idesc, (kb | k) != 0 ? 1u : 0u);
+                      make_desc(b_addr + k * UMMA_K * 2), idesc,
+                      (kb != w.kb0 || k != 0) ? 1u : 0u);
           tc_commit_pair(&empty[s]);
         }
         if (!ok) break;
         tc_commit_pair(&acc_full[buf]);
-        it += nkb;
+        it += w.kb1 - w.kb0;
       }
     }
   } else {
@@ -723,13 +764,24 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     fb_pdl_wait();
     int j = 0;
     bool ok = true;
-    for (int tile = cluster; tile < total_tiles && ok; tile += clusters, ++j) {
-      const int ta = tile % tiles_a, tb = tile / tiles_a;
+    for (int u = cluster; u < total_units && ok; u += clusters, ++j) {
+      const PairUnit w = pair_unit(p, u, tiles_a, nkb);
+      const int ta = w.ta, tb = w.tb;
       const int buf = j & 1;
       ok = mbar_wait(&acc_full[buf], (uint32_t)((j >> 1) & 1), abort_flag, 3, j);
       if (!ok) break;
       tc_fence_after();
-      const long long i_global = (long long)ta * 2 * BM + (long long)rank * BM + quarter * 32 + lane;
+      const int row_in_tile = (int)rank * BM + quarter * 32 + lane;
+      const long long i_global = (long long)ta * 2 * BM + row_in_tile;
+      // a share's sums go to the workspace instead of the output
+      // A share's sums go to the workspace instead of the output. Its layout is this
+      // kernel's own: per (tile, share, CTA, warp) a block of BN / 4 groups of 32
+      // float4, group g holding columns 4g..4g+3 of the warp's 32 rows, so that a warp
+      // writes and later reads 512 contiguous bytes per instruction.
+      float4* mine = w.share < 0 ? nullptr
+                                 : reinterpret_cast<float4*>(p.partial) +
+                                       (((size_t)(w.tail_tile * p.tail_splits + w.share) * 8 +
+                                         rank * 4 + quarter) * (BN / 4)) * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < BN; c += CHUNK) {
         float v[CHUNK];
@@ -748,12 +800,65 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
           for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
         }
-        store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+        if (mine == nullptr) {
+          store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+        } else {
+#pragma unroll
+          for (int e = 0; e < CHUNK; e += 4)
+            mine[(size_t)((c + e) / 4) * 32] = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+        }
       }
       // this warp has read its lanes of the accumulator: tell the leader's MMA warp
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader + (uint32_t)(buf * 8));
+      if (mine != nullptr) {
+        // publish this warp's 32 rows of the share; the warp that completes the set
+        // (the same rows of every share) sums them and stores the result
+        __threadfence();
+        __syncwarp();
+        int before = 0;
+        int* counter = p.tail_counters + w.tail_tile * 8 + (int)rank * 4 + quarter;
+        if (lane == 0) before = atomicAdd(counter, 1);
+        before = __shfl_sync(0xffffffffu, before, 0);
+        if (before == p.tail_splits - 1) {
+          __threadfence();
+          const float4* base = reinterpret_cast<const float4*>(p.partial) +
+                               (((size_t)(w.tail_tile * p.tail_splits) * 8 + rank * 4 + quarter) *
+                                (BN / 4)) * 32 + lane;
+          const size_t share_stride = (size_t)8 * (BN / 4) * 32;  // float4s between shares
+#pragma unroll 1
+          for (int c = 0; c < BN; c += CHUNK) {
+            // all shares' loads of this chunk are issued before the first is used:
+            // one warp reads the whole 32 x BN x shares block, and what it has in
+            // flight decides how long that takes
+            float4 q[MAX_TAIL_SHARES][CHUNK / 4];
+#pragma unroll
+            for (int sh = 0; sh < MAX_TAIL_SHARES; ++sh) {
+              if (sh < p.tail_splits) {
+                const float4* src = base + sh * share_stride + (size_t)(c / 4) * 32;
+#pragma unroll
+                for (int e = 0; e < CHUNK / 4; ++e) q[sh][e] = __ldcg(src + (size_t)e * 32);
+              }
+            }
+            float v[CHUNK];
+#pragma unroll
+            for (int e = 0; e < CHUNK; ++e) v[e] = 0.f;
+#pragma unroll
+            for (int sh = 0; sh < MAX_TAIL_SHARES; ++sh) {
+              if (sh < p.tail_splits) {
+#pragma unroll
+                for (int e = 0; e < CHUNK / 4; ++e) {
+                  v[4 * e] += q[sh][e].x; v[4 * e + 1] += q[sh][e].y;
+                  v[4 * e + 2] += q[sh][e].z; v[4 * e + 3] += q[sh][e].w;
+                }
+              }
+            }
+            store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+          }
+          if (lane == 0) *counter = 0;  // as the next call expects it
+        }
+      }
     }
   }
   // ------------------------------------------------------------------ teardown
@@ -882,7 +987,8 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 
 template <int BN>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_a,
-                int tiles_b, cudaStream_t stream) {
+                int tiles_b, void* workspace, long long workspace_bytes, int* counters,
+                int counters_len, int share_min_kblocks, cudaStream_t stream) {
   static int clusters_max = 0;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(THREADS);
@@ -910,11 +1016,42 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
                      cudaGetErrorString(e));
     clusters_max = n;
   }
+  // Units of work: whole tiles, except that the tiles of a last round that would
+  // leave more than half of the pairs idle are shared along K (see the kernel),
+  // when a share still has `share_min_kblocks` K blocks: measured at 2,048 rows, a
+  // unit costs a few microseconds beside its K loop and the last share's warp
+  // adds the sum and the stores, so sharing paid at K = 8,192 in three shares
+  // (92.5 -> 78.6 us) and did not at K = 3,072 (16 or 12 blocks a share).
   const int total = tiles_a * tiles_b;
-  const int clusters = total < clusters_max ? total : clusters_max;
+  const int nkb = (p.K + BK - 1) / BK;
+  GemmParams q = p;
+  q.full_tiles = total;
+  q.tail_splits = 1;
+  q.tail_kblocks = nkb;
+  const int tail = total % clusters_max;
+  if (workspace != nullptr && counters != nullptr && total > clusters_max && tail > 0 &&
+      2 * tail <= clusters_max) {
+    int shares = clusters_max / tail;
+    if (shares > MAX_TAIL_SHARES) shares = MAX_TAIL_SHARES;
+    if (shares > nkb / share_min_kblocks) shares = nkb / share_min_kblocks;
+    if (shares >= 2) {
+      const int per = (nkb + shares - 1) / shares;
+      shares = (nkb + per - 1) / per;                 // no empty share
+      const long long need = (long long)tail * shares * (2 * BM) * BN * 4;
+      if (shares >= 2 && need <= workspace_bytes && tail * 8 <= counters_len) {
+        q.full_tiles = total - tail;
+        q.tail_splits = shares;
+        q.tail_kblocks = per;
+        q.partial = (float*)workspace;
+        q.tail_counters = counters;
+      }
+    }
+  }
+  const int units = q.full_tiles + (total - q.full_tiles) * q.tail_splits;
+  const int clusters = units < clusters_max ? units : clusters_max;
   cfg.gridDim = dim3(2 * clusters);
   cfg.numAttrs = g_fb_pdl ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN>, ma, mb, p, tiles_a, tiles_b);
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN>, ma, mb, q, tiles_a, tiles_b);
   return fb_check_launch("gemm_tc_pair");
 }
 
@@ -930,14 +1067,20 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
 // in the stream writes (weights); its first loads do not wait for that kernel.
 // persistent 1 runs one CTA per SM over all tiles with two accumulators in
 // tensor memory (for many token rows; one split); persistent 2 does the same
-// with two SMs on each 256 x bn tile (cta_group::2).
+// with two SMs on each 256 x bn tile (cta_group::2). The paired form may share
+// the K of a thin last round's tiles among pairs: for that it takes a float32
+// `workspace` of `workspace_bytes` and `counters` (zero between calls, 8 per
+// tile of a round); without them every tile is computed whole. A share keeps at
+// least `share_min_kblocks` K blocks of 64 (0: the default, 32).
 // epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
 // pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
 // dimension must be 1 and then indexes pairs.
 FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, long long ldb,
                       int rows_b, int K, void* out, long long stride_a, long long stride_b,
                       int out_f32, int bn, int splits, long long split_stride, int epilogue,
-                      int constant_operand, int persistent, cudaStream_t stream) {
+                      int constant_operand, int persistent, void* workspace,
+                      long long workspace_bytes, int* counters, int counters_len,
+                      int share_min_kblocks, cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, K);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
              "gemm_tc: K and the row strides must be multiples of 8 elements (16 bytes), got K=%d "
@@ -957,6 +1100,8 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   p.stride_a = stride_a; p.stride_b = stride_b; p.split_stride = split_stride;
   p.out = out; p.out_f32 = out_f32; p.epilogue = epilogue;
   p.constant_operand = constant_operand;
+  p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = total_kb; p.partial = nullptr;
+  p.tail_counters = nullptr;
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, rows_a, K, lda, BM);
   if (rc) return rc;
@@ -967,19 +1112,20 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   if (persistent == 2) {
     // two SMs per tile: A in blocks of 256 rows, each CTA loads half of a B tile
     FB_REQUIRE(splits == 1, "gemm_tc: the paired form takes one split");
+    const int share_min = share_min_kblocks > 0 ? share_min_kblocks : 32;
     rc = make_map(&mb, b, rows_b, K, ldb, bn / 2);
     if (rc) return rc;
     const int pairs_a = (rows_a + 2 * BM - 1) / (2 * BM);
     switch (bn) {
-      case 128: return launch_pair<128>(ma, mb, p, pairs_a, grid.y, stream);
-      case 144: return launch_pair<144>(ma, mb, p, pairs_a, grid.y, stream);
-      case 160: return launch_pair<160>(ma, mb, p, pairs_a, grid.y, stream);
-      case 176: return launch_pair<176>(ma, mb, p, pairs_a, grid.y, stream);
-      case 192: return launch_pair<192>(ma, mb, p, pairs_a, grid.y, stream);
-      case 208: return launch_pair<208>(ma, mb, p, pairs_a, grid.y, stream);
-      case 224: return launch_pair<224>(ma, mb, p, pairs_a, grid.y, stream);
-      case 240: return launch_pair<240>(ma, mb, p, pairs_a, grid.y, stream);
-      case 256: return launch_pair<256>(ma, mb, p, pairs_a, grid.y, stream);
+      case 128: return launch_pair<128>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 144: return launch_pair<144>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 160: return launch_pair<160>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 176: return launch_pair<176>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 192: return launch_pair<192>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 208: return launch_pair<208>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 224: return launch_pair<224>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 240: return launch_pair<240>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
+      case 256: return launch_pair<256>(ma, mb, p, pairs_a, grid.y, workspace, workspace_bytes, counters, counters_len, share_min, stream);
       default:
         return fb_fail(1, "gemm_tc: the paired form takes tiles 128..256 (steps of 16) wide, "
                           "not %d", bn);
@@ -1011,6 +1157,29 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
     case 256: return launch<256>(ma, mb, p, grid, stream);
     default: return fb_fail(1, "gemm_tc: tile height %d is not one of 16, 32, 64, 128, 256", bn);
   }
+}
+
+// How many CTA pairs of the paired product (256-wide tiles) the device runs at
+// once: the number of tiles of one round. <= 0 on failure (see fb_last_error).
+FB_API int fb_gemm_tc_pair_slots() {
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SmemPair<256>::BYTES;
+  cfg.gridDim = dim3(sm_count() / 2 * 2);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<256>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SmemPair<256>::BYTES);
+  int n = 0;
+  if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<256>, &cfg);
+  if (e != cudaSuccess) return -fb_fail(2, "gemm_tc_pair_slots: %s", cudaGetErrorString(e));
+  return n;
 }
 
 // Reads and clears the device-side status: 0 when no wait ever ran out, else

@@ -41,7 +41,8 @@ _SIGNATURES = {
                           c_int, c_float, c_void_p],
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
-                   c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p],
+                   c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
+                   c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                        c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
@@ -381,6 +382,29 @@ PERSISTENT = _os.environ.get("FOUNDRY_B200_PERSISTENT", "1") != "0"
 PAIRED = _os.environ.get("FOUNDRY_B200_PAIRED", "1") != "0"
 
 
+# The paired product shares the K of a thin last round's tiles among CTA pairs
+# (float32 partial tiles in a workspace, summed by the warp that delivers last).
+PAIR_TAIL_SHARES = _os.environ.get("FOUNDRY_B200_PAIR_TAIL_SHARES", "1") != "0"
+PAIR_SHARE_MIN_KBLOCKS = 0  # K blocks of 64 a share keeps at least (0: the launcher's 32)
+_PAIR_SCRATCH = {}
+
+
+def _pair_scratch(device):
+    """(float32 workspace for the partial tiles of one round: 74 tiles of
+    256 x 256; zeroed int32 counters, 8 per tile), one pair per device."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    got = _PAIR_SCRATCH.get(key)
+    if got is None:
+        if torch.cuda.is_current_stream_capturing():
+            # memory made during a capture belongs to that graph; this must outlive it
+            raise KernelError("the paired product's workspace must be made before a stream "
+                              "capture: run the step once before capturing it")
+        got = _PAIR_SCRATCH[key] = (
+            torch.empty((SM_COUNT // 2) * 256 * 256, dtype=torch.float32, device=device),
+            torch.zeros((SM_COUNT // 2) * 8, dtype=torch.int32, device=device))
+    return got
+
+
 def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
             bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0,
             constant_operand: int = 0, persistent: int = 0) -> None:
@@ -390,11 +414,15 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
         raise KernelError("gemm_tc takes bfloat16 operands")
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"gemm_tc writes float32 or bfloat16, not {out.dtype}")
+    scratch = (0, 0, 0, 0)
+    if int(persistent) == 2 and PAIR_TAIL_SHARES:
+        work, counters = _pair_scratch(a.device)
+        scratch = (work.data_ptr(), work.numel() * 4, counters.data_ptr(), counters.numel())
     _call("fb_gemm_tc", _dev(a, "a", contiguous=False), _rows(a, "a"), a.shape[0],
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
-          constant_operand, int(persistent), _stream(),
+          constant_operand, int(persistent), *scratch, PAIR_SHARE_MIN_KBLOCKS, _stream(),
           tag=("a{} b{} k{} tile{} splits{}", a.shape[0], b.shape[0], a.shape[1], bn, splits))
 
 

@@ -630,6 +630,36 @@ def test_gemm_tensor_core_paired(ops, bn, rows_a, rows_b, K):
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("rows_a,rows_b,K,bn", [(2048, 3072, 1024, 256), (2560, 2304, 2048, 256),
+                                                 (2048, 3000, 520, 176), (4000, 2500, 264, 208)])
+def test_gemm_paired_shares_the_last_round(ops, monkeypatch, rows_a, rows_b, K, bn):
+    """More tiles than CTA pairs with a thin last round: its tiles are shared
+    along K, the shares meet in the workspace, the warp that delivers last sums
+    them. Twice in a row (the counters must be back at zero), with and without
+    the SiLU-mul epilogue, and the same result as with whole tiles only."""
+    a, b = rnd(rows_a, K, dtype=torch.bfloat16, scale=0.5), rnd(rows_b, K, dtype=torch.bfloat16, scale=0.5, seed=6)
+    want = a.double() @ b.double().T
+    assert ops.PAIR_TAIL_SHARES
+    monkeypatch.setattr(ops, "PAIR_SHARE_MIN_KBLOCKS", 4)  # share even these short K loops
+    for _ in range(2):
+        out = torch.full((rows_a, rows_b), 3.0, device=DEV)
+        ops.gemm_tc(a, b, out, rows_b, 1, bn, persistent=2, constant_operand=2)
+        close(out, want, 2e-4 * math.sqrt(K), 1e-5)
+        act = torch.full((rows_a, rows_b // 2), 3.0, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_tc(a, b, act, rows_b // 2, 1, bn, epilogue=1, persistent=2, constant_operand=2)
+        g, u = want[:, 0::2], want[:, 1::2]
+        close(act, g / (1 + torch.exp(-g)) * u, 3e-2, 1e-2)
+    ops.PAIR_TAIL_SHARES = False
+    try:
+        whole = torch.full((rows_a, rows_b), 3.0, device=DEV)
+        ops.gemm_tc(a, b, whole, rows_b, 1, bn, persistent=2, constant_operand=2)
+    finally:
+        ops.PAIR_TAIL_SHARES = True
+    close(out, whole.double(), 1e-4 * math.sqrt(K), 1e-5)
+    assert int(ops._pair_scratch(a.device)[1].abs().sum()) == 0
+    assert ops.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("bn", [64, 128, 144, 176, 192, 208, 240, 256])
 @pytest.mark.parametrize("rows_a,rows_b,K", [(300, 700, 264), (2048, 1024, 512), (130, 70, 64),
                                               (1000, 5000, 72)])
