@@ -44,6 +44,7 @@ _SIGNATURES = {
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
                    c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
+    "fb_gemm_tc_pair_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
                        c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
     "fb_gemm_skinny_rope": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p,
@@ -568,7 +569,7 @@ if _os.environ.get("FOUNDRY_B200_PDL", "1") == "0":
 def gemm_tc_status():
     """0 when no bounded wait of the tcgen05 kernels (products and prompt
     attention) ever ran out, else (role, block, step). Synchronises the device."""
-    for name in ("fb_gemm_tc_status", "fb_attention_tc_status"):
+    for name in ("fb_gemm_tc_status", "fb_gemm_tc_pair_status", "fb_attention_tc_status"):
         detail = (ctypes.c_int * 3)()
         code = _fn(name)(ctypes.cast(detail, ctypes.c_void_p))
         if code != 0:
