@@ -38,12 +38,20 @@ class StepContext:
     slots: torch.Tensor  # int32 [n_seqs]: each sequence's slot (its state row)
     cu_tokens: torch.Tensor  # int32 [n_seqs + 1]
     kv_lens: torch.Tensor  # int32 [n_seqs]: sequence lengths after this step
-    slots_host: List[int]
-    cu_tokens_host: List[int]
-    kv_lens_host: List[int]
+    # Host copies; None in a step that is replayed from a captured graph (its
+    # kernels were recorded once and may not depend on host-side step values)
+    slots_host: Optional[List[int]]
+    cu_tokens_host: Optional[List[int]]
+    kv_lens_host: Optional[List[int]]
     is_decode: bool  # every sequence brings exactly one token
     max_q_len: int
     max_kv_len: int
+    # In a replayed prompt step: an upper bound of the number of query blocks of
+    # 64 rows over all sequences (the attention's grid), else None
+    query_blocks_bound: Optional[int] = None
+    # ... and whether some sequence brings 64 tokens or more (the choice between
+    # the two prompt-attention kernels, made as a plain step makes it)
+    long_queries: bool = False
     _tables: Dict[int, torch.Tensor] = field(default_factory=dict)
     # The weight that the step streams after the part being run (a prefetch
     # hint, set by the model and the blocks as they go; None = unknown).
@@ -54,10 +62,23 @@ class StepContext:
         return self._tables[id(group)]
 
 
-def build_context(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
-                  device: torch.device, max_positions: Optional[int] = None) -> StepContext:
-    """Validate a step, reserve its cache pages, and upload its description.
-    Nothing is changed when validation or the reservation fails."""
+@dataclass
+class StepPlan:
+    """A validated step on the host, its cache pages reserved."""
+    token_ids: np.ndarray
+    positions: np.ndarray
+    seq_of: np.ndarray
+    want_rows: List[int]
+    slots: List[int]
+    cu: List[int]
+    kv_lens: List[int]
+    tables: list  # (group, width, rows [n_seqs][width]) per cache group
+
+
+def plan_step(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
+              max_positions: Optional[int] = None) -> StepPlan:
+    """Validate a step and reserve its cache pages. Nothing is changed when
+    validation or the reservation fails."""
     if not steps:
         raise ValueError("a step needs at least one sequence")
     seen = set()
@@ -102,24 +123,37 @@ def build_context(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_siz
         want_rows.extend(a + int(w) for w in s.want)
     kv_lens = [starts[i] + lens[i] for i in range(n_seqs)]
     slots = [s.slot for s in steps]
-
-    # one packed int32 upload: fixed fields, then one page table per group
-    fields = [token_ids, positions, seq_of, np.asarray(want_rows, np.int32),
-              np.asarray(slots, np.int32), np.asarray(cu, np.int32), np.asarray(kv_lens, np.int32)]
     tables = []
     for group in cache.groups:
         width = max(1, max(len(group.pages.pages(slot)) for slot in slots))
-        tables.append((group, width))
-        fields.append(np.asarray(cache.page_table_rows(group, slots, width), np.int32).reshape(-1))
+        tables.append((group, width, cache.page_table_rows(group, slots, width)))
+    return StepPlan(token_ids, positions, seq_of, want_rows, slots, cu, kv_lens, tables)
+
+
+def build_context(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
+                  device: torch.device, max_positions: Optional[int] = None,
+                  plan: Optional[StepPlan] = None) -> StepContext:
+    """Validate a step, reserve its cache pages, and upload its description
+    (or upload a step already planned)."""
+    if plan is None:
+        plan = plan_step(cache, steps, vocab_size, max_positions)
+    n_seqs, T = len(plan.slots), int(plan.token_ids.size)
+    lens = [plan.cu[i + 1] - plan.cu[i] for i in range(n_seqs)]
+    # one packed int32 upload: fixed fields, then one page table per group
+    fields = [plan.token_ids, plan.positions, plan.seq_of, np.asarray(plan.want_rows, np.int32),
+              np.asarray(plan.slots, np.int32), np.asarray(plan.cu, np.int32),
+              np.asarray(plan.kv_lens, np.int32)]
+    for _, _, rows in plan.tables:
+        fields.append(np.asarray(rows, np.int32).reshape(-1))
     offsets = np.cumsum([0] + [f.size for f in fields])
     packed = torch.from_numpy(np.concatenate(fields)).to(device)
     part = [packed[offsets[i]:offsets[i + 1]] for i in range(len(fields))]
     ctx = StepContext(
-        n_tokens=T, n_seqs=n_seqs, n_want=len(want_rows),
+        n_tokens=T, n_seqs=n_seqs, n_want=len(plan.want_rows),
         token_ids=part[0], positions=part[1], seq_of_token=part[2], want_rows=part[3],
         slots=part[4], cu_tokens=part[5], kv_lens=part[6],
-        slots_host=slots, cu_tokens_host=cu, kv_lens_host=kv_lens,
-        is_decode=all(n == 1 for n in lens), max_q_len=max(lens), max_kv_len=max(kv_lens))
-    for i, (group, width) in enumerate(tables):
+        slots_host=plan.slots, cu_tokens_host=plan.cu, kv_lens_host=plan.kv_lens,
+        is_decode=all(n == 1 for n in lens), max_q_len=max(lens), max_kv_len=max(plan.kv_lens))
+    for i, (group, width, _) in enumerate(plan.tables):
         ctx._tables[id(group)] = part[7 + i].view(n_seqs, width)
     return ctx

@@ -20,6 +20,7 @@ from ..sampling import Sampler, SamplingParams
 from ..weights.safetensors_io import WeightFiles
 from . import generate as loop
 from .context import SequenceStep, build_context
+from .prompt import PromptRunners
 from .decode import DecodeRunner, DecodeSession
 from .model import Model
 
@@ -59,6 +60,7 @@ class Engine:
         self._runners = {}
         self._graph_pool = None
         self._session = None
+        self._prompts = None  # graphs of short prompt steps, made at the first one
 
     # ---------------------------------------------------------------- load
     @classmethod
@@ -123,6 +125,10 @@ class Engine:
         in the order of `steps` and of each `want`."""
         if self._is_decode(steps):
             return self._decode(steps, SamplingParams(), None, None)[1].clone()
+        if self._prompts is None:
+            self._prompts = PromptRunners(self)
+        if self._prompts.wants(steps):
+            return self._prompts.step(steps)
         ctx = build_context(self.cache, steps, self.spec.vocab_size, self.device,
                             self.spec.max_positions)
         return self.model.forward(ctx, self.cache)

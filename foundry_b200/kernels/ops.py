@@ -753,12 +753,18 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                                 num_heads, num_kv_heads, head_dim, scale, splits, stages,
                                 then_reads=then_reads)
-    lens = [ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] for i in range(ctx.n_seqs)]
-    if head_dim in TC_HEAD_DIMS and PREFILL_TC and max(lens) >= 64 and _tc_attention_ok(q, out):
+    if ctx.cu_tokens_host is None:
+        # a step replayed from a graph: the grid comes from the bucket's bound of
+        # 64-row blocks (blocks beyond the real count return at once)
+        blocks, blocks128, longest = (ctx.query_blocks_bound, (ctx.query_blocks_bound + 1) // 2
+                                      + ctx.n_seqs, 64 if ctx.long_queries else 1)
+    else:
+        lens = [ctx.cu_tokens_host[i + 1] - ctx.cu_tokens_host[i] for i in range(ctx.n_seqs)]
+        blocks, blocks128, longest = (sum((n + 63) // 64 for n in lens),
+                                      sum((n + 127) // 128 for n in lens), max(lens))
+    if head_dim in TC_HEAD_DIMS and PREFILL_TC and longest >= 64 and _tc_attention_ok(q, out):
         return attention_prefill_tc(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache,
-                                    v_cache, num_heads, num_kv_heads, head_dim, scale,
-                                    sum((n + 127) // 128 for n in lens))
-    blocks = sum((n + 63) // 64 for n in lens)
+                                    v_cache, num_heads, num_kv_heads, head_dim, scale, blocks128)
     return attention_prefill(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
 

@@ -29,6 +29,8 @@ from .linear import Linear
 
 @register_mixer("gqa_attention")
 class GQAAttention(Part):
+    replay_safe = True  # forward reads nothing of the step on the host
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PartSpec], window: Optional[int] = None, *,
                  dtype: torch.dtype, device: torch.device):

@@ -23,6 +23,8 @@ from .base import (FEED_FORWARDS, MIXERS, NORMS, Fetch, Part, first_weight_of,
 
 @register_block("pre_norm_residual")
 class PreNormResidualBlock(Part):
+    replay_safe = True  # forward reads nothing of the step on the host
+
     def __init__(self, layer: LayerSpec, *, dtype: torch.dtype, device: torch.device):
         ctx = dict(dtype=dtype, device=device)
         self.prefix = layer.prefix

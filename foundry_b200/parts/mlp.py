@@ -16,6 +16,8 @@ from .linear import Linear, matmul_nt
 
 @register_feed_forward("swiglu")
 class SwiGLU(Part):
+    replay_safe = True  # forward reads nothing of the step on the host
+
     def __init__(self, hidden_size: int, intermediate_size: int, *, dtype: torch.dtype,
                  device: torch.device):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size

@@ -19,6 +19,8 @@ from .base import Fetch, Part, register_norm
 
 @register_norm("rms_norm")
 class RMSNorm(Part):
+    replay_safe = True  # forward reads nothing of the step on the host
+
     def __init__(self, size: int, eps: float, *, dtype: torch.dtype, device: torch.device):
         self.size, self.eps = size, float(eps)
         self.dtype, self.device = dtype, device
