@@ -176,6 +176,51 @@ def test_padding_changes_no_result(tiny_folders):
     assert np.array_equal(three, four[:, :3])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompt_steps_replayed_equal_plain_launches(tiny_folders, dtype):
+    """Prompt steps of up to 128 tokens run as replayed graphs over padded
+    buckets. The same steps launched plainly give the same logits bit for bit:
+    one bucket used three times with other lengths, sequence counts and wanted
+    places (the second and third use replay the graph of the first), a
+    continued prompt, a step that wants nothing, and the decode steps after."""
+    from foundry_b200.engine import SequenceStep
+    from foundry_b200.engine import prompt as prompt_graphs
+    name = "tiny_b"
+    cfg, _ = plain.read_model(tiny_folders[name])
+    V = cfg["vocab_size"]
+    rounds = [[(60, [0, 59]), (40, [39])],            # 100 tokens -> bucket (128, 2, 8, 4)
+              [(90, [89, 1, 2]), (20, [19])],          # the same bucket, other cuts
+              [(70, [69]), (30, [0, 29, 5])],
+              [(5, [4])],                              # a small bucket
+              [(16, []), (3, [])],                     # nothing wanted
+              [(64, [63]), (64, [0]), (1, [0])]]       # 129 tokens: launched plainly in both
+    results = []
+    for graphs in (True, False):
+        engine = engine_for(tiny_folders[name], dtype, max_slots=4, max_tokens=1024)
+        engine.use_graphs = graphs
+        out = []
+        for r, round_ in enumerate(rounds):
+            slots = [engine.open_sequence() for _ in round_]
+            prompts = [tiny.random_tokens(100 * r + i, n, V) for i, (n, _) in enumerate(round_)]
+            out.append(engine.step([SequenceStep(s, p, w) for s, p, (_, w) in
+                                    zip(slots, prompts, round_)]).cpu())
+            # the prompts go on: 7 more tokens each, then two single tokens
+            more = [tiny.random_tokens(100 * r + 50 + i, 7, V) for i in range(len(slots))]
+            out.append(engine.step([SequenceStep(s, m, [6]) for s, m in zip(slots, more)]).cpu())
+            for t in range(2):
+                out.append(engine.step([SequenceStep(s, [11 + t], [0]) for s in slots]).cpu())
+            for s in slots:
+                engine.close_sequence(s)
+        if graphs:
+            keys = set(engine._prompts._runners)
+            # rounds 2 and 3 replayed one graph; the seven-token steps of all rounds share theirs
+            assert {(128, 2, 8, 4, True), (128, 2, 8, 4, False)} <= keys and len(keys) <= 7, keys
+        results.append(out)
+    assert prompt_graphs.PROMPT_GRAPH_TOKENS == 128
+    for a, b in zip(*results):
+        assert a.shape == b.shape and torch.equal(a, b)
+
+
 def test_refusals_of_the_step_function(tiny_folders):
     from foundry_b200.cache import CacheFull
     from foundry_b200.engine import SequenceStep
