@@ -437,12 +437,16 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   q.full_tiles = total;
   q.tail_splits = 1;
   q.tail_kblocks = nkb;
+  // tiles of the last round (all tiles, when there are fewer than pairs) and the K
+  // blocks a share must keep: half as many when the pairs would otherwise idle for
+  // the whole call, not only for its last round
   const int tail = total % clusters_max;
-  if (workspace != nullptr && counters != nullptr && total > clusters_max && tail > 0 &&
-      2 * tail <= clusters_max) {
+  const bool few = total < clusters_max;
+  const int min_kblocks = few ? (share_min_kblocks + 1) / 2 : share_min_kblocks;
+  if (workspace != nullptr && counters != nullptr && tail > 0 && 2 * tail <= clusters_max) {
     int shares = clusters_max / tail;
     if (shares > MAX_TAIL_SHARES) shares = MAX_TAIL_SHARES;
-    if (shares > nkb / share_min_kblocks) shares = nkb / share_min_kblocks;
+    if (shares > nkb / min_kblocks) shares = nkb / min_kblocks;
     if (shares >= 2) {
       const int per = (nkb + shares - 1) / shares;
       shares = (nkb + per - 1) / per;                 // no empty share
