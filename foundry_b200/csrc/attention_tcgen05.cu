@@ -15,23 +15,28 @@
 //              two K pages and a ring of two V pages (a K page is free again
 //              when its scores are computed, a V page one product later);
 //   warp 1     allocates tensor memory; one lane issues S = Q K^T (M 128, N 64)
-//              into one of two score buffers and O += P V (M 128, N D, V read
-//              MN-major straight from its [key, d] page) one page behind, so
+//              into one of two score buffers and O += P V one page behind, so
 //              that the next page's scores are computed while this page's
-//              softmax runs;
+//              softmax runs. P is the A operand of that product and comes from
+//              tensor memory (V is read MN-major straight from its [key, d] page);
 //   warps 2-5  softmax: thread r owns query row r. It reads its 64 scores from
 //              tensor memory, masks, exponentiates against a reference maximum,
-//              and writes the probabilities as a K-major swizzled bf16 tile in
-//              shared memory. The reference maximum only moves when the row's
-//              maximum has grown by more than 2^8; only then is the output
-//              accumulator read back, rescaled and stored again.
+//              and stores the probabilities as bfloat16 pairs into the first 32
+//              columns of the score buffer they came from. The reference maximum
+//              only moves when the row's maximum has grown by more than 2^8; only
+//              then does the warp wait for the running product and read the
+//              output accumulator back, rescale and store it again.
 //   At the end the softmax warps read O, divide by the row sums and store.
 //
-// Shared memory (112 KB at head size 128) and tensor memory (256 columns) are
-// sized so that two CTAs share an SM: a row's softmax is one long dependent
-// chain per thread, and with a single CTA each scheduler has one softmax warp
-// and the tensor pipe idles four fifths of the time; the second CTA's warps
-// fill those gaps.
+// With P in the score buffers there are two of them, so the softmax of page
+// j + 1 never waits for the product of page j: an earlier version kept one P tile
+// in shared memory, and a page then cost the whole chain P -> product -> commit ->
+// softmax (2,700 cycles a page whatever the softmax did; taking its loads, exps
+// and stores out changed nothing).
+//
+// Shared memory (96 KB at head size 128) and tensor memory (256 columns) are
+// sized so that two CTAs share an SM: the second CTA's warps fill the gaps that
+// a row's long dependent chain leaves on the schedulers and the tensor pipe.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out raises the CTA's
 // abort flag, all roles run out, tensor memory is freed, and the host can read
@@ -69,8 +74,7 @@ template <int D>
 struct FaSmem {
   static constexpr int Q_BYTES = BQ * D * 2;
   static constexpr int PAGE_BYTES = FB_PAGE * D * 2;       // one K or V page of one head
-  static constexpr int P_BYTES = BQ * FB_PAGE * 2;
-  static constexpr int USED = Q_BYTES + 2 * ST * PAGE_BYTES + P_BYTES + 256;
+  static constexpr int USED = Q_BYTES + 2 * ST * PAGE_BYTES + 256;
   // never three CTAs on an SM: they would need more tensor memory than it has
   static constexpr int BYTES = USED > 77 * 1024 ? USED : 77 * 1024;
   static_assert(BYTES <= (233472 - 2 * 1024) / 2, "two CTAs must fit an SM");
@@ -91,17 +95,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   uint8_t* sQ = base;
   uint8_t* sK = sQ + FaSmem<D>::Q_BYTES;                 // [ST][SUB][64 keys][64]
   uint8_t* sV = sK + ST * FaSmem<D>::PAGE_BYTES;         // [ST][SUB][64 keys][64]
-  uint8_t* sP = sV + ST * FaSmem<D>::PAGE_BYTES;         // [128 rows][64 keys]
-  uint64_t* bars = (uint64_t*)(sP + FaSmem<D>::P_BYTES);
+  uint64_t* bars = (uint64_t*)(sV + ST * FaSmem<D>::PAGE_BYTES);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;         // [ST]
   uint64_t* v_full = k_full + ST;      // [ST]
   uint64_t* k_empty = v_full + ST;     // [ST]
   uint64_t* v_empty = k_empty + ST;    // [ST]
-  uint64_t* s_full = v_empty + ST;     // [2]
-  uint64_t* s_empty = s_full + 2;      // [2]
-  uint64_t* p_full = s_empty + 2;      // completes once per page
-  uint64_t* pv_done = p_full + 1;      // completes once per P.V product
+  uint64_t* s_full = v_empty + ST;     // [2]: the scores of a page are in buffer b
+  uint64_t* p_full = s_full + 2;       // [2]: its probabilities have replaced them
+  uint64_t* pv_done = p_full + 2;      // completes once per P.V product
   uint64_t* o_final = pv_done + 1;     // completes once, after the last one
   uint32_t* tmem_slot = (uint32_t*)(o_final + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
@@ -127,9 +129,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);  // one arrival per softmax warp
+      mbar_init(&p_full[i], 4);  // one arrival per softmax warp
     }
-    mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     mbar_init(o_final, 1);
     *abort_flag = 0;
@@ -202,10 +203,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       bool ok = mbar_wait(q_full, 0, abort_flag, 12, 0);
       for (int j = 0; j <= n_pages && ok; ++j) {
         if (j < n_pages) {
-          // S[j & 1] = Q K_j^T
+          // S[j & 1] = Q K_j^T. The buffer held P of page j - 2, whose product was
+          // issued in the previous iteration: the tensor pipe runs them in order.
           const int s = j % ST, b = j & 1;
-          ok = mbar_wait(&k_full[s], (uint32_t)((j / ST) & 1), abort_flag, 13, j) &&
-               mbar_wait(&s_empty[b], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag, 14, j);
+          ok = mbar_wait(&k_full[s], (uint32_t)((j / ST) & 1), abort_flag, 13, j);
           if (!ok) break;
           tc_fence_after();
           const uint32_t q_addr = smem_u32(sQ);
@@ -220,18 +221,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_commit(&k_empty[s]);
         }
         if (j >= 1) {
-          // O += P_{j-1} V_{j-1}, one page behind the scores
-          const int jj = j - 1, s = jj % ST;
-          ok = mbar_wait(p_full, (uint32_t)(jj & 1), abort_flag, 15, jj) &&
+          // O += P_{j-1} V_{j-1}, one page behind the scores; P from tensor memory
+          const int jj = j - 1, s = jj % ST, b = jj & 1;
+          ok = mbar_wait(&p_full[b], (uint32_t)((jj >> 1) & 1), abort_flag, 15, jj) &&
                mbar_wait(&v_full[s], (uint32_t)((jj / ST) & 1), abort_flag, 9, jj);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t p_addr = smem_u32(sP);
           const uint32_t v_addr = smem_u32(sV + s * FaSmem<D>::PAGE_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)  // 16 keys per instruction: 32 bytes of P, 16 rows of V
-            umma(tmem_base + O_COL, make_desc(p_addr + k * 32),
-                 make_desc_mn(v_addr + k * 16 * 128, KV_SUB), idesc_pv, (jj | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)  // 16 keys per instruction: 8 columns of P, 16 rows of V
+            umma_a_tmem(tmem_base + O_COL, tmem_base + (uint32_t)(b * FB_PAGE + k * 8),
+                        make_desc_mn(v_addr + k * 16 * 128, KV_SUB), idesc_pv,
+                        (jj | k) != 0 ? 1u : 0u);
           tc_commit(&v_empty[s]);
           tc_commit(pv_done);
           if (jj == n_pages - 1) tc_commit(o_final);
@@ -264,10 +265,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           sc[32 + e] = __uint_as_float(r1[e]);
         }
       }
-      // the scores are in registers: the buffer may take the scores of page j + 2
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);
 
       const int key0 = j * FB_PAGE;
       const bool diagonal = key0 + FB_PAGE - 1 > pos0 + quarter * 32;  // some key may be masked
@@ -287,15 +284,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         mx4[3] = fmaxf(mx4[3], sc[e + 3]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-      // P was read by the product of page j - 1, which ran while this page's scores
-      // were fetched and their maximum taken
-      ok = mbar_wait(pv_done, (uint32_t)(j & 1) ^ 1u, abort_flag, 17, j);
-      if (!ok) break;
       const bool grow = mx > m_ref + RESCALE_STEP;  // also the first page (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float corr = grow ? exp2f(m_ref - mx) : 1.0f;  // 0 on the first page
         if (j > 0) {
-          // the accumulator is at rest: the product of page j - 1 is complete
+          // the accumulator must be at rest: wait for the product of page j - 1
+          ok = mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag, 18, j);
+          if (!ok) break;
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
@@ -311,38 +306,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         l *= corr;
         if (grow) m_ref = mx;
       }
-      // probabilities against the reference maximum (at most 2^8), as a K-major tile
-      // with the 128-byte swizzle: 16-byte chunk c of row r lands at chunk c ^ (r & 7)
-      uint8_t* prow = sP + row * 128;
+      // probabilities against the reference maximum (at most 2^8), rounded to bfloat16
+      // and packed two keys to a column: the A operand of the product, in the first 32
+      // columns of this page's score buffer
       const float neg_ref = -m_ref;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float pv[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          // 2^(s * scale - m_ref): one multiply-add and one ex2; the result is at most 2^8
-          // and is rounded to bfloat16 next, so the approximate ex2 costs no accuracy
-          pv[e] = fast_exp2(fmaf(sc[c * 8 + e], p.scale_log2, neg_ref));
-          sum4[e & 3] += pv[e];
-        }
-        uint4 pk;
-        __nv_bfloat162 h0 = __floats2bfloat162_rn(pv[0], pv[1]);
-        __nv_bfloat162 h1 = __floats2bfloat162_rn(pv[2], pv[3]);
-        __nv_bfloat162 h2 = __floats2bfloat162_rn(pv[4], pv[5]);
-        __nv_bfloat162 h3 = __floats2bfloat162_rn(pv[6], pv[7]);
-        pk.x = *reinterpret_cast<uint32_t*>(&h0);
-        pk.y = *reinterpret_cast<uint32_t*>(&h1);
-        pk.z = *reinterpret_cast<uint32_t*>(&h2);
-        pk.w = *reinterpret_cast<uint32_t*>(&h3);
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = pk;
+      for (int c = 0; c < 32; ++c) {
+        // 2^(s * scale - m_ref): one multiply-add and one ex2; the result is at most 2^8
+        // and is rounded to bfloat16 next, so the approximate ex2 costs no accuracy
+        const float p0 = fast_exp2(fmaf(sc[2 * c], p.scale_log2, neg_ref));
+        const float p1 = fast_exp2(fmaf(sc[2 * c + 1], p.scale_log2, neg_ref));
+        sum4[c & 1] += p0;
+        sum4[2 + (c & 1)] += p1;
+        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        packed[c] = *reinterpret_cast<const uint32_t*>(&h);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      l += sum;
-      fence_async_smem();
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st32(tmem_base + lane_base + (uint32_t)(b * FB_PAGE), packed);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[b]);
     }
     // O / l
     if (ok) ok = mbar_wait(o_final, 0, abort_flag, 19, n_pages);
