@@ -24,6 +24,12 @@ FeedForward
 Block
     forward(ctx, resid, delta, cache_view) -> new delta (not yet added to resid)
 Optional, any part
+    replay_safe = True (class attribute): the part's forward launches the same
+    kernels with the same arguments whatever the step's values are, i.e. it
+    reads the step only through the device tensors of `ctx` (never
+    `ctx.*_host`, which are None in a replayed step). Short prompt steps of a
+    model whose parts all say so are captured once per bucket and replayed
+    (engine/prompt.py); otherwise they are launched one by one.
     first_weight() -> the weight tensor its forward streams first, or None.
     `ctx.reads_after_part` holds the first weight of whatever runs after the
     part being called (the block sets it for its mixer and feed-forward, the
