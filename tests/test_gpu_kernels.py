@@ -286,7 +286,7 @@ def test_attention_tcgen05_any_token_counts(ops, lens_q, lens_kv, A, Kh, D):
 
 
 @pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", [c for c in ATT_CASES if max(c[0]) == 1])
-@pytest.mark.parametrize("splits", [1, 2, 7])
+@pytest.mark.parametrize("splits", [1, 2, 7, 12])
 def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, splits):
     # a padding row (length 0) sits between the real ones and must come out as zeros
     lens_q, lens_kv = list(lens_q), list(lens_kv)
