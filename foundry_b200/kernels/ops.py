@@ -595,14 +595,16 @@ def _tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and w.stride(1) == 1 and out.stride(1) == 1)
 
 
-def _swapped_plan(M: int, N: int, K: int):
-    """Tile width and split count for up to 128 token rows."""
-    bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+def _few_rows_plan(N: int, K: int) -> int:
+    """K shares of the one-tile product for 17..128 token rows: tiles are 128
+    token rows (partly empty) by 128 weight rows; K is shared among CTAs until
+    the grid covers the SMs once (a second round cost 0.2 ms a step at batch
+    64), each share writing a float32 plane."""
     tiles = (N + 127) // 128
     kblocks = (K + 63) // 64
-    splits = max(1, min(kblocks // 4, SM_COUNT // tiles))  # one CTA per SM: never a second round
+    splits = max(1, min(kblocks // 4, SM_COUNT // tiles))
     per = (kblocks + splits - 1) // splits
-    return bn, (kblocks + per - 1) // per  # no empty split
+    return (kblocks + per - 1) // per  # no empty share
 
 
 def prompt_tile_width(M: int, N: int) -> int:
@@ -649,9 +651,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
 
     Up to 16 rows: the weight-streaming kernel. More than 128 rows: token rows
     fill the 128-row operand (256 rows over a pair of SMs), weights the other
-    (up to 256 wide), see `prompt_plan`. In between: swapped, the weights fill the 128-row operand and
-    stream through once, the tokens are the narrow operand; K is split over
-    CTAs until the grid covers the SMs, each split writing a float32 plane.
+    (up to 256 wide), see `prompt_plan`. In between: one 128 x 128 tile per
+    CTA, the weights stream through once; K is split over CTAs until the grid
+    covers the SMs, each split writing a float32 plane.
     With `allow_planes` the planes are returned as `Planes` for a consumer that
     sums them as it reads; otherwise one more kernel sums them in a fixed order.
     Shapes TMA cannot address (K or a row stride not a multiple of 8 elements)
@@ -683,14 +685,18 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         bn, form = prompt_plan(M, N)
         gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=form)
         return out
-    bn, splits = _swapped_plan(M, N, K)
+    # 17..128 rows: the tokens are the (partly empty) 128-row operand, so that a thread
+    # of the epilogue owns a token's consecutive features and stores them as vectors;
+    # with the weights as the row operand ("swapped") the same product was 2.5 us a
+    # call slower, all of it in the scalar stores
+    splits = _few_rows_plan(N, K)
     if splits == 1:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        gemm_tc(w, x, out, 1, out.stride(0), bn, constant_operand=1)
+        gemm_tc(x, w, out, out.stride(0), 1, 128, constant_operand=2)
         return out
     planes = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
-    gemm_tc(w, x, planes, 1, N, bn, splits, M * N, constant_operand=1)
+    gemm_tc(x, w, planes, N, 1, 128, splits, M * N, constant_operand=2)
     if allow_planes and out is None:
         return Planes(planes)
     if out is None:
@@ -726,8 +732,7 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         gemm_tc(x, w_pairs, out, out.stride(0), 1, bn, epilogue=1, constant_operand=2,
                 persistent=form)
     else:
-        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-        gemm_tc(w_pairs, x, out, 1, out.stride(0), bn, epilogue=1, constant_operand=1)
+        gemm_tc(x, w_pairs, out, out.stride(0), 1, 128, epilogue=1, constant_operand=2)
     return out
 
 
