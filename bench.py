@@ -193,7 +193,7 @@ def run(args) -> dict:
     # ---------------------------------------------------------------- prefill
     prompt = token_rows(SplitMix64(1), 1, PREFILL_TOKENS, 128000)[0]
     prefill_ms = []
-    for it in range(3 + 3):
+    for it in range(3 + 5):  # three warm-up runs, the median of five
         slot = engine.open_sequence()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
