@@ -381,6 +381,8 @@ SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
 PERSISTENT = _os.environ.get("FOUNDRY_B200_PERSISTENT", "1") != "0"
 # two SMs on one 256-row tile (tcgen05 cta_group::2) for more than 128 token rows
 PAIRED = _os.environ.get("FOUNDRY_B200_PAIRED", "1") != "0"
+# up to this many token rows the one-tile product is considered beside the paired one
+ONE_TILE_ROWS = int(_os.environ.get("FOUNDRY_B200_ONE_TILE_ROWS", "768"))
 
 
 # The paired product shares the K of a thin last round's tiles among CTA pairs
@@ -595,16 +597,20 @@ def _tc_usable(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
             and w.stride(1) == 1 and out.stride(1) == 1)
 
 
-def _few_rows_plan(N: int, K: int) -> int:
-    """K shares of the one-tile product for 17..128 token rows: tiles are 128
-    token rows (partly empty) by 128 weight rows; K is shared among CTAs until
-    the grid covers the SMs once (a second round cost 0.2 ms a step at batch
-    64), each share writing a float32 plane."""
-    tiles = (N + 127) // 128
+def _one_tile_plan(M: int, N: int, K: int):
+    """(K shares, fits) of the one-tile product: tiles of 128 token rows (the
+    last one partly empty) by 128 weight rows; K is shared among CTAs until the
+    grid covers the SMs once (a second round cost 0.2 ms a step at batch 64),
+    each share writing a float32 plane. `fits`: all CTAs run at once and none
+    walks more than 64 K blocks, which is where this form beat the paired one
+    for 129 to 768 rows (e.g. 256 rows: O 13 against 22 us, down 22 against
+    30, q/k/v 23 against 25; the gate/up product has too many tiles for it)."""
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
     kblocks = (K + 63) // 64
     splits = max(1, min(kblocks // 4, SM_COUNT // tiles))
     per = (kblocks + splits - 1) // splits
-    return (kblocks + per - 1) // per  # no empty share
+    splits = (kblocks + per - 1) // per  # no empty share
+    return splits, tiles * splits <= SM_COUNT and per <= 64
 
 
 def prompt_tile_width(M: int, N: int) -> int:
@@ -679,17 +685,18 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_skinny(x, w, out, then_reads=then_reads, warps=warps)
-    if M > 128:
+    splits, fits = _one_tile_plan(M, N, K)
+    if M > 128 and not (fits and M <= ONE_TILE_ROWS):
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         bn, form = prompt_plan(M, N)
         gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=form)
         return out
-    # 17..128 rows: the tokens are the (partly empty) 128-row operand, so that a thread
-    # of the epilogue owns a token's consecutive features and stores them as vectors;
-    # with the weights as the row operand ("swapped") the same product was 2.5 us a
-    # call slower, all of it in the scalar stores
-    splits = _few_rows_plan(N, K)
+    # 17..128 rows (and more, while one round of tiles covers them): the tokens are the
+    # (partly empty) 128-row operand, so that a thread of the epilogue owns a token's
+    # consecutive features and stores them as vectors; with the weights as the row
+    # operand ("swapped") the same product was 2.5 us a call slower, all of it in the
+    # scalar stores
     if splits == 1:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
