@@ -4,11 +4,15 @@
 //             sequence's pages (64 keys each) with an online softmax; the four
 //             warps own 16 query rows each.
 //   decode    one new token per sequence: the G query heads that share a
-//             key-value head form one 16-row tile (rows >= G are padding), the
-//             four warps own 16 keys of each page, the cache range is split
-//             over CTAs, and the CTA that delivers the last partial result of a
-//             (sequence, kv head) merges them all (it learns that it is the
-//             last from an atomic counter; nobody waits for anybody).
+//             key-value head are one tile. With G <= 8 the keys are the 16 rows
+//             of the instruction and the heads its 8 columns (S^T = K Q^T,
+//             O^T = V^T P^T); with more, the heads are a 16-row tile (rows >= G
+//             padding). Each of the four warps streams its own 16 keys of every
+//             page into its own buffers and waits for no other warp; the cache
+//             range is split over CTAs, up to eight of which merge inside a
+//             thread-block cluster; what is left meets in a workspace, where the
+//             CTA that delivers a pair's last result merges (it learns that it
+//             is the last from an atomic counter; nobody waits for anybody).
 //
 // Formulas are the reference's (src/nn/attention.rs:23-60: head a reads kv head
 // a / G; src/models/llama/attention.rs:56-58: scale 1/sqrt(D);
@@ -19,7 +23,7 @@
 // materialises [S, L] scores; nothing of that size exists here.
 //
 // Pages arrive in shared memory by cp.async (16-byte pieces, XOR-swizzled so
-// that ldmatrix is conflict-free), double-buffered. Head sizes 16, 32, 64 and
+// that ldmatrix is conflict-free), two or three buffers deep. Head sizes 16, 32, 64 and
 // 128 are built; other sizes, windows and more than 16 query heads per kv head
 // are served by the CUDA-core kernel (attention_simt.cu).
 #include "common.cuh"
@@ -47,6 +51,17 @@ __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
+               : "=r"(r[0]), "=r"(r[1])
+               : "r"(addr));
+}
+// Transposes an 8 x 8 matrix of 16-bit elements held one row per four lanes.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
 }
 __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -108,10 +123,12 @@ struct AttnParams {
   int n_seqs, A, Kh;
   float scale_log2;  // scale * log2(e)
   // decode only
-  int splits;
-  float* ws_o;   // [n_seqs, Kh, splits, 16, D]
-  float* ws_ml;  // [n_seqs, Kh, splits, 16, 2]
-  int* counters; // [n_seqs, Kh]: splits that have delivered; zero between calls
+  int splits;    // CTAs per (sequence, kv head)
+  int cluster;   // of which this many merge inside a thread-block cluster (1: none)
+  int parts;     // partial results per pair that meet in the workspace: splits / cluster
+  float* ws_o;   // [n_seqs, Kh, parts, 16, D]
+  float* ws_ml;  // [n_seqs, Kh, parts, 16, 2]
+  int* counters; // [n_seqs, Kh]: CTAs that have delivered; zero between calls
   const void* next;      // constant data to bring into L2 for the kernel after this one
   long long next_bytes;  // 0 = none
 };
@@ -303,23 +320,40 @@ __device__ void merge_if_last(const AttnParams& p, int seq, int kvh, int token, 
   __syncthreads();
   if (threadIdx.x == 0) {
     const int before = atomicAdd(&p.counters[seq * p.Kh + kvh], 1);
-    s_last = before == p.splits - 1;
+    s_last = before == p.splits - 1;  // every CTA of the pair arrives once
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const size_t base = (size_t)(seq * p.Kh + kvh) * p.splits;
+  const size_t base = (size_t)(seq * p.Kh + kvh) * p.parts;
   for (int idx = threadIdx.x; idx < G * D; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
-    float M = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(p.ws_ml + (base + s) * 32 + 2 * row));
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < p.splits; ++s) {
-      const float ms = __ldcg(p.ws_ml + (base + s) * 32 + 2 * row);
-      if (ms == -INFINITY) continue;
-      const float f = exp2f(ms - M);
-      L += __ldcg(p.ws_ml + (base + s) * 32 + 2 * row + 1) * f;
-      acc += __ldcg(p.ws_o + ((base + s) * 16 + row) * D + d) * f;
+    // four parts at a time, their twelve loads on the way together
+    float M = -INFINITY, L = 0.f, acc = 0.f;
+    for (int s0 = 0; s0 < p.parts; s0 += 4) {
+      float ms[4], ls[4], os[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool there = s0 + j < p.parts;
+        const size_t s = base + (there ? s0 + j : 0);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + s * 32 + 2 * row));
+        os[j] = __ldcg(p.ws_o + (s * 16 + row) * D + d);
+        ms[j] = there ? ml.x : -INFINITY;
+        ls[j] = ml.y;
+      }
+      const float Mn = fmaxf(fmaxf(M, fmaxf(ms[0], ms[1])), fmaxf(ms[2], ms[3]));
+      if (Mn == -INFINITY) continue;
+      const float keep = M == -INFINITY ? 0.f : exp2f(M - Mn);
+      L *= keep;
+      acc *= keep;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (ms[j] == -INFINITY) continue;  // an empty range: nothing was written for it
+        const float f = exp2f(ms[j] - Mn);
+        L += ls[j] * f;
+        acc += os[j] * f;
+      }
+      M = Mn;
     }
     p.out[(long long)token * p.out_stride + (long long)(kvh * G + row) * D + d] =
         __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
@@ -347,17 +381,21 @@ __device__ __forceinline__ float ld_peer(const float* mine, unsigned rank) {
 constexpr int MAX_CLUSTER = 8;  // portable cluster size
 
 // cO [16][D], cM [16], cL [16]: this CTA's partial result, at the same shared
-// memory offset in every CTA of the cluster.
+// memory offset in every CTA of the cluster. With one cluster per pair the
+// merged result is the output; with several (parts > 1) it is the cluster's
+// partial result, which goes to the workspace where the pair's last CTA merges
+// the clusters' results.
 template <int D>
 __device__ void merge_in_cluster(const AttnParams& p, const float* cO, const float* cM,
-                                 const float* cL, int kvh, int token, int G) {
+                                 const float* cL, int seq, int kvh, int token, int G) {
   unsigned rank;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
   __syncthreads();
   cluster_sync_all();
-  const int S = p.splits;
+  const int S = p.cluster;
   const int total = G * D, share = (total + S - 1) / S;
   const int end = min(total, (int)(rank + 1) * share);
+  const size_t slot = (size_t)(seq * p.Kh + kvh) * p.parts + blockIdx.z / S;
   for (int idx = rank * share + threadIdx.x; idx < end; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
     float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
@@ -382,13 +420,24 @@ __device__ void merge_in_cluster(const AttnParams& p, const float* cO, const flo
       L += ls[s] * f;
       acc += os[s] * f;
     }
-    p.out[(long long)token * p.out_stride + (long long)(kvh * G + row) * D + d] =
-        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    if (p.parts > 1) {
+      p.ws_o[(slot * 16 + row) * D + d] = acc;
+      if (d == 0) { p.ws_ml[slot * 32 + 2 * row] = M; p.ws_ml[slot * 32 + 2 * row + 1] = L; }
+    } else {
+      p.out[(long long)token * p.out_stride + (long long)(kvh * G + row) * D + d] =
+          __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    }
   }
   cluster_sync_all();  // peers may have been reading this CTA's memory until here
+  if (p.parts > 1) merge_if_last<D>(p, seq, kvh, token, G);
 }
 
-template <int D, int ST, bool CLUSTER>
+// NARROW (at most 8 query heads per kv head): the keys are the 16 rows of the
+// tensor-core instruction and the query heads its 8 columns, S^T = K Q^T and
+// O^T = V^T P^T, half the instructions of the 16-query-row form, of whose rows
+// a grouping of 3 or 4 uses a quarter. P^T reaches the second product's operand
+// layout by a transposition inside the warp (movmatrix).
+template <int D, int ST, bool CLUSTER, bool NARROW>
 __global__ void __launch_bounds__(THREADS)
 attn_decode_kernel(const AttnParams p) {
   constexpr int KT = D / 16, NT = D / 8;
@@ -415,8 +464,9 @@ attn_decode_kernel(const AttnParams p) {
   const int pg1 = min(n_pages, pg0 + per);
   const int fresh = max(kv_len - (p.cu_tokens[seq + 1] - token), 0) / FB_PAGE;
 
-  float* ws_o = p.ws_o + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * D;
-  float* ws_ml = p.ws_ml + ((size_t)(seq * p.Kh + kvh) * p.splits + split) * 16 * 2;
+  // without clusters every CTA's result is a part of its own
+  float* ws_o = p.ws_o + ((size_t)(seq * p.Kh + kvh) * p.parts + split) * 16 * D;
+  float* ws_ml = p.ws_ml + ((size_t)(seq * p.Kh + kvh) * p.parts + split) * 16 * 2;
   constexpr int DP = D + 8;                                     // padded row of the warps' merge
   float* cO = reinterpret_cast<float*>(sK) + 4 * 16 * DP + 128;  // [16][D] (cluster merge)
   float* cM = cO + 16 * D;                                      // [16]
@@ -426,7 +476,7 @@ attn_decode_kernel(const AttnParams p) {
     fb_prefetch_l2_slice(p.next, p.next_bytes);
     if (CLUSTER) {
       for (int i = threadIdx.x; i < 16; i += THREADS) { cM[i] = -INFINITY; cL[i] = 0.f; }
-      merge_in_cluster<D>(p, cO, cM, cL, kvh, token, G);
+      merge_in_cluster<D>(p, cO, cM, cL, seq, kvh, token, G);
     } else if (p.splits > 1) {
       for (int i = threadIdx.x; i < G; i += THREADS) { ws_ml[2 * i] = -INFINITY; ws_ml[2 * i + 1] = 0.f; }
       merge_if_last<D>(p, seq, kvh, token, G);
@@ -440,132 +490,240 @@ attn_decode_kernel(const AttnParams p) {
   const __nv_bfloat16* kbase = p.k_cache + (long long)kvh * p.head_stride;
   const __nv_bfloat16* vbase = p.v_cache + (long long)kvh * p.head_stride;
 
-  auto load_page = [&](int ahead) {
-    const long long off = (long long)pages[pg0 + ahead] * p.page_stride;
-    load_tile<D>(sK + ahead * 64 * D, kbase + off, D, 64, 64);
-    load_tile<D>(sV + ahead * 64 * D, vbase + off, D, 64, 64);
+  // Every warp streams its own 16 keys (and values) of each page into its own rows
+  // of the page buffers and waits for nobody else's: no block barrier in the loop.
+  auto load_rows = [&](int buffer, int page) {
+    const long long off = (long long)page * p.page_stride;
+    constexpr int CH = D / 8;
+    for (int id = lane; id < 16 * CH; id += 32) {
+      const int r = warp * 16 + id / CH, c = id % CH;
+      const int so = buffer * 64 * D + Swz<D>::off(r, c * 8);
+      cp_async16(smem_u32(sK + so), kbase + off + r * D + c * 8, true);
+      cp_async16(smem_u32(sV + so), vbase + off + r * D + c * 8, true);
+    }
   };
   // old pages of the first ST - 1 go out now; they complete with the first group
 #pragma unroll
   for (int ahead = 0; ahead < ST - 1; ++ahead)
-    if (pg0 + ahead < min(pg1, fresh)) load_page(ahead);
+    if (pg0 + ahead < min(pg1, fresh)) load_rows(ahead, pages[pg0 + ahead]);
   fb_pdl_wait();
   // rows 0..G-1 of the tile are this kv head's query heads, consecutive in q
   load_tile<D>(sQ, p.q + (long long)token * p.q_stride + (long long)(kvh * G) * D, D, 16, G);
 #pragma unroll
   for (int ahead = 0; ahead < ST - 1; ++ahead) {
-    if (pg0 + ahead < pg1 && pg0 + ahead >= fresh) load_page(ahead);
+    if (pg0 + ahead < pg1 && pg0 + ahead >= fresh) load_rows(ahead, pages[pg0 + ahead]);
     cp_async_commit();  // one group per page, empty when there is no page
   }
 
+  // wide form: Q as the 16-row operand of S = Q K^T; o is O [16 queries, D].
+  // narrow form: Q as the 8-column operand of S^T = K Q^T; o is O^T [D, 8 queries].
+  constexpr int OT = NARROW ? KT : NT;
   uint32_t qf[KT][4];
-  float o[NT][4];
+  float o[OT][4];
 #pragma unroll
-  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  for (int n = 0; n < OT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  // wide: rows g, g + 8; narrow: queries 2t, 2t + 1 (the same in all lanes of a t)
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+  int next_page = pg0 + ST - 1 < pg1 ? pages[pg0 + ST - 1] : 0;
   for (int pg = pg0; pg < pg1; ++pg) {
     const int st = (pg - pg0) % ST;
-    if (pg + ST - 1 < pg1) {  // refill the buffer that the previous iteration finished with
-      const int into = (pg - pg0 + ST - 1) % ST;
-      const long long off = (long long)pages[pg + ST - 1] * p.page_stride;
-      load_tile<D>(sK + into * 64 * D, kbase + off, D, 64, 64);
-      load_tile<D>(sV + into * 64 * D, vbase + off, D, 64, 64);
-    }
+    __syncwarp();  // every lane has read the rows that the refill overwrites
+    // The page number of the refill was read an iteration ago: a warp issues in
+    // order, and a page-table read in front of the copies would hold up the whole
+    // iteration for a trip to L2.
+    const int refill_page = next_page;
+    if (pg + ST < pg1) next_page = pages[pg + ST];
+    if (pg + ST - 1 < pg1)  // refill the buffer that the previous iteration finished with
+      load_rows((pg - pg0 + ST - 1) % ST, refill_page);
     cp_async_commit();
     cp_async_wait<ST - 1>();  // all but the newest ST - 1 groups: page `pg` has landed
-    __syncthreads();
+    if (pg == pg0) __syncthreads();  // the queries came from all warps
+    else __syncwarp();               // the page's rows from this warp's lanes
     if (pg == pg0) {
+      if constexpr (NARROW) {
+        // 8 x 8 matrices of Q: rows = queries 0..7, columns = 8 consecutive elements;
+        // a lane then holds (query g; elements 2t, 2t + 1), the B operand's layout
+        if constexpr (KT == 1) {
+          uint32_t r[2];
+          ldsm_x2(r, smem_u32(sQ + Swz<D>::off(lane & 7, ((lane >> 3) & 1) * 8)));
+          qf[0][0] = r[0]; qf[0][1] = r[1];
+        } else {
 #pragma unroll
-      for (int k = 0; k < KT; ++k)
-        ldsm_x4(qf[k], smem_u32(sQ + Swz<D>::off(lane & 15, k * 16 + (lane >> 4) * 8)));
+          for (int k2 = 0; k2 < KT / 2; ++k2) {
+            uint32_t r[4];
+            ldsm_x4(r, smem_u32(sQ + Swz<D>::off(lane & 7, k2 * 32 + (lane >> 3) * 8)));
+            qf[2 * k2][0] = r[0]; qf[2 * k2][1] = r[1];
+            qf[2 * k2 + 1][0] = r[2]; qf[2 * k2 + 1][1] = r[3];
+          }
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < KT; ++k)
+          ldsm_x4(qf[k], smem_u32(sQ + Swz<D>::off(lane & 15, k * 16 + (lane >> 4) * 8)));
+      }
     }
     const int key0 = pg * FB_PAGE + warp * 16;  // this warp's 16 keys of the page
     if (key0 < kv_len) {
       const __nv_bfloat16* tK = sK + st * 64 * D;
       const __nv_bfloat16* tV = sV + st * 64 * D;
-      float s[2][4];
+      if constexpr (NARROW) {
+        // S^T [16 keys, 8 queries]: two accumulators take alternate k steps
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-#pragma unroll
-      for (int k = 0; k < KT; ++k) {
-        uint32_t b[4];
-        ldsm_x4(b, smem_u32(tK + Swz<D>::off(warp * 16 + (lane & 7) + (lane >> 4) * 8,
-                                            k * 16 + ((lane >> 3) & 1) * 8)));
-        mma_bf16(s[0], qf[k], b[0], b[1]);
-        mma_bf16(s[1], qf[k], b[2], b[3]);
-      }
-      float mx[2] = {m[0], m[1]};
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
+        for (int k = 0; k < KT; ++k) {
+          uint32_t a[4];
+          ldsm_x4(a, smem_u32(tK + Swz<D>::off(warp * 16 + (lane & 15), k * 16 + (lane >> 4) * 8)));
+          if (k & 1) mma_bf16(s2, a, qf[k][0], qf[k][1]);
+          else mma_bf16(s, a, qf[k][0], qf[k][1]);
+        }
+        // s[e]: key g + 8 (e >> 1), query 2t + (e & 1)
+        float mx[2] = {m[0], m[1]};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = s[n][e] * p.scale_log2;
-          if (key0 + n * 8 + 2 * t + (e & 1) >= kv_len) v = -INFINITY;
-          s[n][e] = v;
-          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          float v = (s[e] + s2[e]) * p.scale_log2;
+          if (key0 + g + (e >> 1) * 8 >= kv_len) v = -INFINITY;
+          s[e] = v;
+          mx[e & 1] = fmaxf(mx[e & 1], v);
         }
-      }
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      }
-      float corr[2], sum[2] = {0.f, 0.f};
+        for (int r = 0; r < 2; ++r) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 4));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 8));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 16));
+        }
+        // key0 < kv_len: the warp's first key is visible, so mx is finite
+        float corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-      for (int r = 0; r < 2; ++r) corr[r] = exp2f(m[r] - mx[r]);
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
+        for (int r = 0; r < 2; ++r) corr[r] = exp2f(m[r] - mx[r]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float pv = exp2f(s[n][e] - mx[e >> 1]);
-          s[n][e] = pv;
-          sum[e >> 1] += pv;
+          const float pv = exp2f(s[e] - mx[e & 1]);
+          s[e] = pv;
+          sum[e & 1] += pv;
         }
-      }
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-        l[r] = l[r] * corr[r] + sum[r];
-        m[r] = mx[r];
-      }
+        for (int r = 0; r < 2; ++r) {
+          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 4);
+          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 8);
+          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 16);
+          l[r] = l[r] * corr[r] + sum[r];
+          m[r] = mx[r];
+        }
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        o[n][0] *= corr[0]; o[n][1] *= corr[0];
-        o[n][2] *= corr[1]; o[n][3] *= corr[1];
-      }
-      uint32_t a[4];
-      a[0] = pack_bf16(s[0][0], s[0][1]);
-      a[1] = pack_bf16(s[0][2], s[0][3]);
-      a[2] = pack_bf16(s[1][0], s[1][1]);
-      a[3] = pack_bf16(s[1][2], s[1][3]);
+        for (int n = 0; n < OT; ++n) {
+          o[n][0] *= corr[0]; o[n][1] *= corr[1];
+          o[n][2] *= corr[0]; o[n][3] *= corr[1];
+        }
+        // P^T as the B operand: (keys 2t, 2t + 1 and 2t + 8, 2t + 9; query g)
+        const uint32_t b0 = movmatrix_trans(pack_bf16(s[0], s[1]));
+        const uint32_t b1 = movmatrix_trans(pack_bf16(s[2], s[3]));
 #pragma unroll
-      for (int n2 = 0; n2 < NT / 2; ++n2) {
-        uint32_t b[4];
-        ldsm_x4_trans(b, smem_u32(tV + Swz<D>::off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                                  n2 * 16 + (lane >> 4) * 8)));
-        mma_bf16(o[2 * n2], a, b[0], b[1]);
-        mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+        for (int n = 0; n < OT; ++n) {
+          // V^T [16 elements, 16 keys] from V [key][element], transposed on the way in
+          uint32_t a[4];
+          ldsm_x4_trans(a, smem_u32(tV + Swz<D>::off(warp * 16 + (lane & 7) + (lane >> 4) * 8,
+                                                    n * 16 + ((lane >> 3) & 1) * 8)));
+          mma_bf16(o[n], a, b0, b1);
+        }
+      } else {
+        float s[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int k = 0; k < KT; ++k) {
+          uint32_t b[4];
+          ldsm_x4(b, smem_u32(tK + Swz<D>::off(warp * 16 + (lane & 7) + (lane >> 4) * 8,
+                                              k * 16 + ((lane >> 3) & 1) * 8)));
+          mma_bf16(s[0], qf[k], b[0], b[1]);
+          mma_bf16(s[1], qf[k], b[2], b[3]);
+        }
+        float mx[2] = {m[0], m[1]};
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float v = s[n][e] * p.scale_log2;
+            if (key0 + n * 8 + 2 * t + (e & 1) >= kv_len) v = -INFINITY;
+            s[n][e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        }
+        float corr[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < 2; ++r) corr[r] = exp2f(m[r] - mx[r]);
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float pv = exp2f(s[n][e] - mx[e >> 1]);
+            s[n][e] = pv;
+            sum[e >> 1] += pv;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+          l[r] = l[r] * corr[r] + sum[r];
+          m[r] = mx[r];
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          o[n][0] *= corr[0]; o[n][1] *= corr[0];
+          o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        }
+        uint32_t a[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]);
+        a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]);
+        a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int n2 = 0; n2 < NT / 2; ++n2) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, smem_u32(tV + Swz<D>::off(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                    n2 * 16 + (lane >> 4) * 8)));
+          mma_bf16(o[2 * n2], a, b[0], b[1]);
+          mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+        }
       }
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   fb_prefetch_l2_slice(p.next, p.next_bytes);
+  __syncthreads();  // all warps are through with the page buffers
 
   // merge the four warps' (m, l, O) through shared memory (the page buffers are free now)
   float* sO = reinterpret_cast<float*>(sK);   // [4][16][DP], rows padded: fewer bank conflicts
   float* sM = sO + 4 * 16 * DP;               // [4][16]
   float* sL = sM + 4 * 16;                    // [4][16]
+  if constexpr (NARROW) {
+    // o[n][e]: element 16 n + g + 8 (e >> 1) of query 2t + (e & 1); rows 8..15 stay unused
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = g + r * 8;
-    if (t == 0) { sM[warp * 16 + row] = m[r]; sL[warp * 16 + row] = l[r]; }
+    for (int r = 0; r < 2; ++r) {
+      const int row = 2 * t + r;
+      if (g == 0) { sM[warp * 16 + row] = m[r]; sL[warp * 16 + row] = l[r]; }
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      *reinterpret_cast<float2*>(sO + (warp * 16 + row) * DP + n * 8 + 2 * t) =
-          make_float2(o[n][2 * r], o[n][2 * r + 1]);
+      for (int n = 0; n < OT; ++n) {
+        sO[(warp * 16 + row) * DP + n * 16 + g] = o[n][r];
+        sO[(warp * 16 + row) * DP + n * 16 + g + 8] = o[n][2 + r];
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + r * 8;
+      if (t == 0) { sM[warp * 16 + row] = m[r]; sL[warp * 16 + row] = l[r]; }
+#pragma unroll
+      for (int n = 0; n < OT; ++n) {
+        *reinterpret_cast<float2*>(sO + (warp * 16 + row) * DP + n * 8 + 2 * t) =
+            make_float2(o[n][2 * r], o[n][2 * r + 1]);
+      }
     }
   }
   __syncthreads();
@@ -593,7 +751,7 @@ attn_decode_kernel(const AttnParams p) {
           __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
     }
   }
-  if (CLUSTER) merge_in_cluster<D>(p, cO, cM, cL, kvh, token, G);
+  if (CLUSTER) merge_in_cluster<D>(p, cO, cM, cL, seq, kvh, token, G);
   else if (p.splits > 1) merge_if_last<D>(p, seq, kvh, token, G);
 }
 
@@ -611,7 +769,7 @@ int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
   return fb_check_launch("attention_prefill");
 }
 
-template <int D, int ST, bool CLUSTER>
+template <int D, int ST, bool CLUSTER, bool NARROW>
 int launch_decode_as(const AttnParams& p, cudaStream_t stream) {
   int bytes = (16 + 2 * ST * 64) * D * 2;
   // the merge reuses the page buffers: four warps' outputs, their (max, sum),
@@ -620,26 +778,30 @@ int launch_decode_as(const AttnParams& p, cudaStream_t stream) {
   if (merge > bytes) bytes = merge;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, ST, CLUSTER>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, ST, CLUSTER, NARROW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
     configured = true;
   }
   const dim3 grid(p.n_seqs, p.Kh, p.splits);
   if (CLUSTER)
-    fb_launch_cluster(attn_decode_kernel<D, ST, CLUSTER>, grid, dim3(THREADS), bytes, stream,
-                      (unsigned)p.splits, p);
+    fb_launch_cluster(attn_decode_kernel<D, ST, CLUSTER, NARROW>, grid, dim3(THREADS), bytes, stream,
+                      (unsigned)p.cluster, p);
   else
-    fb_launch(attn_decode_kernel<D, ST, CLUSTER>, grid, dim3(THREADS), bytes, stream, p);
+    fb_launch(attn_decode_kernel<D, ST, CLUSTER, NARROW>, grid, dim3(THREADS), bytes, stream, p);
   return fb_check_launch("attention_decode");
 }
 
-// Several CTAs per (sequence, kv head) merge inside a cluster when the caller
-// gave no workspace, else through the workspace and the arrival counters.
+// Several CTAs per (sequence, kv head) merge inside clusters of p.cluster, and
+// what is left (all of them when p.cluster is 1) through the workspace.
 template <int D, int ST>
 int launch_decode(const AttnParams& p, cudaStream_t stream) {
-  if (p.splits > 1 && p.ws_o == nullptr) return launch_decode_as<D, ST, true>(p, stream);
-  return launch_decode_as<D, ST, false>(p, stream);
+  const bool narrow = p.A / p.Kh <= 8;
+  if (p.cluster > 1)
+    return narrow ? launch_decode_as<D, ST, true, true>(p, stream)
+                  : launch_decode_as<D, ST, true, false>(p, stream);
+  return narrow ? launch_decode_as<D, ST, false, true>(p, stream)
+                : launch_decode_as<D, ST, false, false>(p, stream);
 }
 
 int check_common(const char* what, int n_seqs, int A, int Kh, int D, long long q_stride,
@@ -686,20 +848,22 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
   }
 }
 
-// One token per sequence. `splits` CTAs share each (sequence, kv head). Up to
-// 8 of them merge their partial results inside a thread-block cluster when no
-// workspace is given (ws_o, ws_ml, counters all null). With workspaces (any
-// split count) they must hold n_seqs*Kh*splits*16*D and
-// n_seqs*Kh*splits*32 floats, and `counters` n_seqs*Kh ints that are zero when
-// the call starts (the kernel leaves them zero again). `stages` (2 or 3) is the
-// number of page buffers per CTA. A sequence with kv_lens == 0 is padding: its
-// output rows are zeros.
+// One token per sequence. `splits` CTAs share each (sequence, kv head).
+// `cluster` of them (up to 8; a divisor of `splits`; 0 or 1 for none) form a
+// thread-block cluster and merge their partial results through each other's
+// shared memory. The splits / cluster results per pair that are left (`parts`;
+// all of them without clusters) meet in the workspaces, which must hold
+// n_seqs*Kh*parts*16*D and n_seqs*Kh*parts*32 floats, with `counters` of
+// n_seqs*Kh ints that are zero when the call starts (the kernel leaves them zero
+// again); with one part per pair they are not used and may be null. `stages`
+// (2 or 3) is the number of page buffers per CTA. A sequence with kv_lens == 0
+// is padding: its output rows are zeros.
 FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                const int* cu_tokens, const int* kv_lens, const int* page_table,
                                int max_pages, const void* k_cache, const void* v_cache,
                                long long page_stride, long long head_stride, int n_seqs, int A,
-                               int Kh, int D, float scale, int splits, int stages, float* ws_o,
-                               float* ws_ml, int* counters, const void* next,
+                               int Kh, int D, float scale, int splits, int stages, int cluster,
+                               float* ws_o, float* ws_ml, int* counters, const void* next,
                                long long next_bytes, cudaStream_t stream) {
   FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
              "attention_decode: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
@@ -707,10 +871,14 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
                         v_cache, page_stride, head_stride);
   if (rc) return rc;
   FB_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: bad split count %d", splits);
-  FB_REQUIRE(splits == 1 || (ws_o && ws_ml && counters) ||
-                 (!ws_o && !ws_ml && !counters && splits <= MAX_CLUSTER),
-             "attention_decode: %d split results need workspaces and counters (up to %d merge "
-             "in a cluster without)", splits, MAX_CLUSTER);
+  if (cluster < 1) cluster = 1;
+  FB_REQUIRE(cluster <= MAX_CLUSTER && splits % cluster == 0,
+             "attention_decode: clusters of %d do not divide %d splits (or exceed %d)", cluster,
+             splits, MAX_CLUSTER);
+  const int parts = splits / cluster;
+  FB_REQUIRE(parts == 1 || (ws_o && ws_ml && counters && ((uintptr_t)ws_ml % 8) == 0),
+             "attention_decode: %d partial results per pair need workspaces (8-byte aligned) "
+             "and counters", parts);
   AttnParams p{};
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride;
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;
@@ -718,7 +886,8 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.page_stride = page_stride; p.head_stride = head_stride;
   p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E;
-  p.splits = splits; p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
+  p.splits = splits; p.cluster = cluster; p.parts = parts;
+  p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
   p.next = next; p.next_bytes = next_bytes;
   FB_REQUIRE(stages == 2 || stages == 3, "attention_decode: %d page buffers (2 or 3)", stages);
   if (stages == 2) {
@@ -806,5 +975,5 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, 3, ws_o, ws_ml, counters, nullptr, 0, stream);
+                             D, scale, splits, 3, 1, ws_o, ws_ml, counters, nullptr, 0, stream);
 }

@@ -60,7 +60,8 @@ _SIGNATURES = {
     "fb_attention_tc_status": [c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p],
+                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
+                            c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
 }
@@ -783,16 +784,19 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
 
 def decode_plan(pairs: int, pages: int):
     """(splits, page buffers) of decode attention for `pairs` (sequence, kv head)
-    pairs of up to `pages` cache pages, as measured on B200 with head size 128
-    at 3,072 tokens of context. Three page buffers per CTA (two pages on their
-    way while one is multiplied), of which two CTAs fit an SM; ranges are split
-    while all CTAs stay resident at once (a second round of CTAs cost 10 us a
-    call), at most eightfold (one cluster), or sixteenfold for long contexts."""
+    pairs of up to `pages` cache pages, as measured on B200 with head size 128.
+    Three page buffers per CTA (two pages on their way while one is multiplied),
+    of which two CTAs fit an SM; ranges are split while all CTAs stay resident at
+    once (a second round of CTAs cost 10 us a call). Up to eight CTAs of a pair
+    are one cluster; a long context with few pairs takes several clusters, whose
+    results meet in the workspace (a warp walks a page in 0.6 us whatever else
+    runs, so a range's length is what a short batch waits for)."""
     room = 2 * SM_COUNT // max(pairs, 1)
-    if pages >= 128 and room >= 16:
-        # a long context and few pairs: 16 shares through the workspace merge were 4 %
-        # faster than 8 in a cluster at 16 K tokens (12 and more were slower at 3 K)
-        return 16, 3
+    if room >= 16 and pages >= 160:
+        # clusters of 8 while a CTA keeps 4 pages or more; the second merge costs
+        # 3 to 4 us, which pays from about 10 K tokens on (batch 1 at 16 K tokens:
+        # 26.7 us with 8 shares, 19.4 with 32; at 4 K: 10.6 against 12.9)
+        return min(room // 8 * 8, max(16, pages // 4 // 8 * 8)), 3
     return max(1, min(DECODE_CLUSTER_MAX, pages, room)), 3
 
 
@@ -841,27 +845,35 @@ DECODE_CLUSTER = _os.environ.get("FOUNDRY_B200_DECODE_CLUSTER", "1") != "0"
 
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
                      num_kv_heads, head_dim, scale, splits, stages: int = 3,
-                     then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     then_reads: Optional[torch.Tensor] = None,
+                     cluster: Optional[int] = None) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
-    over `splits` CTAs per (sequence, kv head). Up to 8 form a thread-block
-    cluster and merge their partial results through each other's shared memory;
-    more write them to a workspace, and the CTA that finishes a pair last merges. `then_reads`: weights to ask into L2 for
+    over `splits` CTAs per (sequence, kv head). `cluster` of them (by default as
+    many as divide `splits`, up to 8) form a thread-block cluster and merge their
+    partial results through each other's shared memory; the clusters' results
+    (or, without clusters, every CTA's) go to a workspace, and the CTA that
+    finishes a pair last merges them. `then_reads`: weights to ask into L2 for
     the kernel that follows (see `gemm_skinny`)."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
     n = kv_lens.numel()
+    if cluster is None:
+        cluster = 1
+        if DECODE_CLUSTER:
+            cluster = max(c for c in range(1, DECODE_CLUSTER_MAX + 1) if splits % c == 0)
+    parts = splits // max(cluster, 1)
     ws_o = ws_ml = counters = None
-    if splits > DECODE_CLUSTER_MAX or (splits > 1 and not DECODE_CLUSTER):
-        ws_o = torch.empty(n * num_kv_heads * splits * 16 * head_dim, dtype=torch.float32,
+    if parts > 1:
+        ws_o = torch.empty(n * num_kv_heads * parts * 16 * head_dim, dtype=torch.float32,
                            device=q.device)
-        ws_ml = torch.empty(n * num_kv_heads * splits * 32, dtype=torch.float32, device=q.device)
+        ws_ml = torch.empty(n * num_kv_heads * parts * 32, dtype=torch.float32, device=q.device)
         counters = _arrival_counters(q.device, n * num_kv_heads)
     _call("fb_attention_decode", _dev(q, "q", torch.bfloat16, contiguous=False), _rows(q, "q"),
           _dev(out, "out", torch.bfloat16, contiguous=False), _rows(out, "out"),
           _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
-          head_dim, float(scale), splits, stages, 0 if ws_o is None else ws_o.data_ptr(),
-          0 if ws_ml is None else ws_ml.data_ptr(),
+          head_dim, float(scale), splits, stages, cluster,
+          0 if ws_o is None else ws_o.data_ptr(), 0 if ws_ml is None else ws_ml.data_ptr(),
           0 if counters is None else counters.data_ptr(), *_prefetch_range(then_reads),
           _stream())
     return out

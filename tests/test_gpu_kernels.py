@@ -234,6 +234,9 @@ ATT_CASES = [  # (q lengths, kv lengths, heads, kv heads, head_dim)
     ([1, 1, 1, 1], [200, 3, 128, 129], 6, 2, 32),
     ([1, 1], [500, 77], 8, 8, 64),
     ([1, 1, 1], [300, 64, 1000], 12, 4, 128),
+    ([1, 1, 1], [90, 10, 260], 16, 2, 64),  # 8 query heads per kv head: the narrow form's most
+    ([1, 1], [150, 70], 12, 1, 32),  # 12 per kv head: the 16-row form
+    ([1, 1], [33, 190], 5, 1, 16),
     ([5, 70, 1], [5, 70, 130], 4, 2, 16),
     ([64, 65, 3], [64, 65, 200], 6, 3, 32),
     ([130, 20], [130, 220], 4, 1, 64),
@@ -286,8 +289,11 @@ def test_attention_tcgen05_any_token_counts(ops, lens_q, lens_kv, A, Kh, D):
 
 
 @pytest.mark.parametrize("lens_q,lens_kv,A,Kh,D", [c for c in ATT_CASES if max(c[0]) == 1])
-@pytest.mark.parametrize("splits", [1, 2, 7, 12])
-def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, splits):
+@pytest.mark.parametrize("splits,cluster", [(1, None), (2, None), (7, None), (7, 1), (12, None),
+                                            (12, 4), (16, None), (24, 8)])
+def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, splits, cluster):
+    """Ranges merged in one cluster, through the workspace alone (cluster 1), and
+    in several clusters whose results meet in the workspace."""
     # a padding row (length 0) sits between the real ones and must come out as zeros
     lens_q, lens_kv = list(lens_q), list(lens_kv)
     case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, torch.bfloat16, seed=2, sharp=True)
@@ -298,7 +304,7 @@ def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, sp
     for stages in (2, 3):
         out = torch.full_like(q, 5.0)
         ops.attention_decode(q, out, cu, kv, table, case["k"], case["v"], A, Kh, D,
-                             1.0 / math.sqrt(D), splits, stages)
+                             1.0 / math.sqrt(D), splits, stages, cluster=cluster)
         close(out[:-1], want, 3e-2, 1e-2)
         assert float(out[-1].abs().max()) == 0.0
 
