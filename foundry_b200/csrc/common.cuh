@@ -37,14 +37,21 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
 // calls `fb_pdl_wait()` before it reads anything an earlier kernel wrote and
 // before it writes anything an earlier kernel may still read (only constants
 // such as weights may be touched before; the products request their first
-// weight tiles there). Only the short kernels of few blocks (norm, rotary)
-// trigger their successor early (griddepcontrol.launch_dependents). Measured on
-// the 3B decode step: when the long kernels triggered early too, blocks of later
-// kernels sat waiting on the SMs, held registers and shared memory that the
-// running kernel's next blocks needed, and the step took half as long again.
-// The prompt step lost too: with the persistent product or the prompt attention
-// triggering early, 12.1 ms became 13.0 to 13.8 ms (the successors' blocks wait
-// on the SMs beside the running kernel and slow it).
+// weight tiles there). When a kernel lets its successor's blocks be placed
+// (griddepcontrol.launch_dependents) decides whether that helps. The short
+// kernels of few blocks (norm, rotary) do it at once. The single-token products
+// do it when a block's main loop is through (its last loads are on their way, the
+// epilogue is left): the successor's blocks then take the places that this
+// kernel's blocks leave and have their first weights requested when it ends (3B
+// decode step at batch 8: 2.09 -> 1.98 ms). The single-token attention doing the
+// same lost (2.01 -> 2.56 ms: its blocks end at different times and still have
+// their merge across the cluster to do while the successor's sit beside them), and
+// in the tcgen05 products (after the last tile's loads) it changed nothing. At the
+// START of a long kernel the same instruction lost, on the decode step (blocks of
+// later kernels sat waiting on the SMs, held registers and shared memory that the
+// running kernel's next blocks needed, and the step took half as long again) and
+// on the prompt step (with the persistent product or the prompt attention
+// triggering at their start, 12.1 ms became 13.0 to 13.8 ms).
 // Every kernel reads what an earlier kernel wrote with ordinary (coherent)
 // loads only: pointers to such data carry no `__restrict__` read-only promise
 // and no `ld.global.nc`, because after an early trigger the writer may still
@@ -95,9 +102,8 @@ inline cudaError_t fb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 b
 
 #ifdef __CUDACC__
 __device__ __forceinline__ void fb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Lets the next kernel's blocks be placed now. Only for short kernels of few
-// blocks (norm, rotary): the product or attention kernel that follows then sits
-// ready, its first weight tiles requested, when this kernel ends.
+// Lets the next kernel's blocks be placed as soon as every block of this kernel
+// has said so or ended (see the notes on launching above for where to call it).
 __device__ __forceinline__ void fb_pdl_launch() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

@@ -200,6 +200,37 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
   return fb_check_launch("add_rmsnorm");
 }
 
+// ------------------------------------------------- a deferred norm's row scale
+// out[t, i] = values[t, i] / sqrt(sum_c shares[c * stride + t] / dim + eps): the
+// plain tensor of a norm whose scale the weight-streaming products would have
+// applied themselves (gemm_skinny.cu), for a consumer that is none of them.
+__global__ void apply_row_scale_kernel(const __nv_bfloat16* values, long long ld,
+                                       const float* shares, int count, int stride, float inv_dim,
+                                       float eps, __nv_bfloat16* __restrict__ out, long long ldo,
+                                       int H) {
+  fb_pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < count; c += blockDim.x) sum += shares[(size_t)c * stride + t];
+  sum = fb_block_sum(sum, scratch);
+  const float r = 1.0f / sqrtf(sum * inv_dim + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[t * ldo + i] = __float2bfloat16_rn(__bfloat162float(values[t * ld + i]) * r);
+}
+
+FB_API int fb_apply_row_scale(const void* values, long long ld, const float* shares, int count,
+                              int stride, int dim, float eps, void* out, long long ldo, int T,
+                              int H, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && H > 0 && count > 0 && stride >= T && dim > 0 && eps > 0.f,
+             "apply_row_scale: bad sizes T=%d H=%d count=%d stride=%d", T, H, count, stride);
+  if (T == 0) return 0;
+  fb_launch(apply_row_scale_kernel, dim3(T), dim3(256), 0, stream,
+            (const __nv_bfloat16*)values, ld, shares, count, stride, 1.0f / (float)dim, eps,
+            (__nv_bfloat16*)out, ldo, H);
+  return fb_check_launch("apply_row_scale");
+}
+
 // ------------------------------------------------------------- SiLU(g) * u
 // gate_up is [T, 2I]. Plain layout: columns [0, I) hold the gate, [I, 2I) the
 // up projection. Interleaved layout: column 2i holds gate i, column 2i+1 up i

@@ -23,6 +23,16 @@
 // pair with in the rotation, so that a thread's two accumulator rows are a
 // rotation pair and nothing crosses CTAs.
 //
+// Two more pieces take the RMS norm between two projections out of the step
+// as a kernel of its own (y = x / sqrt(mean(x^2) + eps) * g, src/nn/norm.rs:31-51).
+// The projection BEFORE the norm adds its result to the float32 residual rows
+// in its epilogue, writes resid * g in bfloat16 for the next projection, and
+// leaves each CTA's share of the rows' sums of squares ("residual sink"). The
+// projection AFTER the norm sums those shares (in a fixed order) and multiplies
+// its accumulators by 1 / sqrt(mean + eps): the product is linear in the row
+// scale, so scaling after the sum over K is the same normalisation, with the one
+// rounding to bfloat16 made before the scale instead of after it.
+//
 // Larger token counts run on the tcgen05 kernel (gemm_tcgen05.cu).
 #include "common.cuh"
 
@@ -74,23 +84,57 @@ struct RopeWrite {
   int write_cache;          // 0: keys and values are not computed at all
 };
 struct NoRope {};
+
+// Most shares of a row scale (rows of 64 bytes in the consumer's shared memory,
+// within the 48 KB a kernel has without opting in for more, beside its own).
+constexpr int FB_SKINNY_MAX_SHARES = 384;
+
+// Row scale of the input: token t's accumulators are multiplied by
+// 1 / sqrt(sum_c ss[c * stride + t] * inv_dim + eps). ss == nullptr: no scale.
+struct RowScale {
+  const float* ss;
+  int count, stride;
+  float inv_dim, eps;
+};
+// Residual sink (epilogue 3): resid[t, n] += out[t, n]; xg[t, n] = bf16(resid * gamma[n]);
+// ss_out[blockIdx.x * ss_stride + t] = this CTA's sum over its rows of resid^2.
+struct ResidualSink {
+  float* resid;
+  long long ldr;
+  const float* gamma;
+  __nv_bfloat16* xg;
+  long long ldxg;
+  float* ss_out;
+  int ss_stride;
+};
 template <bool ROPE> struct RopeArg { using type = NoRope; };
 template <> struct RopeArg<true> { using type = RopeWrite; };
+struct NoSink {};
+template <bool SINK> struct SinkArg { using type = NoSink; };
+template <> struct SinkArg<true> { using type = ResidualSink; };
+// what a kernel instance ends with
+constexpr int MODE_PLAIN = 0;  // store, or SiLU(gate) * up
+constexpr int MODE_ROPE = 1;   // rotate and write queries, keys, values
+constexpr int MODE_SINK = 2;   // add into the residual rows in front of a norm
 
 // NT: token tiles of 8 (1 or 2). WARPS: warps per CTA, each with a K range.
 // UNROLL: chunks whose loads are in flight together.
-// No register cap beyond the block size: the compiler's own choice (128
-// registers with four chunks in flight, so four CTAs of 4 warps on an SM) was
-// the fastest on the 3B decode step. Capped to 96 registers (five CTAs) the
-// 1,024 CTAs of the gate/up product run as 740 and a thin 284, which was slower.
-template <int NT, int WARPS, int UNROLL, bool ROPE>
-__global__ void __launch_bounds__(WARPS * 32)
+// Registers are capped at 128 (four chunks in flight; four CTAs of 4 warps on
+// an SM), the fastest on the 3B decode step: at 130 the gate/up product of 8
+// tokens ran three CTAs to an SM and took 3 us longer; capped to 96 (five CTAs)
+// its 1,024 CTAs run as 740 and a thin 284, which was slower too.
+template <int NT, int WARPS, int UNROLL, int MODE>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
 gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
                    const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
                    long long ldo, int out_f32, int T, int N, int K, int epilogue,
                    const void* next, long long next_bytes, long long plane_stride,
-                   const typename RopeArg<ROPE>::type rw) {
+                   const typename RopeArg<MODE == MODE_ROPE>::type rw, const RowScale scale,
+                   const typename SinkArg<MODE == MODE_SINK>::type sink) {
+  constexpr bool ROPE = MODE == MODE_ROPE, SINK = MODE == MODE_SINK;
   __shared__ float red[WARPS][16][8 * NT + 1];
+  __shared__ float scale_part[4][16];
+  extern __shared__ __align__(16) float shares[];  // [scale.count][16] when there is a row scale
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -155,6 +199,65 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   const int full_end = min(c1, K / CHUNK);  // chunks that lie entirely inside K
   int c = c0;
   bool waited = false;
+  // What the epilogue needs from the kernel before this one is asked for as soon
+  // as that kernel is through, so that nothing is fetched at the end: the shares
+  // of the row scale go to shared memory behind the weight stream (cp.async), a
+  // thread's old residual values and norm weights into registers.
+  constexpr int SINK_ITEMS = SINK ? (16 * 8 * NT + WARPS * 32 - 1) / (WARPS * 32) : 1;
+  float old_resid[SINK_ITEMS], gamma[SINK_ITEMS];
+  auto after_wait = [&]() {
+    fb_pdl_wait();
+    if (scale.ss != nullptr) {
+      // Every CTA of the grid wants the same few lines: through L1 (.ca), so that
+      // the CTAs of an SM ask L2 once, and only the T floats of a row that count
+      // (with .cg and whole rows the 1,024 CTAs of a gate/up product queued up
+      // at the L2 slices of those lines for 5 us).
+      const int pieces = (T + 3) >> 2;  // 16-byte pieces of a 64-byte row
+      for (int i = threadIdx.x; i < scale.count * pieces; i += WARPS * 32) {
+        const int off = (i / pieces) * 16 + (i % pieces) * 4;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(shares + off);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(scale.ss + off)
+                     : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if constexpr (SINK) {
+      {
+#pragma unroll
+        for (int it = 0; it < SINK_ITEMS; ++it) {
+          const int idx = threadIdx.x + it * WARPS * 32;
+          const int row = idx & 15, tok = idx >> 4;
+          const bool live = tok < T && n0 + row < N;
+          old_resid[it] = live ? *reinterpret_cast<const volatile float*>(
+                                     sink.resid + (size_t)tok * sink.ldr + n0 + row) : 0.f;
+          gamma[it] = live ? sink.gamma[n0 + row] : 0.f;
+        }
+      }
+    }
+  };
+  // The row scales, in a fixed order and in few instructions. Called once by every
+  // thread, right after the first loads of x have gone out, so that waiting for
+  // the shares costs nothing beyond waiting for x (at the end of the kernel, where
+  // every CTA of an SM arrives together and nothing else hides it, the same work
+  // cost the gate/up product of 8 tokens 1.5 us, and 5 us as a loop of whole warps
+  // over the tokens). Of the first 128 threads, thread i sums every GROUPS-th share
+  // of token i % TOKS; the groups of a warp meet by shuffles, the four warps' sums
+  // in shared memory, where every thread of the epilogue adds its token's four and
+  // takes the root.
+  auto finish_scale = [&]() {
+    if (scale.ss == nullptr) return;
+    constexpr int TOKS = 8 * NT, GROUPS = 128 / TOKS;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int tok = threadIdx.x & (TOKS - 1);
+      float sum = 0.f;
+      for (int c0 = threadIdx.x / TOKS; c0 < scale.count; c0 += GROUPS) sum += shares[c0 * 16 + tok];
+#pragma unroll
+      for (int o = TOKS; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane < TOKS) scale_part[warp][lane] = sum;
+    }
+  };
   for (; c + UNROLL <= full_end; c += UNROLL) {
     uint4 a[UNROLL][4];
     uint4 b[UNROLL][NT][2];
@@ -166,8 +269,9 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
       a[u][2] = ld_stream(w1 + off);
       a[u][3] = ld_stream(w1 + off + 32);
     }
-    if (!waited) {
-      fb_pdl_wait();
+    const bool first = !waited;
+    if (first) {
+      after_wait();
       waited = true;
     }
 #pragma unroll
@@ -179,10 +283,14 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
         b[u][j][1] = ld_cached(xr[j] + off + 32);
       }
     }
+    if (first) finish_scale();
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) multiply(a[u], b[u]);
   }
-  if (!waited) fb_pdl_wait();
+  if (!waited) {
+    after_wait();
+    finish_scale();
+  }
   // the rest: single chunks, the last of which may reach beyond K
   for (; c < c1; ++c) {
     const size_t off = (size_t)c * CHUNK;
@@ -203,6 +311,10 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   }
   // this block's weights are in; the kernel after this one can have its own on the way
   fb_prefetch_l2_slice(next, next_bytes);
+  // ... and its blocks may be placed as this kernel's leave: the weights' last bytes
+  // are on their way, what is left is the epilogue. (At the start of the kernel the
+  // same instruction lost: the next kernel's blocks then take the room of this one's.)
+  fb_pdl_launch();
   // acc[j][0..1]: row g, tokens j*8 + 2t, 2t+1; acc[j][2..3]: row g + 8
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
@@ -212,6 +324,13 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
     red[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
   }
   __syncthreads();
+  // token `tok`'s scale, by whoever needs it (no barrier more for a shared copy)
+  auto row_scale = [&](int tok) {
+    if (scale.ss == nullptr) return 1.f;
+    const float sum = (scale_part[0][tok] + scale_part[1][tok]) +
+                      (scale_part[2][tok] + scale_part[3][tok]);
+    return 1.0f / sqrtf(sum * scale.inv_dim + scale.eps);
+  };
   float* out_f = reinterpret_cast<float*>(out) + (size_t)blockIdx.y * plane_stride;
   __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(out);
   if constexpr (ROPE) {
@@ -226,6 +345,9 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
         x1 += red[wi][p][tok];
         x2 += red[wi][p + 8][tok];
       }
+      const float rs = row_scale(tok);
+      x1 *= rs;
+      x2 *= rs;
       const int pos = rw.positions[tok];
       if (rotated) {
         float sn, cs;
@@ -249,6 +371,28 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
       dst[e_lo + p] = __float2bfloat16_rn(x1);
       dst[e_hi + p] = __float2bfloat16_rn(x2);
     }
+  } else if constexpr (SINK) {
+    // 16 consecutive lanes hold a token's 16 rows of this CTA
+#pragma unroll
+    for (int it = 0; it < SINK_ITEMS; ++it) {
+      const int idx = threadIdx.x + it * WARPS * 32;
+      if (idx < 16 * 8 * NT) {  // whole warps are in or out
+        const int row = idx & 15, tok = idx >> 4;
+        const bool live = tok < T && n0 + row < N;
+        float v = 0.f;
+        if (live) {
+#pragma unroll
+          for (int wi = 0; wi < WARPS; ++wi) v += red[wi][row][tok];
+          v = old_resid[it] + v * row_scale(tok);
+          sink.resid[(size_t)tok * sink.ldr + n0 + row] = v;
+          sink.xg[(size_t)tok * sink.ldxg + n0 + row] = __float2bfloat16_rn(v * gamma[it]);
+        }
+        float sq = v * v;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (row == 0 && tok < T) sink.ss_out[(size_t)blockIdx.x * sink.ss_stride + tok] = sq;
+      }
+    }
   } else {
     if (epilogue == 0) {
       for (int idx = threadIdx.x; idx < 16 * T; idx += WARPS * 32) {
@@ -257,6 +401,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
         float v = 0.f;
 #pragma unroll
         for (int wi = 0; wi < WARPS; ++wi) v += red[wi][row][tok];
+        v *= row_scale(tok);
         const size_t o = (size_t)tok * ldo + n0 + row;
         if (out_f32) out_f[o] = v;
         else out_h[o] = __float2bfloat16_rn(v);
@@ -272,6 +417,9 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
           gate += red[wi][2 * p][tok];
           up += red[wi][2 * p + 1][tok];
         }
+        const float rs = row_scale(tok);
+        gate *= rs;
+        up *= rs;
         out_h[(size_t)tok * ldo + (n0 >> 1) + p] =
             __float2bfloat16_rn(gate / (1.0f + __expf(-gate)) * up);
       }
@@ -282,7 +430,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
 int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, void* out,
                   long long ldo, int out_f32, int T, int N, int K, int epilogue, const void* next,
                   long long next_bytes, int ksplit, long long plane_stride, int warps,
-                  const RopeWrite& rw, cudaStream_t stream) {
+                  const RopeWrite& rw, const RowScale& scale, const ResidualSink& sink,
+                  cudaStream_t stream) {
   FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
              "gemm_skinny: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
   FB_REQUIRE(T > 0 && T <= 16 && N > 0 && K > 0, "gemm_skinny: bad sizes T=%d N=%d K=%d", T, N, K);
@@ -296,6 +445,16 @@ int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, vo
              "gemm_skinny: %d K shares need float32 planes and the plain epilogue", ksplit);
   FB_REQUIRE(warps == 0 || warps == 4 || warps == 8 || warps == 16,
              "gemm_skinny: %d warps per CTA (4, 8 or 16)", warps);
+  FB_REQUIRE(scale.ss == nullptr || (scale.count > 0 && scale.count <= FB_SKINNY_MAX_SHARES &&
+                                     scale.stride == 16 && ((uintptr_t)scale.ss % 16) == 0 &&
+                                     scale.inv_dim > 0.f && scale.eps > 0.f),
+             "gemm_skinny: the row scale needs 1..%d shares in 16-byte aligned rows of 16 floats "
+             "and a positive eps", FB_SKINNY_MAX_SHARES);
+  const size_t shares_bytes = scale.ss != nullptr ? (size_t)scale.count * 64 : 0;
+  FB_REQUIRE(epilogue != 3 || (sink.resid && sink.gamma && sink.xg && sink.ss_out &&
+                               sink.ldr >= N && sink.ldxg >= N && sink.ss_stride >= T),
+             "gemm_skinny: the residual sink needs its four arrays, rows of %d and shares of %d",
+             N, T);
   const int blocks = (N + 15) / 16;
   // Warps per CTA: as many as still let every CTA of the grid be resident at
   // once (one CTA of 16 warps, two of 8 or five of 4 fit an SM). A second, thin
@@ -309,14 +468,17 @@ int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, vo
   }
   const int per = (chunks + warps - 1) / warps;
   const int unroll = per >= 4 ? 4 : per >= 3 ? 3 : 2;
-#define FB_SKINNY_R(NT, W, U, R, EXTRA)                                                       \
-  fb_launch(gemm_skinny_kernel<NT, W, U, R>, dim3(blocks, ksplit), dim3(W * 32), 0, stream,    \
-            (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw, out, ldo, out_f32, T, N, \
-            K, epilogue, next, next_bytes, plane_stride, EXTRA)
-#define FB_SKINNY(NT, W, U)                                   \
-  do {                                                        \
-    if (epilogue == 2) FB_SKINNY_R(NT, W, U, true, rw);       \
-    else FB_SKINNY_R(NT, W, U, false, NoRope{});              \
+#define FB_SKINNY_R(NT, W, U, MODE, ROPE_ARG, SINK_ARG)                                        \
+  do {                                                                                         \
+  fb_launch(gemm_skinny_kernel<NT, W, U, MODE>, dim3(blocks, ksplit), dim3(W * 32),            \
+            shares_bytes, stream, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw,   \
+            out, ldo, out_f32, T, N, K, epilogue, next, next_bytes, plane_stride, ROPE_ARG,     \
+            scale, SINK_ARG); } while (0)
+#define FB_SKINNY(NT, W, U)                                                      \
+  do {                                                                           \
+    if (epilogue == 2) FB_SKINNY_R(NT, W, U, MODE_ROPE, rw, NoSink{});            \
+    else if (epilogue == 3) FB_SKINNY_R(NT, W, U, MODE_SINK, NoRope{}, sink);     \
+    else FB_SKINNY_R(NT, W, U, MODE_PLAIN, NoRope{}, NoSink{});                   \
   } while (0)
 #define FB_SKINNY_U(NT, W)                                    \
   do {                                                        \
@@ -348,21 +510,48 @@ int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, vo
 // ksplit > 1: K is shared by ksplit CTAs per row group and out is ksplit float32
 // planes [T, N], plane_stride elements apart, for a consumer that sums them
 // (epilogue 0 only). warps: 4, 8 or 16 per CTA, or 0 to have it chosen here.
+// scale_ss (or null): x is resid * g of a norm whose 1 / sqrt(mean + eps) is
+// still missing; token t's results are multiplied by
+// 1 / sqrt(sum_c scale_ss[c * scale_stride + t] / scale_dim + scale_eps), c < scale_count.
 FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long ldw, void* out,
                           long long ldo, int out_f32, int T, int N, int K, int epilogue,
                           const void* next, long long next_bytes, int ksplit,
-                          long long plane_stride, int warps, cudaStream_t stream) {
+                          long long plane_stride, int warps, const float* scale_ss,
+                          int scale_count, int scale_stride, int scale_dim, float scale_eps,
+                          cudaStream_t stream) {
   FB_REQUIRE(epilogue == 0 || epilogue == 1, "gemm_skinny: epilogue %d", epilogue);
+  const RowScale scale{scale_ss, scale_count, scale_stride,
+                       scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, out, ldo, out_f32, T, N, K, epilogue, next, next_bytes,
-                       ksplit, plane_stride, warps, RopeWrite{}, stream);
+                       ksplit, plane_stride, warps, RopeWrite{}, scale, ResidualSink{}, stream);
 }
+
+// The projection in front of a norm (see the top of the file): resid [T, N]
+// float32 (row stride ldr) += x w^T; xg [T, N] bf16 (row stride ldxg) =
+// resid * gamma; ss_out[c * ss_stride + t] = CTA c's share of token t's sum of
+// squares of the new resid, c < ceil(N / 16); ss_stride must be 16 for the
+// products behind the norm.
+FB_API int fb_gemm_skinny_residual(const void* x, long long ldx, const void* w, long long ldw,
+                                   int T, int N, int K, float* resid, long long ldr,
+                                   const float* gamma, void* xg, long long ldxg, float* ss_out,
+                                   int ss_stride, const void* next, long long next_bytes,
+                                   int warps, cudaStream_t stream) {
+  ResidualSink sink{resid, ldr, gamma, (__nv_bfloat16*)xg, ldxg, ss_out, ss_stride};
+  return launch_skinny(x, ldx, w, ldw, resid, ldr, 1, T, N, K, 3, next, next_bytes, 1, 0, warps,
+                       RopeWrite{}, RowScale{}, sink, stream);
+}
+
+// Most shares of a row scale that the products behind a norm take
+// (fb_gemm_skinny_residual leaves one per 16 features).
+FB_API int fb_gemm_skinny_max_shares() { return FB_SKINNY_MAX_SHARES; }
 
 // The fused q/k/v projection of up to 16 tokens with the rotary epilogue:
 // w is [(A + 2 Kh) * D, K] (query, key, value heads); rotated queries go to
 // q_out [T, A * D], rotated keys and the values into the cache pages of each
 // token's position (page_table[seq, position / FB_PAGE], modulo ring_pages when
 // that is > 0). Tokens with seq_of_token < 0 are padding and write nothing;
-// with write_cache == 0 only the queries are computed.
+// with write_cache == 0 only the queries are computed. scale_*: as in
+// fb_gemm_skinny.
 FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long long ldw, int T,
                                int K, const int* positions, const int* seq_of_token,
                                const int* page_table, int max_pages, const float* inv_freq,
@@ -370,7 +559,8 @@ FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long
                                void* v_cache, long long page_stride, long long head_stride,
                                int ring_pages, int A, int Kh, int D, int write_cache,
                                const void* next, long long next_bytes, int warps,
-                               cudaStream_t stream) {
+                               const float* scale_ss, int scale_count, int scale_stride,
+                               int scale_dim, float scale_eps, cudaStream_t stream) {
   FB_REQUIRE(A > 0 && Kh > 0 && D > 0 && D % 16 == 0,
              "gemm_skinny_rope: head size %d is not a multiple of 16", D);
   FB_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 16 == 0,
@@ -385,6 +575,8 @@ FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long
   rw.k_cache = (__nv_bfloat16*)k_cache; rw.v_cache = (__nv_bfloat16*)v_cache;
   rw.page_stride = page_stride; rw.head_stride = head_stride; rw.ring_pages = ring_pages;
   rw.A = A; rw.Kh = Kh; rw.D = D; rw.write_cache = write_cache;
+  const RowScale scale{scale_ss, scale_count, scale_stride,
+                       scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, q_out, q_stride, 0, T, (A + 2 * Kh) * D, K, 2, next,
-                       next_bytes, 1, 0, warps, rw, stream);
+                       next_bytes, 1, 0, warps, rw, scale, ResidualSink{}, stream);
 }

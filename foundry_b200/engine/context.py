@@ -56,6 +56,10 @@ class StepContext:
     # The weight that the step streams after the part being run (a prefetch
     # hint, set by the model and the blocks as they go; None = unknown).
     reads_after_part: Optional[torch.Tensor] = None
+    # An `ops.ResidualSink` when the result of the part being run goes into a sum
+    # with the residual rows and a norm whose consumer takes it unscaled; the
+    # part's last projection may then do both (set like `reads_after_part`).
+    residual_sink: Optional[object] = None
 
     def page_table(self, group: KVGroup) -> torch.Tensor:
         """int32 [n_seqs, width]: the pages of each sequence in `group`."""

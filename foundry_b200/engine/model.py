@@ -132,8 +132,12 @@ class Model:
                         else None)
             ctx.reads_after_part = (first_weight_of(follower) if follower is not None
                                     else self.output_head if ctx.n_want else None)
+            # the last block's result meets the final norm on the wanted rows only
+            offer = getattr(follower, "input_sink", None)
+            ctx.residual_sink = offer(resid) if callable(offer) else None
             delta = block.forward(ctx, resid, delta, cache.view(entry.cache, entry.writes_cache))
         ctx.reads_after_part = None
+        ctx.residual_sink = None
         n = ctx.n_want
         logits = torch.empty((n, spec.vocab_size), dtype=torch.float32, device=self.device)
         if n == 0:

@@ -128,7 +128,6 @@ def build(force: bool = False, verbose: bool = True) -> str:
             raise KernelLibraryError(f"nvcc failed on {src}:\n{proc.stdout}\n{proc.stderr}")
         return obj
 
-    objects: List[str] = []
     try:
         with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
             objects = list(pool.map(compile_one, srcs))
@@ -142,9 +141,10 @@ def build(force: bool = False, verbose: bool = True) -> str:
             handle.write(digest)
     finally:
         done.set()
-        for obj in objects:
+        # also the objects of sources that compiled before another one failed
+        for src in srcs:
             try:
-                os.remove(obj)
+                os.remove(os.path.join(out_dir, os.path.basename(src)[:-3] + f".{os.getpid()}.o"))
             except OSError:
                 pass
     if verbose:

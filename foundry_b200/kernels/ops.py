@@ -46,11 +46,17 @@ _SIGNATURES = {
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_tc_pair_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
-                       c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p],
+                       c_int, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p, c_int, c_int, c_int,
+                       c_float, c_void_p],
+    "fb_gemm_skinny_residual": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_void_p,
+                                c_ll, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_ll,
+                                c_int, c_void_p],
+    "fb_apply_row_scale": [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                           c_ll, c_int, c_int, c_void_p],
     "fb_gemm_skinny_rope": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_int, c_void_p, c_ll, c_void_p, c_void_p,
                             c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int,
-                            c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
@@ -233,6 +239,76 @@ class Planes:
         return sum_planes(self.tensor, out)
 
 
+class ResidualSink:
+    """What a part's last projection may do instead of returning its result:
+    add it to the float32 residual rows `resid` and prepare the input of the
+    norm with weight `gamma` and `eps` that follows (see `gemm_bf16`)."""
+
+    def __init__(self, resid: torch.Tensor, gamma: torch.Tensor, eps: float):
+        self.resid, self.gamma, self.eps = resid, gamma, float(eps)
+
+
+class RowScaled:
+    """A norm's output that still lacks its row scale: `values` [T, H] bfloat16
+    hold resid * gamma, and token t's scale is
+    1 / sqrt(sum_c shares[c, t] / H + eps). The weight-streaming products
+    multiply their results by it (the product is linear in the scale);
+    `materialize` gives the plain tensor for anything else."""
+
+    def __init__(self, values: torch.Tensor, shares: torch.Tensor, eps: float):
+        self.values, self.shares, self.eps = values, shares, float(eps)
+
+    @property
+    def shape(self):
+        return self.values.shape
+
+    @property
+    def dtype(self):
+        return self.values.dtype
+
+    @property
+    def device(self):
+        return self.values.device
+
+    def scale_args(self):
+        """(shares, count, stride, dim, eps) as the kernels take them."""
+        return (self.shares.data_ptr(), self.shares.shape[0], self.shares.stride(0),
+                self.values.shape[1], self.eps)
+
+    def materialize(self) -> torch.Tensor:
+        T, H = self.values.shape
+        out = torch.empty_like(self.values)
+        _call("fb_apply_row_scale", _dev(self.values, "values", torch.bfloat16), H,
+              *self.scale_args(), out.data_ptr(), H, T, H, _stream())
+        return out
+
+
+class NormPending:
+    """The result of a projection that took a `ResidualSink`: the sum is already
+    in `sink.resid`; the norm that `sink` named turns this into a `RowScaled`."""
+
+    def __init__(self, sink: ResidualSink, values: torch.Tensor, shares: torch.Tensor):
+        self.sink, self.values, self.shares = sink, values, shares
+
+
+_NO_SCALE = (0, 0, 0, 0, 0.0)
+MAX_SCALE_SHARES = 384  # FB_SKINNY_MAX_SHARES in csrc/gemm_skinny.cu
+
+
+def _scale_of(x):
+    """(scale arguments, tensor) of a weight-streaming product's input."""
+    if not isinstance(x, RowScaled):
+        return _NO_SCALE, x
+    if x.shares.shape[0] > MAX_SCALE_SHARES:  # more than the kernel stages: apply it here
+        return _NO_SCALE, x.materialize()
+    return x.scale_args(), x.values
+
+
+def plain(x):
+    """`x` as a tensor: a `RowScaled` gets its scale applied."""
+    return x.materialize() if isinstance(x, RowScaled) else x
+
+
 # ------------------------------------------------------------------ embedding
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[t,:] = table[ids[t],:] as float32; `out` is [T, H] float32."""
@@ -249,8 +325,17 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> t
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
                 out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """resid += delta (a tensor, split-K `Planes`, or None), in place, float32;
-    out = rmsnorm(resid) * weight. With `out=None` only the sum is made."""
+    out = rmsnorm(resid) * weight. With `out=None` only the sum is made. A
+    `NormPending` delta (the sum was made by the projection) comes back as the
+    `RowScaled` input of the next projection, and no kernel runs."""
     T, H = resid.shape
+    if isinstance(delta, NormPending):
+        sink = delta.sink
+        if sink.resid.data_ptr() != resid.data_ptr() or sink.gamma.data_ptr() != weight.data_ptr() \
+                or sink.eps != float(eps):
+            raise KernelError("add_rmsnorm: the projection before this norm prepared its input "
+                              "for another residual or another norm")
+        return RowScaled(delta.values, delta.shares, eps)
     planes, plane_stride = 1, 0
     if isinstance(delta, Planes):
         planes, plane_stride = delta.count, T * H
@@ -455,6 +540,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     `ksplit` > 1: K is shared by that many CTAs per row group and `out` is
     float32 planes [ksplit, M, N]. `warps`: 4, 8 or 16 per CTA (0: the
     launcher's choice)."""
+    scale, x = _scale_of(x)
     M, K = x.shape
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -470,15 +556,40 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
           _dev(w, "w", contiguous=False), _rows(w, "w"), _dev(out, "out", contiguous=False),
           _rows(out, "out") if ksplit == 1 else N, 1 if out.dtype == torch.float32 else 0,
           M, N, K, epilogue,
-          *_prefetch_range(then_reads), ksplit, M * N if ksplit > 1 else 0, warps, _stream(),
-          tag=("m{} k{} n{}", M, K, N))
+          *_prefetch_range(then_reads), ksplit, M * N if ksplit > 1 else 0, warps, *scale,
+          _stream(), tag=("m{} k{} n{}", M, K, N))
     return out
+
+
+def gemm_skinny_residual(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink,
+                         then_reads: Optional[torch.Tensor] = None, warps: int = 0) -> NormPending:
+    """Up to 16 token rows in front of a norm: sink.resid += x w^T in the
+    product's epilogue, which also leaves resid * gamma in bfloat16 and each
+    CTA's share of the rows' sums of squares for the product behind the norm."""
+    M, K = x.shape
+    N = w.shape[0]
+    resid = sink.resid
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != K:
+        raise KernelError(f"gemm_skinny_residual: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)}")
+    if tuple(resid.shape) != (M, N) or tuple(sink.gamma.shape) != (N,):
+        raise KernelError(f"gemm_skinny_residual: resid {tuple(resid.shape)}, gamma "
+                          f"{tuple(sink.gamma.shape)} for a product of {(M, N)}")
+    values = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    shares = torch.empty(((N + 15) // 16, 16), dtype=torch.float32, device=x.device)
+    _call("fb_gemm_skinny_residual", _dev(x, "x", contiguous=False), _rows(x, "x"),
+          _dev(w, "w", contiguous=False), _rows(w, "w"), M, N, K,
+          _dev(resid, "resid", torch.float32, contiguous=False), _rows(resid, "resid"),
+          _dev(sink.gamma, "gamma", torch.float32), values.data_ptr(), N, shares.data_ptr(), 16,
+          *_prefetch_range(then_reads), warps, _stream(), tag=("m{} k{} n{}", M, K, N))
+    return NormPending(sink, values, shares)
 
 
 def qkv_rope_fusable(x: torch.Tensor, w: torch.Tensor, rotary_dim: int, head_dim: int,
                      k_cache: Optional[torch.Tensor]) -> bool:
     """Whether `gemm_skinny_rope` takes this projection: bfloat16, few token
     rows, and a rotation whose pairs fall into the kernel's 8-row halves."""
+    if isinstance(x, RowScaled):
+        x = x.values
     return (FUSE_QKV_ROPE and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
             and 0 < x.shape[0] <= SKINNY_ROWS and _tc_usable(x, w, x)
             and rotary_dim % 16 == 0 and head_dim % 16 == 0
@@ -495,6 +606,7 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
     product's epilogue: returns the rotated queries [T, heads * head_dim]; the
     rotated keys and the values go into the cache pages (`rope_kv_write` has
     the meaning of the arguments). `w` is [(heads + 2 kv_heads) * head_dim, K]."""
+    scale, x = _scale_of(x)
     T, K = x.shape
     if w.shape != ((num_heads + 2 * num_kv_heads) * head_dim, K):
         raise KernelError(f"gemm_skinny_rope: w is {tuple(w.shape)} for {num_heads}+2x{num_kv_heads} "
@@ -518,12 +630,14 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
           _dev(inv_freq, "inv_freq", torch.float32) if rotary_dim else 0, rotary_dim,
           q_out.data_ptr(), q_out.stride(0), kp, vp, page_stride, head_stride, ring_pages,
           num_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
-          *_prefetch_range(then_reads), skinny_plan(w.shape[0], K, False)[1], _stream(),
+          *_prefetch_range(then_reads), skinny_plan(w.shape[0], K, False)[1], *scale, _stream(),
           tag=("m{} k{} n{}", T, K, w.shape[0]))
     return q_out
 
 
 FUSE_QKV_ROPE = _os.environ.get("FOUNDRY_B200_FUSE_QKV_ROPE", "1") != "0"
+# the projections around a norm take the norm over (see `ResidualSink`, `RowScaled`)
+NORM_FUSION = _os.environ.get("FOUNDRY_B200_NORM_FUSION", "1") != "0"
 
 
 def skinny_plan(N: int, K: int, planes_ok: bool):
@@ -653,7 +767,8 @@ def prompt_plan(M: int, N: int):
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
               out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
-              then_reads: Optional[torch.Tensor] = None):
+              then_reads: Optional[torch.Tensor] = None,
+              residual: Optional[ResidualSink] = None):
     """out[M,N] = x[M,K] @ w[N,K]^T in bfloat16 with 32-bit accumulation.
 
     Up to 16 rows: the weight-streaming kernel. More than 128 rows: token rows
@@ -665,6 +780,11 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     sums them as it reads; otherwise one more kernel sums them in a fixed order.
     Shapes TMA cannot address (K or a row stride not a multiple of 8 elements)
     take the CUDA-core kernel.
+    `x` may be a `RowScaled` (the weight-streaming kernel applies the scale, the
+    others get the plain tensor). `residual`: the caller would add the result to
+    these residual rows and normalise them next; when the weight-streaming kernel
+    runs unsplit it does both in its epilogue and a `NormPending` comes back,
+    otherwise the result comes back as usual.
     """
     M, K = x.shape
     N = w.shape[0]
@@ -672,13 +792,19 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         out_dtype = out_dtype or x.dtype
     if M == 0:
         return out if out is not None else torch.empty((0, N), dtype=out_dtype, device=x.device)
-    probe = out if out is not None else x
-    if not _tc_usable(x, w, probe):
+    values = x.values if isinstance(x, RowScaled) else x
+    usable = _tc_usable(values, w, out if out is not None else values)
+    if not (usable and M <= SKINNY_ROWS):
+        x = plain(x)
+    if not usable:
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_simt(x, w, out)
     if M <= SKINNY_ROWS:
         ksplit, warps = skinny_plan(N, K, allow_planes and out is None)
+        if (residual is not None and NORM_FUSION and ksplit == 1 and out is None
+                and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
+            return gemm_skinny_residual(x, w, residual, then_reads=then_reads, warps=warps)
         if ksplit > 1:
             planes = torch.empty((ksplit, M, N), dtype=torch.float32, device=x.device)
             gemm_skinny(x, w, planes, then_reads=then_reads, ksplit=ksplit, warps=warps)
@@ -728,7 +854,10 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
         raise KernelError("gemm_bf16_silu_mul: out must be [M, I] bfloat16 with contiguous rows")
     if M == 0:
         return out
-    if not _tc_usable(x, w_pairs, out):
+    usable = _tc_usable(x.values if isinstance(x, RowScaled) else x, w_pairs, out)
+    if not (usable and M <= SKINNY_ROWS):
+        x = plain(x)
+    if not usable:
         tmp = torch.empty((M, two_i), dtype=torch.bfloat16, device=x.device)
         gemm_simt(x, w_pairs, tmp)
         return silu_mul(tmp, out, interleaved=True)

@@ -30,6 +30,7 @@ from .linear import Linear
 @register_mixer("gqa_attention")
 class GQAAttention(Part):
     replay_safe = True  # forward reads nothing of the step on the host
+    accepts_row_scaled = True  # the q/k/v product applies a deferred norm's row scale
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PartSpec], window: Optional[int] = None, *,
@@ -70,7 +71,7 @@ class GQAAttention(Part):
         return self.qkv.weight
 
     # ------------------------------------------------------------------- run
-    def forward(self, ctx, x: torch.Tensor, cache: KVView):
+    def forward(self, ctx, x, cache: KVView):
         table = ctx.page_table(cache.group)
         if ops.qkv_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k):
             # a handful of tokens: projection, rotation and cache write in one kernel
@@ -79,6 +80,7 @@ class GQAAttention(Part):
                                      self.num_heads, self.num_kv_heads, self.head_dim,
                                      ring_pages=cache.group.ring_pages, write_cache=cache.writes)
         else:
+            x = ops.plain(x)
             qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
             q = ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
                                   self.rotary_dim, cache.k, cache.v, self.num_heads,
@@ -90,4 +92,5 @@ class GQAAttention(Part):
                       self.head_dim, self.scale, window=cache.group.window,
                       ring_pages=cache.group.ring_pages, then_reads=self.o.weight)
         return self.o.forward(attn, allow_planes=True,
-                        then_reads=getattr(ctx, "reads_after_part", None))
+                              then_reads=getattr(ctx, "reads_after_part", None),
+                              residual=getattr(ctx, "residual_sink", None))

@@ -36,6 +36,15 @@ Optional, any part
     model for the block); a part may hand it to its last product as
     `then_reads`, which single-token steps turn into an L2 prefetch. A part
     that ignores both is still correct.
+    The norm between two parts as work of the projections around it (single-
+    token steps): a norm may offer `sink(resid) -> ops.ResidualSink`; a part
+    that sets `accepts_row_scaled = True` takes `x` as an `ops.RowScaled`
+    (a norm's output that still lacks its row scale; `ops.plain(x)` gives the
+    tensor); where both hold, the block puts the sink into
+    `ctx.residual_sink` for the part in front, which may hand it to its last
+    product (`Linear.forward(residual=...)`) and return what that returns. A
+    part that ignores `ctx.residual_sink` is still correct: the norm then runs
+    as a kernel of its own.
 
 A new part is a class with these methods plus one `register_*` call; the
 engine builds it from `PartSpec(kind, params)` as `cls(**params, dtype=...,

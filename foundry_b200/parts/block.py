@@ -7,7 +7,11 @@
 
 The residual stream is float32 and each sum is made in the kernel that also
 normalises for the next part, so a block receives the previous block's output
-still un-added (`delta`) and returns its own the same way.
+still un-added (`delta`) and returns its own the same way. In single-token
+steps that kernel is the projection in front of the norm: the block offers the
+norm's `sink` to the part in front through `ctx.residual_sink`, and a part
+that used it returns an `ops.NormPending`, which the norm turns into the
+`ops.RowScaled` input of the part behind it.
 """
 from __future__ import annotations
 
@@ -57,11 +61,28 @@ class PreNormResidualBlock(Part):
     def first_weight(self):
         return first_weight_of(self.mixer)
 
-    def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], cache):
+    def input_sink(self, resid: torch.Tensor):
+        """The sink of this block's first norm, if its mixer takes the norm's
+        output without its row scale; for whatever runs in front of the block."""
+        return _sink_for(self.mixer_norm, self.mixer, resid)
+
+    def forward(self, ctx, resid: torch.Tensor, delta, cache):
         after_block = getattr(ctx, "reads_after_part", None)  # what follows this block
+        sink_after_block = getattr(ctx, "residual_sink", None)
         normed = self.mixer_norm.add_norm(resid, delta)
         ctx.reads_after_part = first_weight_of(self.feed_forward)
+        ctx.residual_sink = _sink_for(self.feed_forward_norm, self.feed_forward, resid)
         mixed = self.mixer.forward(ctx, normed, cache)
         normed = self.feed_forward_norm.add_norm(resid, mixed)
         ctx.reads_after_part = after_block
+        ctx.residual_sink = sink_after_block
         return self.feed_forward.forward(ctx, normed)
+
+
+def _sink_for(norm, consumer, resid: torch.Tensor):
+    """`norm.sink(resid)` where the norm offers one and `consumer` takes the
+    norm's output as an `ops.RowScaled`; else None."""
+    offer = getattr(norm, "sink", None)
+    if not callable(offer) or not getattr(consumer, "accepts_row_scaled", False):
+        return None
+    return offer(resid)

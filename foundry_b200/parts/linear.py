@@ -16,14 +16,17 @@ from ..weights.loader import ExpectedTensor
 from .base import Fetch, Part
 
 
-def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+def matmul_nt(x, w: torch.Tensor, out: Optional[torch.Tensor] = None,
               out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
-              then_reads: Optional[torch.Tensor] = None):
+              then_reads: Optional[torch.Tensor] = None,
+              residual: Optional[ops.ResidualSink] = None):
     """out[M,N] = x[M,K] @ w[N,K]^T, accumulated in 32-bit, by the kernel that
     fits the element type and the shape. With `allow_planes` a split-K product
     may come back as `ops.Planes` (float32 partial results) for a consumer that
     sums them while it reads. `then_reads` names the weights the step streams
-    next, a hint that the single-token kernel turns into an L2 prefetch."""
+    next, a hint that the single-token kernel turns into an L2 prefetch. `x` may
+    be an `ops.RowScaled`; with `residual` the product may add its result to the
+    residual rows itself and return an `ops.NormPending` (see `ops.gemm_bf16`)."""
     M, N = x.shape[0], w.shape[0]
     if x.dtype != w.dtype:
         raise ops.KernelError(
@@ -33,7 +36,7 @@ def matmul_nt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
         return ops.gemm_simt(x, w, out)
-    return ops.gemm_bf16(x, w, out, out_dtype, allow_planes, then_reads)
+    return ops.gemm_bf16(x, w, out, out_dtype, allow_planes, then_reads, residual)
 
 
 class Linear(Part):
@@ -58,7 +61,8 @@ class Linear(Part):
             raise ops.KernelError(f"{prefix}: fused projections are stored in different dtypes")
         self.weight = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, 0).contiguous()
 
-    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+    def forward(self, x, out: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None, allow_planes: bool = False,
-                then_reads: Optional[torch.Tensor] = None):
-        return matmul_nt(x, self.weight, out, out_dtype, allow_planes, then_reads)
+                then_reads: Optional[torch.Tensor] = None,
+                residual: Optional[ops.ResidualSink] = None):
+        return matmul_nt(x, self.weight, out, out_dtype, allow_planes, then_reads, residual)

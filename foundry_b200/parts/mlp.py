@@ -17,6 +17,7 @@ from .linear import Linear, matmul_nt
 @register_feed_forward("swiglu")
 class SwiGLU(Part):
     replay_safe = True  # forward reads nothing of the step on the host
+    accepts_row_scaled = True  # the gate/up product applies a deferred norm's row scale
 
     def __init__(self, hidden_size: int, intermediate_size: int, *, dtype: torch.dtype,
                  device: torch.device):
@@ -44,12 +45,13 @@ class SwiGLU(Part):
     def first_weight(self):
         return self.gate_up
 
-    def forward(self, ctx, x: torch.Tensor):
+    def forward(self, ctx, x):
         hidden = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16:
             ops.gemm_bf16_silu_mul(x, self.gate_up, hidden,  # activation in the epilogue
                                    then_reads=self.down.weight)
         else:
-            ops.silu_mul(matmul_nt(x, self.gate_up), hidden, interleaved=True)
+            ops.silu_mul(matmul_nt(ops.plain(x), self.gate_up), hidden, interleaved=True)
         return self.down.forward(hidden, allow_planes=True,
-                        then_reads=getattr(ctx, "reads_after_part", None))
+                                 then_reads=getattr(ctx, "reads_after_part", None),
+                                 residual=getattr(ctx, "residual_sink", None))

@@ -32,9 +32,19 @@ class RMSNorm(Part):
     def load(self, prefix: str, fetch: Fetch) -> None:
         self.weight = fetch(f"{prefix}.weight").to(torch.float32).contiguous()
 
-    def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def sink(self, resid: torch.Tensor) -> Optional[ops.ResidualSink]:
+        """What the projection in front of this norm needs to make the sum and
+        prepare the norm itself (bfloat16 steps only)."""
+        if self.dtype != torch.bfloat16 or self.weight is None:
+            return None
+        return ops.ResidualSink(resid, self.weight, self.eps)
+
+    def add_norm(self, resid: torch.Tensor, delta, out: Optional[torch.Tensor] = None):
         """resid += delta (a tensor, split-K `ops.Planes`, or None); returns
-        norm(resid) in the activation dtype."""
+        norm(resid) in the activation dtype. A delta that a projection made
+        with this norm's `sink` comes back as an `ops.RowScaled`."""
+        if isinstance(delta, ops.NormPending):
+            return ops.add_rmsnorm(resid, delta, self.weight, self.eps, None)
         if out is None:
             out = torch.empty(resid.shape, dtype=self.dtype, device=resid.device)
         return ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)

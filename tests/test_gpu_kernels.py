@@ -494,6 +494,73 @@ def test_gemm_skinny_rope(ops, A, Kh, D, rot, T):
     assert float(k_cache.float().abs().max()) == 0.0 and float(v_cache.float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("T,H,K", [(1, 96, 72), (8, 200, 264), (13, 3072, 520), (16, 104, 64)])
+def test_gemm_skinny_takes_the_norm_over(ops, T, H, K):
+    """The projection in front of a norm adds into the residual rows and leaves
+    resid * gamma and the shares of the sums of squares; the projections behind
+    the norm (plain, SiLU-mul, rotary) apply 1/sqrt(mean + eps) to their sums.
+    Against the plain formulas, and against the norm as a kernel of its own."""
+    eps = 3e-5
+    x, w = rnd(T, K, dtype=torch.bfloat16), rnd(H, K, dtype=torch.bfloat16, scale=0.2, seed=1)
+    resid0 = rnd(T, H, seed=2) * 3.0
+    resid0[0] *= 40.0  # rows of very different scale
+    gamma = (1.0 + 0.3 * rnd(H, seed=3)).contiguous()
+    resid = resid0.clone()
+    pending = ops.gemm_skinny_residual(x, w, ops.ResidualSink(resid, gamma, eps),
+                                       then_reads=rnd(8, 64, dtype=torch.bfloat16))
+    want_resid = resid0.double() + x.double() @ w.double().T
+    close(resid, want_resid, 1e-4, 1e-5)
+    close(pending.values, want_resid * gamma.double(), 1e-6, 2.0 ** -8)
+    assert pending.shares.shape == ((H + 15) // 16, 16)
+    close(pending.shares[:, :T].sum(0), (want_resid ** 2).sum(1), 1e-3, 1e-5)
+    scaled = ops.add_rmsnorm(resid, pending, gamma, eps, None)
+    assert isinstance(scaled, ops.RowScaled)
+    rstd = 1.0 / torch.sqrt((resid.double() ** 2).mean(1, keepdim=True) + eps)
+    # the plain tensor
+    close(scaled.materialize(), pending.values.double() * rstd, 1e-6, 2.0 ** -8)
+    # behind the norm: plain product (whole and in K shares), SiLU-mul, rotary
+    N = 80
+    w2 = rnd(N, H, dtype=torch.bfloat16, scale=0.1, seed=5)
+    want = (pending.values.double() @ w2.double().T) * rstd
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(scaled, w2, out)
+    close(out, want, 1e-3, 8e-3)
+    planes = torch.empty(2, T, N, dtype=torch.float32, device=DEV)
+    ops.gemm_skinny(scaled, w2, planes, ksplit=2)
+    close(planes.sum(0), want, 1e-4, 1e-4)
+    act = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(scaled, w2, act, epilogue=1)
+    close(act, torch.nn.functional.silu(want[:, 0::2]) * want[:, 1::2], 1e-3, 1e-2)
+    A, Kh, D = 3, 1, 16
+    inv_freq = torch.from_numpy((10000.0 ** (-np.arange(0, D, 2, dtype=np.float32) / D))).to(DEV)
+    positions = torch.arange(5, 5 + T, dtype=torch.int32, device=DEV)
+    seqs = torch.zeros(T, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[1]], dtype=torch.int32, device=DEV)
+    k_cache = torch.zeros(2, Kh, 64, D, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    q = ops.gemm_skinny_rope(scaled, w2, positions, seqs, table, inv_freq, D, k_cache, v_cache,
+                             A, Kh, D)
+    for t in range(T):
+        row = want[t].cpu().view(A + 2 * Kh, D)
+        close(q[t].view(A, D), plain_rope(row[:A], 5 + t, inv_freq.cpu().numpy(), D), 2e-3, 8e-3)
+        close(v_cache[1, :, 5 + t], row[A + Kh:], 2e-3, 8e-3)
+    # the same through the general entry: it hands the sink to the skinny kernel
+    resid2 = resid0.clone()
+    pending2 = ops.gemm_bf16(x, w, residual=ops.ResidualSink(resid2, gamma, eps))
+    assert isinstance(pending2, ops.NormPending) and torch.equal(resid2, resid)
+    # ... and agrees with the norm as its own kernel to the rounding of its output
+    resid3, delta = resid0.clone(), torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(x, w, delta)
+    normed = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.add_rmsnorm(resid3, delta, gamma, eps, normed)
+    apart = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_skinny(normed, w2, apart)
+    close(out, apart.double(), 2e-2 * float(want.abs().max()), 2e-2)
+    # a sink for other rows or another norm is refused
+    with pytest.raises(ops.KernelError, match="another"):
+        ops.add_rmsnorm(resid3, pending, gamma, eps, None)
+
+
 def test_gemm_skinny_rope_ring_pages(ops):
     """A windowed group's pages are a ring: position p lands in page slot (p / 64) % ring."""
     A, Kh, D, K, ring = 2, 1, 32, 64, 3

@@ -12,6 +12,7 @@ call's leftovers in the shared array, and checks both results against
 alone in a fresh process as well as after every other test.
 """
 import ctypes
+import gc
 import math
 
 import pytest
@@ -66,6 +67,7 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
         want = torch.zeros_like(q)
         ops.attention_decode(q, want, cu, kv, table, k, v, A, Kh, D, 1.0 / math.sqrt(D), splits)
         got = torch.full_like(q, 7.0)
+        gc.collect()  # garbage of earlier tests must not be freed inside the window
         before = torch.cuda.memory_allocated()
         rc = _call_static(lib, q, got, cu, kv, table, k, v, A, Kh, D, splits)
         assert rc == 0, lib.fb_last_error().decode()
