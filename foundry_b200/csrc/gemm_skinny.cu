@@ -119,17 +119,21 @@ constexpr int MODE_SINK = 2;   // add into the residual rows in front of a norm
 
 // NT: token tiles of 8 (1 or 2). WARPS: warps per CTA, each with a K range.
 // UNROLL: chunks whose loads are in flight together.
-// Registers are capped at 128 (four chunks in flight; four CTAs of 4 warps on
-// an SM), the fastest on the 3B decode step: at 130 the gate/up product of 8
-// tokens ran three CTAs to an SM and took 3 us longer; capped to 96 (five CTAs)
-// its 1,024 CTAs run as 740 and a thin 284, which was slower too.
+// For up to 8 tokens registers are capped at 128 (four chunks in flight; four
+// CTAs of 4 warps on an SM), the fastest on the 3B decode step: at 130 the
+// gate/up product of 8 tokens ran three CTAs to an SM and took 3 us longer;
+// capped to 96 (five CTAs) its 1,024 CTAs run as 740 and a thin 284, which was
+// slower too. 16 tokens want 134 registers; capped they spilled and the step at
+// batch 16 lost 6 %, so they stay as the compiler sizes them.
+constexpr int min_blocks(int nt, int warps) { return nt == 1 ? 16 / warps : 1; }
 template <int NT, int WARPS, int UNROLL, int MODE>
-__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS)
+__global__ void __launch_bounds__(WARPS * 32, min_blocks(NT, WARPS))
 gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
                    const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
                    long long ldo, int out_f32, int T, int N, int K, int epilogue,
                    const void* next, long long next_bytes, long long plane_stride,
-                   const typename RopeArg<MODE == MODE_ROPE>::type rw, const RowScale scale,
+                   int late_trigger, const typename RopeArg<MODE == MODE_ROPE>::type rw,
+                   const RowScale scale,
                    const typename SinkArg<MODE == MODE_SINK>::type sink) {
   constexpr bool ROPE = MODE == MODE_ROPE, SINK = MODE == MODE_SINK;
   __shared__ float red[WARPS][16][8 * NT + 1];
@@ -313,8 +317,9 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   fb_prefetch_l2_slice(next, next_bytes);
   // ... and its blocks may be placed as this kernel's leave: the weights' last bytes
   // are on their way, what is left is the epilogue. (At the start of the kernel the
-  // same instruction lost: the next kernel's blocks then take the room of this one's.)
-  fb_pdl_launch();
+  // same instruction lost: the next kernel's blocks then take the room of this one's.
+  // In front of an attention over a long context it lost too, so the caller decides.)
+  if (late_trigger) fb_pdl_launch();
   // acc[j][0..1]: row g, tokens j*8 + 2t, 2t+1; acc[j][2..3]: row g + 8
 #pragma unroll
   for (int j = 0; j < NT; ++j) {
@@ -430,8 +435,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
 int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, void* out,
                   long long ldo, int out_f32, int T, int N, int K, int epilogue, const void* next,
                   long long next_bytes, int ksplit, long long plane_stride, int warps,
-                  const RopeWrite& rw, const RowScale& scale, const ResidualSink& sink,
-                  cudaStream_t stream) {
+                  int late_trigger, const RopeWrite& rw, const RowScale& scale,
+                  const ResidualSink& sink, cudaStream_t stream) {
   FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
              "gemm_skinny: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
   FB_REQUIRE(T > 0 && T <= 16 && N > 0 && K > 0, "gemm_skinny: bad sizes T=%d N=%d K=%d", T, N, K);
@@ -472,8 +477,8 @@ int launch_skinny(const void* x, long long ldx, const void* w, long long ldw, vo
   do {                                                                                         \
   fb_launch(gemm_skinny_kernel<NT, W, U, MODE>, dim3(blocks, ksplit), dim3(W * 32),            \
             shares_bytes, stream, (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, ldw,   \
-            out, ldo, out_f32, T, N, K, epilogue, next, next_bytes, plane_stride, ROPE_ARG,     \
-            scale, SINK_ARG); } while (0)
+            out, ldo, out_f32, T, N, K, epilogue, next, next_bytes, plane_stride,               \
+            late_trigger, ROPE_ARG, scale, SINK_ARG); } while (0)
 #define FB_SKINNY(NT, W, U)                                                      \
   do {                                                                           \
     if (epilogue == 2) FB_SKINNY_R(NT, W, U, MODE_ROPE, rw, NoSink{});            \
@@ -523,7 +528,7 @@ FB_API int fb_gemm_skinny(const void* x, long long ldx, const void* w, long long
   const RowScale scale{scale_ss, scale_count, scale_stride,
                        scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, out, ldo, out_f32, T, N, K, epilogue, next, next_bytes,
-                       ksplit, plane_stride, warps, RopeWrite{}, scale, ResidualSink{}, stream);
+                       ksplit, plane_stride, warps, 1, RopeWrite{}, scale, ResidualSink{}, stream);
 }
 
 // The projection in front of a norm (see the top of the file): resid [T, N]
@@ -538,7 +543,7 @@ FB_API int fb_gemm_skinny_residual(const void* x, long long ldx, const void* w, 
                                    int warps, cudaStream_t stream) {
   ResidualSink sink{resid, ldr, gamma, (__nv_bfloat16*)xg, ldxg, ss_out, ss_stride};
   return launch_skinny(x, ldx, w, ldw, resid, ldr, 1, T, N, K, 3, next, next_bytes, 1, 0, warps,
-                       RopeWrite{}, RowScale{}, sink, stream);
+                       1, RopeWrite{}, RowScale{}, sink, stream);
 }
 
 // Most shares of a row scale that the products behind a norm take
@@ -550,8 +555,9 @@ FB_API int fb_gemm_skinny_max_shares() { return FB_SKINNY_MAX_SHARES; }
 // q_out [T, A * D], rotated keys and the values into the cache pages of each
 // token's position (page_table[seq, position / FB_PAGE], modulo ring_pages when
 // that is > 0). Tokens with seq_of_token < 0 are padding and write nothing;
-// with write_cache == 0 only the queries are computed. scale_*: as in
-// fb_gemm_skinny.
+// with write_cache == 0 only the queries are computed. late_trigger: whether the
+// kernel behind this one (the attention) may have its blocks placed as this
+// one's main loops end. scale_*: as in fb_gemm_skinny.
 FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long long ldw, int T,
                                int K, const int* positions, const int* seq_of_token,
                                const int* page_table, int max_pages, const float* inv_freq,
@@ -559,8 +565,9 @@ FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long
                                void* v_cache, long long page_stride, long long head_stride,
                                int ring_pages, int A, int Kh, int D, int write_cache,
                                const void* next, long long next_bytes, int warps,
-                               const float* scale_ss, int scale_count, int scale_stride,
-                               int scale_dim, float scale_eps, cudaStream_t stream) {
+                               int late_trigger, const float* scale_ss, int scale_count,
+                               int scale_stride, int scale_dim, float scale_eps,
+                               cudaStream_t stream) {
   FB_REQUIRE(A > 0 && Kh > 0 && D > 0 && D % 16 == 0,
              "gemm_skinny_rope: head size %d is not a multiple of 16", D);
   FB_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 16 == 0,
@@ -578,5 +585,5 @@ FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long
   const RowScale scale{scale_ss, scale_count, scale_stride,
                        scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, q_out, q_stride, 0, T, (A + 2 * Kh) * D, K, 2, next,
-                       next_bytes, 1, 0, warps, rw, scale, ResidualSink{}, stream);
+                       next_bytes, 1, 0, warps, late_trigger, rw, scale, ResidualSink{}, stream);
 }

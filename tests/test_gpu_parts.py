@@ -442,3 +442,42 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
         unregister_architecture("Toy2ForCausalLM")
         POSITION_ENCODINGS.unregister("toy_half_rotary")
         FEED_FORWARDS.unregister("toy_routed_relu2")
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_single_token_steps_fold_the_norms_into_the_projections(tmp_path, monkeypatch, name):
+    """In single-token steps the norm between two parts is work of the
+    projections around it: only the first layer's first norm and the final norm
+    still run as kernels. The logits agree with the plain model either way, and
+    the two ways agree with each other."""
+    import foundry_b200 as fb
+    from foundry_b200.engine import SequenceStep
+    from foundry_b200.kernels import ops
+    folder = tiny.write_folder(str(tmp_path / name), name)
+    cfg, w = plain.read_model(folder)
+    reqs = [tiny.random_tokens(500 + i, n, cfg["vocab_size"]) for i, n in enumerate((33, 9, 20))]
+    want = [plain.forward(cfg, w, r).numpy() for r in reqs]
+    logits = {}
+    for fused in (True, False):
+        monkeypatch.setattr(ops, "NORM_FUSION", fused)
+        engine = fb.Engine.from_folder(folder, dtype="bfloat16", max_tokens=512, max_slots=4)
+        engine.use_graphs = False
+        slots = [engine.open_sequence() for _ in reqs]
+        engine.step([SequenceStep(s, r[:-4], []) for s, r in zip(slots, reqs)])
+        rows = [[] for _ in reqs]
+        for k in range(4, 0, -1):
+            ops.PROFILER.start("steps")
+            out = engine.step([SequenceStep(s, [r[-k]], [0]) for s, r in zip(slots, reqs)])
+            counts = ops.PROFILER.take()["kernels"]
+            ops.PROFILER.start(None)
+            norms = sum(v["dispatch_count"] for key, v in counts.items() if key.startswith("add_rmsnorm"))
+            layers = cfg["num_hidden_layers"]
+            assert norms == (2 if fused else 2 * layers + 1), counts
+            for i in range(len(reqs)):
+                rows[i].append(out[i:i + 1].cpu().numpy())
+        for i, r in enumerate(reqs):
+            got = np.concatenate(rows[i])
+            tiny.assert_logits_close(got, want[i][-4:], "bfloat16", f"{name} fused={fused} request {i}")
+        logits[fused] = np.concatenate([np.concatenate(x) for x in rows])
+    scale = float(np.abs(logits[False]).max())
+    assert float(np.abs(logits[True] - logits[False]).max()) <= 0.03 * scale
