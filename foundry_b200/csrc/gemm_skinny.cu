@@ -119,15 +119,15 @@ constexpr int MODE_SINK = 2;   // add into the residual rows in front of a norm
 
 // NT: token tiles of 8 (1 or 2). WARPS: warps per CTA, each with a K range.
 // UNROLL: chunks whose loads are in flight together.
-// For up to 8 tokens registers are capped at 128 (four chunks in flight; four
-// CTAs of 4 warps on an SM), the fastest on the 3B decode step: at 130 the
-// gate/up product of 8 tokens ran three CTAs to an SM and took 3 us longer;
-// capped to 96 (five CTAs) its 1,024 CTAs run as 740 and a thin 284, which was
-// slower too. 16 tokens want 134 registers; capped they spilled and the step at
-// batch 16 lost 6 %, so they stay as the compiler sizes them.
-constexpr int min_blocks(int nt, int warps) { return nt == 1 ? 16 / warps : 1; }
+// Registers are capped at 128 (four chunks of weights in flight; four CTAs of 4
+// warps on an SM), the fastest on the 3B decode step: at 130 the gate/up product
+// of 8 tokens ran three CTAs to an SM and took 3 us longer; capped to 96 (five
+// CTAs) its 1,024 CTAs run as 740 and a thin 284, which was slower too. With 16
+// tokens the cap holds only because x is fetched one chunk ahead instead of all
+// chunks at once (batch 16: 3.05 -> 2.85 ms a step).
+constexpr int min_blocks(int warps) { return 16 / warps; }
 template <int NT, int WARPS, int UNROLL, int MODE>
-__global__ void __launch_bounds__(WARPS * 32, min_blocks(NT, WARPS))
+__global__ void __launch_bounds__(WARPS * 32, min_blocks(WARPS))
 gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
                    const __nv_bfloat16* __restrict__ w, long long ldw, void* __restrict__ out,
                    long long ldo, int out_f32, int T, int N, int K, int epilogue,
@@ -264,7 +264,6 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   };
   for (; c + UNROLL <= full_end; c += UNROLL) {
     uint4 a[UNROLL][4];
-    uint4 b[UNROLL][NT][2];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const size_t off = (size_t)(c + u) * CHUNK;
@@ -278,18 +277,35 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
       after_wait();
       waited = true;
     }
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
+    auto load_x = [&](uint4 (&b)[NT][2], int u) {
       const size_t off = (size_t)(c + u) * CHUNK;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
-        b[u][j][0] = ld_cached(xr[j] + off);
-        b[u][j][1] = ld_cached(xr[j] + off + 32);
+        b[j][0] = ld_cached(xr[j] + off);
+        b[j][1] = ld_cached(xr[j] + off + 32);
+      }
+    };
+    if constexpr (NT == 1) {
+      uint4 b[UNROLL][NT][2];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) load_x(b[u], u);
+      if (first) finish_scale();
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) multiply(a[u], b[u]);
+    } else {
+      // 16 tokens: x comes from L1 or L2, the weights from DRAM. One chunk's x at a
+      // time, the next chunk's on its way, leaves the registers to the weights in
+      // flight (with all chunks' x held at once the kernel wanted 134 registers
+      // and ran three CTAs to an SM, or spilled under the cap).
+      uint4 b[2][NT][2];
+      load_x(b[0], 0);
+      if (first) finish_scale();
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        if (u + 1 < UNROLL) load_x(b[(u + 1) & 1], u + 1);
+        multiply(a[u], b[u & 1]);
       }
     }
-    if (first) finish_scale();
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) multiply(a[u], b[u]);
   }
   if (!waited) {
     after_wait();
