@@ -24,9 +24,10 @@ extern "C" {
 #define FB_ATTENTION_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
 
 // Decode attention (one new token per sequence) over the paged bfloat16 cache,
-// with the same arguments and the same result as `fb_attention_decode`, except
-// that no workspace is passed: partial results of the `splits` cache ranges go
-// to the library's own scratch array.
+// with the arguments and the result of `fb_attention_decode`, except that no
+// workspace is passed (nor a page-buffer count or a cluster size: three buffers,
+// no clusters): the partial results of the `splits` cache ranges go to the
+// library's own scratch array, where the last CTA of a pair merges them.
 //
 //   needs  n_seqs * Kh * splits * (16 * D + 32) + n_seqs * Kh (rounded up to 64)
 //          <= FB_ATTENTION_STATIC_SCRATCH_FLOATS, else it returns non-zero with a

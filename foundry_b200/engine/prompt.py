@@ -2,9 +2,10 @@
 
 A prompt step of the 3B model is some 230 kernel launches; from Python that is
 about 4 ms of host time, more than the GPU needs for a prompt of up to about a
-hundred tokens (measured: 20 tokens 4.0 -> 2.3 ms, 128 tokens 4.0 -> 3.2 ms;
-from 300 tokens on the GPU is the slower side and padding only costs). So steps
-of up to `PROMPT_GRAPH_TOKENS` tokens run like the single-token steps (decode.py): padded up to a bucket (tokens, sequences,
+hundred tokens (measured: 20 tokens 4.0 -> 2.3 ms, 128 tokens 4.0 -> 2.65 ms;
+from 300 tokens on the GPU is the slower side: replayed, 300 to 1,000 tokens
+gained 1 to 4 %). So steps of up to `PROMPT_GRAPH_TOKENS` tokens run like the
+single-token steps (decode.py): padded up to a bucket (tokens, sequences,
 page-table width, wanted rows), described by fixed device buffers that one copy
 from pinned memory refreshes, captured once per bucket and replayed.
 
