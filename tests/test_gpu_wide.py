@@ -94,18 +94,21 @@ def test_benchmark_widths_on_an_unequal_batch(wide, dtype):
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("streams", [3, 12])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_replayed_steps_equal_plainly_launched_steps(wide, dtype):
+def test_replayed_steps_equal_plainly_launched_steps(wide, dtype, streams):
     """Single-token steps replayed as a graph run their kernels back to back, so
     that dependent launches really overlap; launched one by one they do not.
-    Both must give the same logits, bit for bit, step after step."""
+    Both must give the same logits, bit for bit, step after step. Three streams
+    take the products' 8-token form, twelve the 16-token form."""
     import foundry_b200 as fb
     from foundry_b200.engine import SequenceStep
     folder, seqs, _, _ = wide
-    seqs = [seqs[1], seqs[2], seqs[2][100:]]  # three streams of at least 48 tokens
+    # streams of at least 48 tokens
+    seqs = [seqs[1], seqs[2], seqs[2][100:]] + [seqs[2][150 * i:] for i in range(1, streams - 2)]
     results = []
     for graphs in (True, False):
-        engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=4096, max_slots=4)
+        engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=4096, max_slots=streams + 1)
         engine.use_graphs = graphs
         slots = [engine.open_sequence() for _ in seqs]
         engine.step([SequenceStep(s, q[:40], []) for s, q in zip(slots, seqs)])
