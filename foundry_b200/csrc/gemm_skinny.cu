@@ -213,9 +213,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
     fb_pdl_wait();
     if (scale.ss != nullptr) {
       // Every CTA of the grid wants the same few lines: through L1 (.ca), so that
-      // the CTAs of an SM ask L2 once, and only the T floats of a row that count
-      // (with .cg and whole rows the 1,024 CTAs of a gate/up product queued up
-      // at the L2 slices of those lines for 5 us).
+      // the CTAs of an SM ask L2 once, and only the T floats of a row that count.
       const int pieces = (T + 3) >> 2;  // 16-byte pieces of a 64-byte row
       for (int i = threadIdx.x; i < scale.count * pieces; i += WARPS * 32) {
         const int off = (i / pieces) * 16 + (i % pieces) * 4;
@@ -226,16 +224,14 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
     if constexpr (SINK) {
-      {
 #pragma unroll
-        for (int it = 0; it < SINK_ITEMS; ++it) {
-          const int idx = threadIdx.x + it * WARPS * 32;
-          const int row = idx & 15, tok = idx >> 4;
-          const bool live = tok < T && n0 + row < N;
-          old_resid[it] = live ? *reinterpret_cast<const volatile float*>(
-                                     sink.resid + (size_t)tok * sink.ldr + n0 + row) : 0.f;
-          gamma[it] = live ? sink.gamma[n0 + row] : 0.f;
-        }
+      for (int it = 0; it < SINK_ITEMS; ++it) {
+        const int idx = threadIdx.x + it * WARPS * 32;
+        const int row = idx & 15, tok = idx >> 4;
+        const bool live = tok < T && n0 + row < N;
+        old_resid[it] = live ? *reinterpret_cast<const volatile float*>(
+                                   sink.resid + (size_t)tok * sink.ldr + n0 + row) : 0.f;
+        gamma[it] = live ? sink.gamma[n0 + row] : 0.f;
       }
     }
   };

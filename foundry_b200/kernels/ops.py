@@ -809,7 +809,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if M <= SKINNY_ROWS:
         ksplit, warps = skinny_plan(N, K, allow_planes and out is None)
         if (residual is not None and NORM_FUSION and ksplit == 1 and out is None
-                and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
+                and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)
+                and (N + 15) // 16 <= MAX_SCALE_SHARES):
             return gemm_skinny_residual(x, w, residual, then_reads=then_reads, warps=warps)
         if ksplit > 1:
             planes = torch.empty((ksplit, M, N), dtype=torch.float32, device=x.device)
