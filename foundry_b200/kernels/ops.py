@@ -156,8 +156,6 @@ def add_launches(n: int) -> None:
     _COUNT[0] += n
 
 
-add_graph_launches = add_launches
-
 
 def _call(name: str, *args, tag=None) -> None:
     """Launch `name`. `tag` is (format, values...) naming the shape for the

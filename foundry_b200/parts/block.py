@@ -15,7 +15,7 @@ that used it returns an `ops.NormPending`, which the norm turns into the
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 
