@@ -43,7 +43,9 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
 // do it when a block's main loop is through (its last loads are on their way, the
 // epilogue is left): the successor's blocks then take the places that this
 // kernel's blocks leave and have their first weights requested when it ends (3B
-// decode step at batch 8: 2.09 -> 1.98 ms). The single-token attention doing the
+// decode step at batch 8: 2.09 -> 1.98 ms); the CTAs of the grid's last half round
+// do it as they start, when no CTA of the kernel waits for room any more (1.93 ms).
+// The single-token attention doing the
 // same lost (2.01 -> 2.56 ms: its blocks end at different times and still have
 // their merge across the cluster to do while the successor's sit beside them), and
 // in the tcgen05 products (after the last tile's loads) it changed nothing. At the
