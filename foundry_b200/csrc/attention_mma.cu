@@ -758,12 +758,11 @@ attn_decode_kernel(const AttnParams p) {
 template <int D>
 int launch_prefill(const AttnParams& p, int q_blocks, cudaStream_t stream) {
   const int bytes = (64 + 4 * 64) * D * 2;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return fb_fail(2, "attention_prefill: %s", cudaGetErrorString(e));
-    configured = true;
   }
   fb_launch(attn_prefill_kernel<D>, dim3(dim3(q_blocks, p.A)), dim3(THREADS), bytes, stream, p);
   return fb_check_launch("attention_prefill");
@@ -776,12 +775,11 @@ int launch_decode_as(const AttnParams& p, cudaStream_t stream) {
   // and the CTA's own partial result for its cluster
   const int merge = 16 * D * 2 + (4 * 16 * (D + 8) + 128 + 16 * D + 32) * 4;
   if (merge > bytes) bytes = merge;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, ST, CLUSTER, NARROW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return fb_fail(2, "attention_decode: %s", cudaGetErrorString(e));
-    configured = true;
   }
   const dim3 grid(p.n_seqs, p.Kh, p.splits);
   if (CLUSTER)

@@ -44,6 +44,7 @@
 #include <mutex>
 #include <unordered_map>
 
+#define FB_STATUS_KERNEL 3
 #include "tcgen05.cuh"
 
 namespace {
@@ -141,11 +142,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int seq = s_info[0];
   if (seq < 0) return;  // a block beyond the real count: nothing allocated yet
   if (smem_u32(base) & 1023u) {  // the tiles' swizzle pattern assumes this alignment
-    if (threadIdx.x == 0 && atomicCAS(&g_status[0], 0, 1) == 0) {
-      g_status[1] = 20;
-      g_status[2] = (int)(blockIdx.x + gridDim.x * blockIdx.y);
-      g_status[3] = (int)(smem_u32(base) & 1023u);
-    }
+    if (threadIdx.x == 0)
+      record_failure(20, (int)(blockIdx.x + gridDim.x * blockIdx.y), (int)(smem_u32(base) & 1023u));
     return;
   }
   if (warp == 1) {
@@ -409,13 +407,12 @@ int make_map(CUtensorMap* map, const void* ptr, int rank, const long long* dims,
 template <int D>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p,
            int q_blocks, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          FaSmem<D>::BYTES);
     if (e != cudaSuccess) return fb_fail(2, "attention_tc: %s", cudaGetErrorString(e));
-    configured = true;
   }
   fb_launch(attn_prefill_tc_kernel<D>, dim3(p.A, q_blocks), dim3(THREADS), FaSmem<D>::BYTES, stream,
             mq, mk, mv, p);
@@ -444,6 +441,7 @@ FB_API int fb_attention_prefill_tc(const void* q, long long q_stride, int T, voi
                  ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0,
              "attention_tc: pointers and strides must keep 16-byte alignment");
   if (q_blocks <= 0) return 0;
+  bind_status_mirror(stream);
   CUtensorMap mq, mk, mv;
   {
     const long long dims[2] = {(long long)A * D, T}, strides[1] = {q_stride};

@@ -24,6 +24,18 @@ constexpr int FB_PAGE = 64;
 int fb_fail(int code, const char* fmt, ...);  // records the message, returns code
 int fb_check_launch(const char* what);        // cudaGetLastError -> code
 
+// True the first time it is called with this table on the current device: for
+// per-kernel set-up (shared-memory opt-in, occupancy queries) that CUDA keeps
+// per device. `seen` is a static table of the call site. Devices beyond the
+// table are set up on every call, which is slower and still right.
+inline bool fb_first_use_on_device(bool (&seen)[64]) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return true;
+  if (seen[device]) return false;
+  seen[device] = true;
+  return true;
+}
+
 #define FB_REQUIRE(cond, ...)                      \
   do {                                             \
     if (!(cond)) return fb_fail(1, __VA_ARGS__);   \
@@ -38,22 +50,13 @@ int fb_check_launch(const char* what);        // cudaGetLastError -> code
 // before it writes anything an earlier kernel may still read (only constants
 // such as weights may be touched before; the products request their first
 // weight tiles there). When a kernel lets its successor's blocks be placed
-// (griddepcontrol.launch_dependents) decides whether that helps. The short
-// kernels of few blocks (norm, rotary) do it at once. The single-token products
-// do it when a block's main loop is through (its last loads are on their way, the
-// epilogue is left): the successor's blocks then take the places that this
-// kernel's blocks leave and have their first weights requested when it ends (3B
-// decode step at batch 8: 2.09 -> 1.98 ms); the CTAs of the grid's last half round
-// do it as they start, when no CTA of the kernel waits for room any more (1.93 ms).
-// The single-token attention doing the
-// same lost (2.01 -> 2.56 ms: its blocks end at different times and still have
-// their merge across the cluster to do while the successor's sit beside them), and
-// in the tcgen05 products (after the last tile's loads) it changed nothing. At the
-// START of a long kernel the same instruction lost, on the decode step (blocks of
-// later kernels sat waiting on the SMs, held registers and shared memory that the
-// running kernel's next blocks needed, and the step took half as long again) and
-// on the prompt step (with the persistent product or the prompt attention
-// triggering at their start, 12.1 ms became 13.0 to 13.8 ms).
+// (griddepcontrol.launch_dependents) decides whether that helps: the short
+// kernels of few blocks (norm, rotary) do it at once; the single-token
+// products when a block's main loop is through (the CTAs of the grid's last
+// half round as they start, when no CTA of the kernel waits for room any
+// more); the single-token attention and the tcgen05 products not at all, and
+// no long kernel at its start (the successor's blocks would sit on the SMs
+// holding registers and shared memory that this kernel's next blocks need).
 // Every kernel reads what an earlier kernel wrote with ordinary (coherent)
 // loads only: pointers to such data carry no `__restrict__` read-only promise
 // and no `ld.global.nc`, because after an early trigger the writer may still

@@ -19,6 +19,7 @@
 // Every wait on an mbarrier is bounded: when the bound is hit the CTA records
 // where in `fb_gemm_tc_status`, stops issuing work, lets the other roles run
 // out as well, frees its tensor memory and returns.
+#define FB_STATUS_KERNEL 1
 #include "gemm_tcgen05.cuh"
 
 namespace {
@@ -368,13 +369,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid,
            cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem<BN>::BYTES);
     if (e != cudaSuccess) return fb_fail(2, "gemm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
-    configured = true;
   }
   fb_launch(gemm_tc_kernel<BN>, dim3(grid), dim3(THREADS), Smem<BN>::BYTES, stream, ma, mb, p);
   return fb_check_launch("gemm_tc");
@@ -383,13 +383,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
 template <int BN>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
                       int tiles_a, int tiles_b, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};
+  if (fb_first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem<BN>::BYTES);
     if (e != cudaSuccess) return fb_fail(2, "gemm_tc: shared memory opt-in: %s", cudaGetErrorString(e));
-    configured = true;
   }
   const int total = tiles_a * tiles_b;
   const int ctas = total < sm_count() ? total : sm_count();
@@ -437,6 +436,7 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
              "unit stride");
   const int total_kb = (K + BK - 1) / BK;
   FB_REQUIRE(splits <= total_kb, "gemm_tc: %d splits for %d K blocks", splits, total_kb);
+  bind_status_mirror(stream);
   GemmParams p;
   p.rows_a = rows_a; p.rows_b = rows_b; p.K = K;
   p.kblocks_per_split = (total_kb + splits - 1) / splits;

@@ -1,5 +1,6 @@
 // The tcgen05 product with two SMs on one tile (cta_group::2); the one-CTA forms
 // and the entry point `fb_gemm_tc` are in gemm_tcgen05.cu.
+#define FB_STATUS_KERNEL 2
 #include "gemm_tcgen05.cuh"
 
 namespace {
@@ -101,11 +102,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     if ((spin & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
-  if (atomicCAS(&g_status[0], 0, 1) == 0) {
-    g_status[1] = where;
-    g_status[2] = (int)blockIdx.x;
-    g_status[3] = kb;
-  }
+  record_failure(where, (int)blockIdx.x, kb);
   return false;
 }
 
@@ -398,7 +395,11 @@ template <int BN>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_a,
                 int tiles_b, void* workspace, long long workspace_bytes, int* counters,
                 int counters_len, int share_min_kblocks, cudaStream_t stream) {
-  static int clusters_max = 0;
+  static int clusters_of_device[64] = {};  // CTA pairs that run at once, per device
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64) device = 63;
+  int& clusters_max = clusters_of_device[device];
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = SmemPair<BN>::BYTES;
@@ -476,6 +477,7 @@ int fb_gemm_tc_pair(const void* a, long long lda, int rows_a, const void* b, lon
                     int rows_b, int bn, const FbGemmParams& p, void* workspace,
                     long long workspace_bytes, int* counters, int counters_len,
                     int share_min_kblocks, cudaStream_t stream) {
+  bind_status_mirror(stream);
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, rows_a, p.K, lda, BM);
   if (rc) return rc;

@@ -4,19 +4,73 @@
 //
 // Every wait is bounded: when the bound is hit the caller's `abort_flag` (in
 // shared memory) is raised so that the CTA's other roles give up too, and the
-// place is recorded in a status word that the host can read
-// (`fb_gemm_tc_status`).
+// place is recorded twice: in a status word on the device (`fb_gemm_tc_status`
+// and its siblings read and clear it) and in a record in pinned host memory
+// that the host reads without a copy (`fb_status_mirror`), so that the engine
+// can check it wherever it has just synchronised.
+//
+// A file that includes this header first defines FB_STATUS_KERNEL, the code
+// under which its kernels report (1 the one-CTA products, 2 the paired
+// product, 3 the prompt attention).
 #pragma once
 
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
+
+#ifndef FB_STATUS_KERNEL
+#error "define FB_STATUS_KERNEL before including tcgen05.cuh"
+#endif
+
+int* fb_status_mirror_host();  // common.cu: the pinned record, or null
 
 namespace {
 
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ int g_status[4];  // [0] != 0: a wait ran out; [1] where; [2] block; [3] k-block
+__device__ int* g_status_mirror;  // the host-visible record {kernel, where, block, k-block}
+
+// The first failure of this file's kernels since the status was last cleared.
+__device__ __forceinline__ void record_failure(int where, int block, int kb) {
+  if (atomicCAS(&g_status[0], 0, 1) != 0) return;
+  g_status[1] = where;
+  g_status[2] = block;
+  g_status[3] = kb;
+  volatile int* mirror = g_status_mirror;
+  if (mirror != nullptr && mirror[0] == 0) {
+    mirror[1] = where;
+    mirror[2] = block;
+    mirror[3] = kb;
+    __threadfence_system();
+    mirror[0] = FB_STATUS_KERNEL;  // last, so that a host that sees it sees the rest
+    __threadfence_system();
+  }
+}
+
+// Points this file's kernels at the host-visible record, once per device.
+// Launchers call it before their launch; a capturing stream puts it off (the
+// copy to the symbol is no stream work), and a device beyond the table goes
+// without the mirror: the status on the device is recorded either way.
+inline void bind_status_mirror(cudaStream_t stream) {
+  static std::mutex mu;
+  static bool bound[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return;
+  std::lock_guard<std::mutex> lock(mu);
+  if (bound[device]) return;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess ||
+      capturing != cudaStreamCaptureStatusNone)
+    return;
+  int* host = fb_status_mirror_host();
+  int* mapped = nullptr;
+  if (host != nullptr && cudaHostGetDevicePointer((void**)&mapped, host, 0) == cudaSuccess)
+    cudaMemcpyToSymbol(g_status_mirror, &mapped, sizeof(mapped));
+  bound[device] = true;
+}
 
 // ------------------------------------------------------------------ PTX faces
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -52,11 +106,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if ((spin & 1023u) == 1023u && *abort_flag) return false;
   }
   *abort_flag = 1;
-  if (atomicCAS(&g_status[0], 0, 1) == 0) {
-    g_status[1] = where;
-    g_status[2] = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-    g_status[3] = kb;
-  }
+  record_failure(where, (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)), kb);
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar,

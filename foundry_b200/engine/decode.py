@@ -26,6 +26,7 @@ from ..cache.pages import PAGE
 from ..kernels import ops
 from ..sampling.params import SamplingParams
 from .context import StepContext
+from .staging import StagingRing
 
 
 def bucket_of(n: int) -> int:
@@ -48,17 +49,22 @@ class DecodeRunner:
         # cu_tokens | kv_lens | one page table per group
         sizes = [b, b, b, b, b, b + 1, b] + [b * width for _ in groups]
         offsets = [int(o) for o in np.cumsum([0] + sizes)]
-        total = offsets[-1]
-        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
-        self.host_np = self.host.numpy()
-        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        # the host may prepare steps ahead of the device: uploads go through a ring
+        self.fields = StagingRing(offsets[-1], torch.int32, dev)
+        self.dev = self.fields.dev
+        self.host_np = self.fields.values
         part = [self.dev[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
         self.h = [self.host_np[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
         self.meta_start = offsets[1]  # everything after the token ids
+        # A captured step must not depend on host-side values of the step, so its
+        # context carries none. A model with a part that reads them (one that does
+        # not set `replay_safe`) is never captured: its steps are launched plainly
+        # and the session fills the host copies in before each one.
+        self.capturable = engine.model.replay_safe()
         self.ctx = StepContext(
             n_tokens=b, n_seqs=b, n_want=b, token_ids=part[0], positions=part[1],
             seq_of_token=part[2], want_rows=part[3], slots=part[4], cu_tokens=part[5],
-            kv_lens=part[6], slots_host=[], cu_tokens_host=list(range(b + 1)), kv_lens_host=[],
+            kv_lens=part[6], slots_host=None, cu_tokens_host=None, kv_lens_host=None,
             is_decode=True, max_q_len=1, max_kv_len=width * PAGE)
         for i, group in enumerate(groups):
             self.ctx._tables[id(group)] = part[7 + i].view(b, width)
@@ -69,8 +75,8 @@ class DecodeRunner:
         # sampling inputs: temperature per row; random stream and step count per row
         self.temperature = torch.zeros(b, dtype=torch.float32, device=dev)
         self.temperature_value = 0.0
-        self.meta64_host = torch.zeros(2 * b, dtype=torch.int64).pin_memory()
-        self.meta64 = torch.zeros(2 * b, dtype=torch.int64, device=dev)
+        self.sampling_fields = StagingRing(2 * b, torch.int64, dev)
+        self.meta64 = self.sampling_fields.dev
         self.next_tokens = torch.zeros(b, dtype=torch.int32, device=dev)
         self.tokens_host = torch.zeros(b, dtype=torch.int32).pin_memory()
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -88,7 +94,7 @@ class DecodeRunner:
 
     def run(self) -> None:
         """One step over the buffers' current contents."""
-        if not self.engine.use_graphs:
+        if not self.engine.use_graphs or not self.capturable:
             self._body()
             return
         if self.graph is None:
@@ -163,7 +169,11 @@ class DecodeSession:
             width = 8
             while width < need:
                 width *= 2
+            previous = runner
             runner = self.runner = engine.decode_runner(bucket, width)
+            if previous is not None and previous is not runner and previous.bucket == bucket:
+                # tokens that stay on the device (`step`) move on with the session
+                runner.ctx.token_ids.copy_(previous.next_tokens)
         h = runner.h
         h[1][:n] = lengths
         h[1][n:] = 0
@@ -185,6 +195,11 @@ class DecodeSession:
                     table[i, :len(pages)] = pages
         for i in range(n, bucket):
             runner.row_sig[i] = None
+        if not runner.capturable:  # plain launches: the parts may read the step on the host
+            pad = bucket - n
+            runner.ctx.slots_host = self.slots + [cache.scratch_slot] * pad
+            runner.ctx.cu_tokens_host = list(range(bucket + 1))
+            runner.ctx.kv_lens_host = [length + 1 for length in lengths] + [0] * pad
         return runner
 
     def _upload(self, runner: DecodeRunner, tokens: Optional[Sequence[int]]) -> None:
@@ -194,19 +209,17 @@ class DecodeSession:
             runner.host_np[:n] = tokens
             runner.host_np[n:runner.bucket] = 0
             start = 0
-        runner.dev[start:].copy_(runner.host[start:], non_blocking=True)
-        self.h2d_bytes_per_step = (runner.host.numel() - start) * 4
+        self.h2d_bytes_per_step = runner.fields.upload(start)
         temperature = float(self.sampling.temperature)
         if runner.temperature_value != temperature:
             runner.temperature.fill_(temperature)
             runner.temperature_value = temperature
         if temperature > 0.0:
             b = runner.bucket
-            m = runner.meta64_host.numpy()
+            m = runner.sampling_fields.values
             m[:n] = self.streams
             m[b:b + n] = self.counts
-            runner.meta64.copy_(runner.meta64_host, non_blocking=True)
-            self.h2d_bytes_per_step += runner.meta64_host.numel() * 8
+            self.h2d_bytes_per_step += runner.sampling_fields.upload()
 
     def set_tokens(self, tokens: Sequence[int]) -> None:
         """Device-resident stepping (`step`) starts from these input tokens."""
@@ -229,10 +242,14 @@ class DecodeSession:
         n = len(self.slots)
         runner.tokens_host[:n].copy_(runner.next_tokens[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        ops.raise_on_device_failure()
         self.d2h_bytes_per_step = n * 4
         self.counts = [c + 1 for c in self.counts]
         return runner.tokens_host[:n].tolist()
 
     def logits(self) -> torch.Tensor:
-        """float32 logits [rows, vocab] of the last step (a buffer the next step reuses)."""
+        """float32 logits [rows, vocab] of the last step (a buffer the next step
+        reuses). Waits for the step and raises if one of its kernels gave up."""
+        torch.cuda.current_stream().synchronize()
+        ops.raise_on_device_failure()
         return self.runner.logits[:len(self.slots)]

@@ -23,6 +23,7 @@ from .context import SequenceStep, build_context
 from .prompt import PromptRunners
 from .decode import DecodeRunner, DecodeSession
 from .model import Model
+from ..kernels import ops
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "f32": torch.float32, "fp32": torch.float32,
@@ -128,10 +129,17 @@ class Engine:
         if self._prompts is None:
             self._prompts = PromptRunners(self)
         if self._prompts.wants(steps):
-            return self._prompts.step(steps)
-        ctx = build_context(self.cache, steps, self.spec.vocab_size, self.device,
-                            self.spec.max_positions)
-        return self.model.forward(ctx, self.cache)
+            logits = self._prompts.step(steps)
+        else:
+            ctx = build_context(self.cache, steps, self.spec.vocab_size, self.device,
+                                self.spec.max_positions)
+            logits = self.model.forward(ctx, self.cache)
+        if logits.shape[0]:
+            # logits leave the engine: wait for them, and let none out after a
+            # kernel gave up on a bounded wait
+            torch.cuda.current_stream().synchronize()
+            ops.raise_on_device_failure()
+        return logits
 
     def step_select(self, steps: Sequence[SequenceStep], params: SamplingParams,
                     keys: Sequence[int], counts: Sequence[int]) -> List[int]:

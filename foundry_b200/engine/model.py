@@ -107,6 +107,17 @@ class Model:
         total += self.output_head.numel() * self.output_head.element_size()
         return total
 
+    def replay_safe(self) -> bool:
+        """Whether every part says that its forward reads nothing of the step
+        on the host (`replay_safe = True`, see parts/base.py): only then may a
+        step of this model be captured once and replayed."""
+        for block in self.blocks:
+            parts = [block] + [getattr(block, name, None) for name in
+                               ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")]
+            if not all(p is not None and getattr(p, "replay_safe", False) for p in parts):
+                return False
+        return bool(getattr(self.final_norm, "replay_safe", False))
+
     # --------------------------------------------------------------- cache
     def cache_requests(self) -> Dict[int, CacheRequest]:
         requests: Dict[int, CacheRequest] = {}

@@ -32,6 +32,7 @@ from ..cache.pages import PAGE
 from ..kernels import ops
 from .context import SequenceStep, StepContext, StepPlan, plan_step
 from .decode import bucket_of
+from .staging import StagingRing
 
 # steps of more tokens than this run as plain launches (0: always plain)
 PROMPT_GRAPH_TOKENS = int(os.environ.get("FOUNDRY_B200_PROMPT_GRAPH_TOKENS", "128"))
@@ -59,9 +60,11 @@ class PromptRunner:
         # packed int32 fields, as in build_context
         sizes = [t, t, t, want, s, s + 1, s] + [s * width for _ in groups]
         offsets = [int(o) for o in np.cumsum([0] + sizes)]
-        self.host = torch.zeros(offsets[-1], dtype=torch.int32).pin_memory()
-        host_np = self.host.numpy()
-        self.dev = torch.zeros(offsets[-1], dtype=torch.int32, device=dev)
+        # steps may be queued ahead of the device (portions of a prompt whose logits
+        # nobody waits for): the upload goes through a ring of pinned buffers
+        self.fields = StagingRing(offsets[-1], torch.int32, dev)
+        self.dev = self.fields.dev
+        host_np = self.fields.values
         part = [self.dev[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
         self.h = [host_np[offsets[i]:offsets[i + 1]] for i in range(len(sizes))]
         self.h_tables = [self.h[7 + i].reshape(s, width) for i in range(len(groups))]
@@ -98,7 +101,7 @@ class PromptRunner:
         h[6][S:] = 0
         for table, (_, w, rows) in zip(self.h_tables, plan.tables):
             table[:S, :w] = np.asarray(rows, np.int32).reshape(S, w)
-        self.dev.copy_(self.host, non_blocking=True)
+        self.fields.upload()
 
     def _body(self) -> None:
         self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
@@ -138,12 +141,7 @@ class PromptRunner:
 def replay_safe(model) -> bool:
     """Whether every part of the model says that its forward reads nothing of
     the step on the host."""
-    for block in model.blocks:
-        parts = [block] + [getattr(block, name, None) for name in
-                           ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")]
-        if not all(p is not None and getattr(p, "replay_safe", False) for p in parts):
-            return False
-    return bool(getattr(model.final_norm, "replay_safe", False))
+    return model.replay_safe()
 
 
 class PromptRunners:

@@ -687,15 +687,57 @@ if _os.environ.get("FOUNDRY_B200_PDL", "1") == "0":
     set_dependent_launch(False)
 
 
+_STATUS_READERS = ("fb_gemm_tc_status", "fb_gemm_tc_pair_status", "fb_attention_tc_status")
+# kernel codes of the host-visible failure record (FB_STATUS_KERNEL in csrc)
+_STATUS_KERNELS = {1: "tcgen05 product", 2: "paired tcgen05 product", 3: "tcgen05 prompt attention"}
+_STATUS_ROLES = {1: "tile loads", 2: "matrix instructions", 3: "epilogue",
+                 20: "shared-memory alignment"}
+_MIRROR = []
+
+
 def gemm_tc_status():
     """0 when no bounded wait of the tcgen05 kernels (products and prompt
-    attention) ever ran out, else (role, block, step). Synchronises the device."""
-    for name in ("fb_gemm_tc_status", "fb_gemm_tc_pair_status", "fb_attention_tc_status"):
+    attention) ever ran out, else (role, block, step). Reads and clears the
+    status words on the device; synchronises the device."""
+    for name in _STATUS_READERS:
         detail = (ctypes.c_int * 3)()
         code = _fn(name)(ctypes.cast(detail, ctypes.c_void_p))
         if code != 0:
             return (code, detail[1], detail[2])
     return 0
+
+
+def _status_mirror():
+    """The failure record in pinned host memory as four ints (kernel, role,
+    block, K block), or None if the library could not make it."""
+    if not _MIRROR:
+        lib = library.load()
+        lib.fb_status_mirror.restype = ctypes.c_void_p
+        lib.fb_status_mirror.argtypes = []
+        address = lib.fb_status_mirror()
+        _MIRROR.append((ctypes.c_int * 4).from_address(address) if address else None)
+    return _MIRROR[0]
+
+
+def raise_on_device_failure() -> None:
+    """Raise `KernelError` if a kernel gave up on a bounded wait since the last
+    check: what it computed after that is garbage, so nothing computed since
+    may leave the engine. The kernels record the failure in pinned host memory,
+    so the check is a host load; call it where the stream was just
+    synchronised (the reference turns device failures into errors of the
+    call the same way, src/generate/error.rs `Forward`, `Synchronize`)."""
+    record = _status_mirror()
+    if record is None or record[0] == 0:
+        return
+    kernel, role, block, kblock = (int(v) for v in record)
+    for i in range(4):
+        record[i] = 0
+    for name in _STATUS_READERS:  # clear the words on the device too
+        _fn(name)(None)
+    raise KernelError(
+        f"{_STATUS_KERNELS.get(kernel, f'kernel {kernel}')}: a bounded wait ran out "
+        f"({_STATUS_ROLES.get(role, f'role {role}')}, block {block}, K block {kblock}); "
+        f"the results of this step are not valid")
 
 
 def sum_planes(planes: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

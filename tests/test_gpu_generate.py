@@ -111,6 +111,101 @@ def test_temperature_sampling_is_the_host_restatement(tiny_folders):
     assert other_seed.token_ids != out.token_ids
 
 
+def test_temperature_sampling_in_bfloat16(tiny_folders):
+    """The 16-bit decode graph with temperature > 0 (random streams and counts
+    uploaded every step). Its logits differ from the plain model's by 16-bit
+    rounding, so a token is right when it is the plain model's choice or when
+    the plain model scores it within that rounding of its choice; most tokens
+    must be the plain choice itself. Checked along the engine's own sequence."""
+    from foundry_b200 import SamplingParams
+    name = "tiny_b"
+    cfg, w = plain.read_model(tiny_folders[name])
+    prompts = [tiny.random_tokens(80 + i, n, cfg["vocab_size"]) for i, n in enumerate((1, 7, 40, 90, 23))]
+    temperature = 0.8
+    params = SamplingParams(temperature=temperature, seed=4321)
+    engine = engine_for(tiny_folders[name], "bfloat16")
+    out = engine.generate(prompts, 16, eos_token_id=[], sampling=params)
+    assert [len(r) for r in out.token_ids] == [16] * 5
+    equal = total = 0
+    for r, (prompt, row) in enumerate(zip(prompts, out.token_ids)):
+        seq = list(prompt)
+        for count, token in enumerate(row):
+            logits = plain.forward(cfg, w, seq)[-1]
+            scores = plain.sample_scores(logits, temperature, 4321, r, count)
+            best = int(torch.argmax(scores))
+            # the bound of `tiny.assert_logits_close` on a 16-bit logit, on both candidates
+            slack = 2 * 1e-2 * max(1.0, float(logits.abs().max())) / temperature
+            assert token == best or float(scores[best] - scores[token]) < slack, (r, count)
+            equal += token == best
+            total += 1
+            seq.append(token)
+    assert equal >= 0.9 * total, f"{equal} of {total} tokens are the plain model's choice"
+    assert len({tuple(r) for r in out.token_ids}) > 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_ahead_of_the_device(tiny_folders, dtype):
+    """The host may prepare steps faster than the device runs them: decode steps
+    whose tokens stay on the device are queued without waiting, and so are
+    portions of a prompt whose logits nobody asks for. Every step must still
+    run with its own positions, lengths and page tables (the upload of a step's
+    description is staged so that a later step cannot overwrite it). The device
+    is kept busy first, so that everything below is queued before any of it runs."""
+    from foundry_b200 import SamplingParams
+    from foundry_b200.engine import SequenceStep
+    name = "tiny_b"
+    cfg, w = plain.read_model(tiny_folders[name])
+    V = cfg["vocab_size"]
+    prompts = [tiny.random_tokens(700 + i, n, V) for i, n in enumerate((60, 5, 33))]
+    steps = 70  # across a page boundary for every sequence
+    # with the host in every step
+    engine = engine_for(tiny_folders[name], dtype)
+    slots = [engine.open_sequence() for _ in prompts]
+    first = engine.step_select([SequenceStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)],
+                               SamplingParams(), [0, 1, 2], [0, 0, 0])
+    session = engine.decode_session(slots)
+    by_host, tokens = [first], first
+    for _ in range(steps):
+        tokens = session.step_host(tokens)
+        by_host.append(tokens)
+    for s in slots:
+        engine.close_sequence(s)
+    # the same, queued ahead
+    engine = engine_for(tiny_folders[name], dtype)
+    slots = [engine.open_sequence() for _ in prompts]
+    engine.step([SequenceStep(s, p, []) for s, p in zip(slots, prompts)])
+    session = engine.decode_session(slots)
+    session.set_tokens(first)
+    session.step()  # the first call of a bucket runs plainly and captures
+    torch.cuda.synchronize()
+    record = torch.zeros((steps, len(slots)), dtype=torch.int32, device="cuda:0")
+    record[0].copy_(session.runner.next_tokens[:len(slots)])
+    torch.cuda._sleep(400_000_000)  # a fifth of a second: the host gets far ahead
+    for i in range(1, steps):
+        session.step()
+        record[i].copy_(session.runner.next_tokens[:len(slots)])
+    queued = record.cpu().tolist()
+    assert queued == by_host[1:]
+    if dtype == "float32":  # and both are the plain model's greedy tokens
+        for i, p in enumerate(prompts):
+            want = plain.greedy_generate(cfg, w, p, 12)
+            assert [first[i]] + [row[i] for row in queued[:11]] == want
+    for s in slots:
+        engine.close_sequence(s)
+    # a prompt in ten portions of one bucket, none of them waited for
+    tokens = tiny.random_tokens(77, 101, V)
+    want = plain.forward(cfg, w, tokens).numpy()[-1:]
+    slot = engine.open_sequence()
+    engine.step([SequenceStep(slot, tokens[:10], [])])  # captures the bucket's graph
+    torch.cuda.synchronize()
+    torch.cuda._sleep(400_000_000)
+    for at in range(10, 100, 10):
+        engine.step([SequenceStep(slot, tokens[at:at + 10], [])])
+    got = engine.step([SequenceStep(slot, tokens[100:], [0])]).cpu().numpy()
+    scale = max(1.0, float(np.abs(want).max()))
+    assert np.abs(got - want).max() <= (2e-5 if dtype == "float32" else 5e-2) * scale
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_stays_on_the_plain_model(tiny_folders, dtype):
     """200 single-token steps after a short prompt, across several page
@@ -219,6 +314,41 @@ def test_short_prompt_steps_replayed_equal_plain_launches(tiny_folders, dtype):
     assert prompt_graphs.PROMPT_GRAPH_TOKENS == 128
     for a, b in zip(*results):
         assert a.shape == b.shape and torch.equal(a, b)
+
+
+def test_a_kernel_that_gave_up_is_an_error_of_the_call(tiny_folders, monkeypatch):
+    """No logits or tokens leave the engine once a kernel has recorded that a
+    bounded wait ran out. The record is a stand-in here (no wait is made to run
+    out on the GPU): each entry point must look at it after it synchronised."""
+    import ctypes
+    from foundry_b200.engine import SequenceStep
+    from foundry_b200.kernels import ops
+    engine = engine_for(tiny_folders["tiny_a"], "bfloat16")
+    fake = (ctypes.c_int * 4)()
+    monkeypatch.setattr(ops, "_MIRROR", [fake])
+
+    def fail():
+        fake[0], fake[1], fake[2], fake[3] = 1, 2, 3, 4
+
+    slot = engine.open_sequence()
+    engine.step([SequenceStep(slot, [1, 2, 3], [2])])  # nothing recorded: fine
+    fail()
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        engine.step([SequenceStep(slot, [4, 5], [1])])
+    engine.step([SequenceStep(slot, [6], [0])])  # the record was cleared with the report
+    fail()
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        engine.step([SequenceStep(slot, [7], [0])])
+    session = engine.decode_session([slot])
+    fail()
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        session.step_host([8])
+    engine.close_sequence(slot)
+    fail()
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        engine.generate([[1, 2, 3]], 4, eos_token_id=[])
+    assert engine.cache.table.slots.held == 0  # the loop gave its slots back
+    assert engine.generate([[1, 2, 3]], 4, eos_token_id=[]).token_ids[0]
 
 
 def test_refusals_of_the_step_function(tiny_folders):

@@ -174,20 +174,19 @@ def register_toy():
             return StateRequest((self.h,), torch.float32)
 
         def forward(self, ctx, x, state):
-            rows = ctx.slots.long()
+            # Reads the step on the host in every kind of step, single-token steps
+            # included: the part does not set `replay_safe`, so the engine must
+            # launch its steps plainly and hand it the host copies (a captured
+            # step would replay the first step's slots and lengths for ever).
+            assert ctx.slots_host is not None and ctx.cu_tokens_host is not None
             xf = x.float()
-            if ctx.is_decode:  # one token per sequence: a vector update per row
-                total = state.rows.index_select(0, rows) + xf
-                state.rows.index_copy_(0, rows, total)
-                mean = total / (ctx.positions.float() + 1.0).unsqueeze(1)
-            else:
-                parts = []
-                for i, slot in enumerate(ctx.slots_host):
-                    a, b = ctx.cu_tokens_host[i], ctx.cu_tokens_host[i + 1]
-                    total = state.rows[slot] + torch.cumsum(xf[a:b], 0)
-                    state.rows[slot] = total[-1]
-                    parts.append(total)
-                mean = torch.cat(parts) / (ctx.positions.float() + 1.0).unsqueeze(1)
+            parts = []
+            for i, slot in enumerate(ctx.slots_host):
+                a, b = ctx.cu_tokens_host[i], ctx.cu_tokens_host[i + 1]
+                total = state.rows[slot] + torch.cumsum(xf[a:b], 0)
+                state.rows[slot] = total[-1]
+                parts.append(total)
+            mean = torch.cat(parts) / (ctx.positions.float() + 1.0).unsqueeze(1)
             return self.proj.forward(mean.to(self.dtype))
 
     register_mixer("toy_running_mean", RunningMean, replace=True)

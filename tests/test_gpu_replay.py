@@ -32,9 +32,9 @@ def oracle(tiny_folders):
     return out
 
 
-def make_engine(folder, dtype, max_tokens=1024):
+def make_engine(folder, dtype, max_tokens=1024, max_slots=16):
     from foundry_b200.engine import Engine
-    return Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens, max_slots=16)
+    return Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens, max_slots=max_slots)
 
 
 def run_whole(engine, tokens):
@@ -122,6 +122,43 @@ def test_unequal_batches_with_slot_reuse(tiny_folders, oracle, name, dtype):
     requests, expected = oracle[name]
     for batch_size, share in ((3, 0.5), (2, 0.9), (4, 0.1)):
         got = run_batches(engine, requests, batch_size, share)
+        for i, want in enumerate(expected):
+            tiny.assert_logits_close(got[i], want, dtype,
+                                     f"{name} request {i} in batches of {batch_size}")
+
+
+MANY = 60  # requests of the crowded schedules below
+
+
+@pytest.fixture(scope="module")
+def crowd(tiny_folders):
+    """{config: (requests, plain logits)}: many requests of unequal lengths,
+    from one token to nearly the model's position limit."""
+    out = {}
+    for name, folder in tiny_folders.items():
+        cfg, w = plain.read_model(folder)
+        rng = np.random.default_rng(7)
+        top = cfg["max_position_embeddings"] - 2
+        lengths = [1, 2, top, 64, 65] + [int(n) for n in rng.integers(3, top, size=MANY - 5)]
+        reqs = [tiny.random_tokens(900 + i, n, cfg["vocab_size"]) for i, n in enumerate(lengths)]
+        out[name] = (reqs, [plain.forward(cfg, w, r).numpy() for r in reqs])
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_twenty_and_forty_sequences_live_at_once(tiny_folders, crowd, name, dtype):
+    """Single-token steps of 17 to 64 rows: batches of 20 and of 40 requests,
+    prompts in one step, then one token each while the short ones end (so the
+    live count walks down through the row buckets 64, 32, 16, ... with their
+    padding rows), and the next batch takes the slots and pages given back."""
+    requests, expected = crowd[name]
+    longest = max(len(r) for r in requests)
+    for batch_size, share in ((40, 0.5), (20, 0.3)):
+        engine = make_engine(tiny_folders[name], dtype, max_slots=batch_size,
+                             max_tokens=batch_size * (-(-longest // 64)) * 64)
+        got = run_batches(engine, requests, batch_size, share)
+        assert max(b for b, _ in engine._runners) == (64 if batch_size == 40 else 32)
         for i, want in enumerate(expected):
             tiny.assert_logits_close(got[i], want, dtype,
                                      f"{name} request {i} in batches of {batch_size}")
