@@ -156,6 +156,16 @@ class SequenceCache:
         for slot, length in growth.items():
             self.table.grow(slot, length)
 
+    def step_token_limit(self) -> Optional[int]:
+        """The most tokens one sequence may bring in one step, or None for no
+        limit. A step writes all its keys before any of them is read, and a
+        windowed group's pages are a ring of `ring_pages * PAGE` rows in which
+        position p takes the row of p - ring_pages * PAGE: a step of c tokens
+        from position s on leaves s's window (s - window, s] intact only if
+        s + c - 1 - ring_pages * PAGE < s - window + 1."""
+        limits = [g.ring_pages * PAGE - g.window + 1 for g in self.groups if g.window]
+        return min(limits) if limits else None
+
     def free_tokens(self) -> int:
         return min((g.pages.pool.free for g in self.groups), default=0) * PAGE
 

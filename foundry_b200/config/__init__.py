@@ -2,7 +2,8 @@
 registry from architecture name to both."""
 from . import errors
 from .errors import ConfigError
-from .llama import CONFIG_FILE, Llama3RopeScaling, LlamaConfig, read_config_json
+from .files import CONFIG_FILE, read_config_json
+from .llama import Llama3RopeScaling, LlamaConfig
 from .registry import (Architecture, register_architecture, registered_architectures,
                        resolve_architecture, unregister_architecture)
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedule

@@ -21,9 +21,8 @@ from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Tuple
 
 from . import errors
+from .files import decode_json, read_config_json
 
-CONFIG_FILE = "config.json"
-MAX_CONFIG_BYTES = 1024 * 1024  # src/models/llama/config.rs:10
 MODEL_TYPE = "llama"  # src/models/llama/config.rs:11
 ROPE_TYPE_LLAMA3 = "llama3"  # src/models/llama/config.rs:12
 
@@ -191,34 +190,6 @@ class LlamaConfig:
 
 
 # ---------------------------------------------------------------- helpers
-
-
-def read_config_json(directory: str) -> dict:
-    path = os.path.join(directory, CONFIG_FILE)
-    try:
-        size = os.stat(path).st_size
-    except OSError as exc:
-        raise errors.ConfigRead(f"cannot read {path}: {exc}") from exc
-    if size > MAX_CONFIG_BYTES:
-        raise errors.ConfigTooLarge(f"{path} holds {size} bytes, the limit is {MAX_CONFIG_BYTES}")
-    try:
-        with open(path, "rb") as handle:
-            raw = handle.read()
-    except OSError as exc:
-        raise errors.ConfigRead(f"cannot read {path}: {exc}") from exc
-    return decode_json(raw)
-
-
-def decode_json(source) -> dict:
-    if isinstance(source, Mapping):
-        return dict(source)
-    try:
-        doc = json.loads(source)
-    except (ValueError, TypeError) as exc:
-        raise errors.ConfigJson(f"config is not valid JSON: {exc}") from exc
-    if not isinstance(doc, dict):
-        raise errors.ConfigJson("config.json does not hold a JSON object")
-    return doc
 
 
 class _Reader:

@@ -79,10 +79,9 @@ class StepPlan:
     tables: list  # (group, width, rows [n_seqs][width]) per cache group
 
 
-def plan_step(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
-              max_positions: Optional[int] = None) -> StepPlan:
-    """Validate a step and reserve its cache pages. Nothing is changed when
-    validation or the reservation fails."""
+def check_steps(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
+                max_positions: Optional[int] = None) -> Dict[int, int]:
+    """Validate a step; returns slot -> length after the step. Changes nothing."""
     if not steps:
         raise ValueError("a step needs at least one sequence")
     seen = set()
@@ -106,6 +105,14 @@ def plan_step(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: i
             raise ValueError(f"slot {s.slot} would reach {new_len} positions, the model's "
                              f"limit is {max_positions}")
         growth[s.slot] = new_len
+    return growth
+
+
+def plan_step(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
+              max_positions: Optional[int] = None) -> StepPlan:
+    """Validate a step and reserve its cache pages. Nothing is changed when
+    validation or the reservation fails."""
+    growth = check_steps(cache, steps, vocab_size, max_positions)
     starts = [cache.length(s.slot) for s in steps]
     cache.reserve(growth)
 

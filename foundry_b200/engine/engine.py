@@ -19,7 +19,8 @@ from ..config.spec import ModelSpec
 from ..sampling import Sampler, SamplingParams
 from ..weights.safetensors_io import WeightFiles
 from . import generate as loop
-from .context import SequenceStep, build_context
+from ..cache.pages import CacheFull
+from .context import SequenceStep, build_context, check_steps
 from .prompt import PromptRunners
 from .decode import DecodeRunner, DecodeSession
 from .model import Model
@@ -126,6 +127,9 @@ class Engine:
         in the order of `steps` and of each `want`."""
         if self._is_decode(steps):
             return self._decode(steps, SamplingParams(), None, None)[1].clone()
+        limit = self.cache.step_token_limit()
+        if limit is not None and any(len(s.tokens) > limit for s in steps):
+            return self._step_in_portions(steps, limit)
         if self._prompts is None:
             self._prompts = PromptRunners(self)
         if self._prompts.wants(steps):
@@ -140,6 +144,36 @@ class Engine:
             torch.cuda.current_stream().synchronize()
             ops.raise_on_device_failure()
         return logits
+
+    def _step_in_portions(self, steps: Sequence[SequenceStep], limit: int) -> torch.Tensor:
+        """A step in rounds of at most `limit` tokens per sequence, for models
+        with a windowed cache group (see `SequenceCache.step_token_limit`): the
+        logits come back as one step's would, in the order of `steps` and of
+        each `want`. The whole step is validated first, so that a refused step
+        changes nothing."""
+        plan_check = [SequenceStep(s.slot, list(s.tokens), list(s.want)) for s in steps]
+        growth = check_steps(self.cache, plan_check, self.spec.vocab_size, self.spec.max_positions)
+        if not self.cache.table.can_grow(growth):
+            raise CacheFull("the step needs more pages than are free")
+        rows = {}  # (sequence of the step, index into its `want`) -> logits row
+        longest = max(len(s.tokens) for s in plan_check)
+        for start in range(0, longest, limit):
+            portion, keys = [], []
+            for i, s in enumerate(plan_check):
+                if start >= len(s.tokens):
+                    continue
+                chunk = s.tokens[start:start + limit]
+                wanted = [(k, w - start) for k, w in enumerate(s.want)
+                          if start <= w < start + len(chunk)]
+                portion.append(SequenceStep(s.slot, chunk, [w for _, w in wanted]))
+                keys.extend((i, k) for k, _ in wanted)
+            logits = self.step(portion)
+            for row, key in zip(logits, keys):
+                rows[key] = row
+        ordered = [rows[(i, k)] for i, s in enumerate(plan_check) for k in range(len(s.want))]
+        if not ordered:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        return torch.stack(ordered)
 
     def step_select(self, steps: Sequence[SequenceStep], params: SamplingParams,
                     keys: Sequence[int], counts: Sequence[int]) -> List[int]:

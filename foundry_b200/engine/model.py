@@ -90,21 +90,21 @@ class Model:
                 f"--dtype float32 for a 32-bit weight file")
 
     def weight_bytes_read_per_step(self) -> int:
-        """Bytes of weights a decode step reads once: all but the embedding
-        rows (which are gathered), plus the output head."""
+        """Bytes of weights a single-token step reads once: every tensor the
+        model lists (`expected_tensors`), in the run dtype, except the embedding
+        table when a separate output head exists (its rows are only gathered;
+        a tied table is read whole as the head). A feed-forward that routes
+        tokens to some of its weights reads fewer than this counts."""
+        spec = self.spec
+        size = torch.empty((), dtype=self.dtype).element_size()
         total = 0
-        seen = set()
-        for entry in self.spec.schedule:
-            if entry.layer in seen:
+        for name, want in self.expected_tensors().items():
+            if name == spec.embedding_name and spec.output_head_name is not None:
                 continue
-            seen.add(entry.layer)
-            block = self.blocks[entry.layer]
-            for part in (block.mixer, block.feed_forward):
-                for held in vars(part).values():
-                    w = held if isinstance(held, torch.Tensor) else getattr(held, "weight", None)
-                    if isinstance(w, torch.Tensor) and w.dim() == 2:
-                        total += w.numel() * w.element_size()
-        total += self.output_head.numel() * self.output_head.element_size()
+            count = 1
+            for d in want.shape:
+                count *= int(d)
+            total += count * size
         return total
 
     def replay_safe(self) -> bool:

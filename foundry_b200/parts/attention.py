@@ -70,6 +70,15 @@ class GQAAttention(Part):
     def first_weight(self):
         return self.qkv.weight
 
+    def context_flops(self, token_counts, starts) -> float:
+        """Operations of the scores and the weighted sums of one step: 4 per
+        query head, head element and visible (query, key) pair."""
+        pairs = 0.0
+        for n, start in zip(token_counts, starts):
+            for p in (start, start + n - 1):  # causal: the mean of the first and last query
+                pairs += 0.5 * n * (min(p + 1, self.window) if self.window else p + 1)
+        return 4.0 * self.num_heads * self.head_dim * pairs
+
     # ------------------------------------------------------------------- run
     def forward(self, ctx, x, cache: KVView):
         table = ctx.page_table(cache.group)

@@ -17,7 +17,7 @@ from typing import Callable, Dict, Mapping, Optional
 
 import torch
 
-from ..config.llama import CONFIG_FILE
+from ..config.files import CONFIG_FILE
 from .safetensors_io import SINGLE_FILE, save_file
 
 

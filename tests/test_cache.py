@@ -116,3 +116,30 @@ def test_given_back_pages_are_used_again():
     table.close(a)
     table.grow(b, 3 * PAGE)
     assert sorted(table.groups[0].pages(b)) == sorted(first)
+
+
+def test_a_window_ring_limits_the_tokens_of_one_step():
+    """A step writes all its keys before it reads any: with a ring of
+    ceil(W / 64) + 1 pages, a step of c tokens from position s keeps the keys
+    (s - W, s] of its first token only while c <= ring * 64 - W + 1. Checked by
+    replaying the ring's overwrites."""
+    import torch
+    from foundry_b200.cache import KVRequest, SequenceCache
+    for window in (1, 33, 64, 100, 128, 200):
+        cache = SequenceCache({0: KVRequest(2, 16), 1: KVRequest(2, 16, window)}, 1024, 2,
+                              torch.float32, torch.device("cpu"))
+        limit = cache.step_token_limit()
+        ring = pages_for(window) + 1
+        assert limit == ring * PAGE - window + 1 >= PAGE
+        for start in (0, 5, 63, 64, 300):
+            for count, intact in ((limit, True), (limit + 1, False)):
+                rows = {}  # ring row -> position held after the step's writes
+                for p in range(max(0, start - ring * PAGE), start + count):
+                    rows[p % (ring * PAGE)] = p
+                needed = range(max(0, start - window + 1), start + 1)
+                ok = all(rows.get(p % (ring * PAGE)) == p for p in needed)
+                assert ok or not intact
+                if not intact and start >= window:
+                    assert not ok
+    no_window = SequenceCache({0: KVRequest(2, 16)}, 1024, 2, torch.float32, torch.device("cpu"))
+    assert no_window.step_token_limit() is None

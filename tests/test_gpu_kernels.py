@@ -333,6 +333,55 @@ def test_attention_picks_out_a_far_key(ops):
         close(out, want, 2e-2, 1e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,L,queries", [(100, 500, 93), (64, 130, 1), (70, 70, 70), (33, 400, 5)])
+def test_attention_cuda_cores_window_and_ring(ops, dtype, window, L, queries):
+    """A windowed layer group: the sequence's pages are a ring of
+    ceil(window / 64) + 1 in which position p lies in page (p / 64) % ring, and a
+    query at p reads the keys (p - window, p]. The ring is filled as L
+    single-token steps would leave it; the last `queries` tokens ask. For the
+    last query the key just outside the window and the key just inside it both
+    match the query far better than any other: the first must not count, the
+    second must."""
+    A, Kh, D = 4, 2, 32
+    ring = (window + 63) // 64 + 1
+    assert queries <= ring * 64 - window + 1  # what one step may bring
+    g = torch.Generator().manual_seed(window)
+    k = torch.randn(L, Kh, D, generator=g)
+    v = torch.randn(L, Kh, D, generator=g)
+    q = torch.randn(queries, A, D, generator=g)
+    p_last = L - 1
+    if p_last - window >= 0:
+        q[-1] = 0.0
+        q[-1, :, 0] = 6.0
+        k[p_last - window, :, 0] = 9.0      # just outside
+        k[p_last - window + 1, :, 0] = 8.0  # just inside
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    pages = [5, 2, 7, 1, 4][:ring]
+    store = torch.randn(8, 2, Kh, 64, D, generator=g).to(dtype)
+    for pos in range(L):  # later positions overwrite the ring's rows
+        store[pages[(pos // 64) % ring], 0, :, pos % 64] = k[pos]
+        store[pages[(pos // 64) % ring], 1, :, pos % 64] = v[pos]
+    store = store.to(DEV)
+    table = torch.tensor([pages], dtype=torch.int32, device=DEV)
+    positions = torch.arange(L - queries, L, dtype=torch.int32, device=DEV)
+    seq_of = torch.zeros(queries, dtype=torch.int32, device=DEV)
+    out = torch.full((queries, A * D), 5.0, dtype=dtype, device=DEV)
+    ops.attention_simt(q.reshape(queries, A * D).to(DEV), out, positions, seq_of, table,
+                       store[:, 0], store[:, 1], A, Kh, D, 1.0 / math.sqrt(D), window=window,
+                       ring_pages=ring)
+    want = torch.zeros(queries, A, D, dtype=torch.float64)
+    kd, vd, qd = k.double(), v.double(), q.double()
+    for r in range(queries):
+        pos = L - queries + r
+        lo = max(0, pos - window + 1)
+        for a in range(A):
+            s_ = (kd[lo:pos + 1, a // (A // Kh)] @ qd[r, a]) / math.sqrt(D)
+            want[r, a] = torch.softmax(s_, 0) @ vd[lo:pos + 1, a // (A // Kh)]
+    close(out, want.reshape(queries, A * D), 2e-5 if dtype == torch.float32 else 3e-2,
+          1e-5 if dtype == torch.float32 else 1e-2)
+
+
 def test_attention_refuses_sizes_it_does_not_build(ops):
     case, _ = make_paged_case([1], [10], 4, 2, 48, torch.bfloat16)
     out = torch.zeros_like(case["q"])

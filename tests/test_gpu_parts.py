@@ -443,6 +443,101 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
         FEED_FORWARDS.unregister("toy_routed_relu2")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_layer_beside_a_full_one(tmp_path, dtype):
+    """A toy architecture whose second layer attends to a window of 100 keys
+    while its first sees all of them: two cache groups, the windowed one a ring
+    of three pages. Prompts far longer than the ring (the engine feeds them in
+    portions that leave every window intact), a prompt cut so that a portion
+    ends exactly at the window's edge, and decoding past the ring's wrap, all
+    against the plain model with the same window."""
+    import foundry_b200 as fb
+    from dataclasses import replace
+    from foundry_b200.config import (Architecture, LlamaConfig, PartSpec, register_architecture,
+                                     unregister_architecture)
+    from foundry_b200.engine import SequenceStep
+    W = 100
+
+    def build_spec(config):
+        from foundry_b200.models.llama import build_llama_spec
+        base = build_llama_spec(config)
+        layers = list(base.layers)
+        layers[1] = replace(layers[1], mixer=PartSpec("gqa_attention",
+                                                      {**layers[1].mixer.params, "window": W}))
+        return replace(base, architecture="ToyWindowForCausalLM", layers=tuple(layers))
+
+    register_architecture(Architecture(
+        "ToyWindowForCausalLM", "llama",
+        lambda d: LlamaConfig.parse({**d, "architectures": ["ToyWindowForCausalLM"]}), build_spec),
+        replace=True)
+    try:
+        doc = {**tiny.CONFIGS["tiny_b"], "architectures": ["ToyWindowForCausalLM"],
+               "num_hidden_layers": 2, "max_position_embeddings": 640}
+        folder = fb.write_model_folder(str(tmp_path / "window"), LlamaConfig.parse(doc), 21, std=0.1)
+        cfg, w = plain.read_model(folder)
+
+        def plain_forward(tokens):
+            x = w["model.embed_tokens.weight"][torch.as_tensor(tokens)]
+            positions = list(range(len(tokens)))
+            for i, window in enumerate((None, W)):
+                p = f"model.layers.{i}"
+                n = plain.rms_norm(x, w[f"{p}.input_layernorm.weight"], cfg["rms_norm_eps"])
+                h = x + plain.attention(n, w, f"{p}.self_attn", cfg, positions, window=window)
+                n = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+                x = h + plain.mlp(n, w, f"{p}.mlp")
+            x = plain.rms_norm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+            return (x @ w["lm_head.weight"].T).numpy()
+
+        engine = fb.Engine.from_folder(folder, dtype=dtype, max_tokens=2048, max_slots=3)
+        assert len(engine.cache.groups) == 2
+        assert sorted(g.ring_pages for g in engine.cache.groups) == [0, 3]
+        assert engine.cache.step_token_limit() == 3 * 64 - W + 1
+        reqs = [tiny.random_tokens(400 + i, n, cfg["vocab_size"]) for i, n in enumerate((600, 93, 250))]
+        want = [plain_forward(r) for r in reqs]
+        # each whole in one call (600 tokens are seven portions of 93)
+        for i, r in enumerate(reqs):
+            s = engine.open_sequence()
+            got = engine.step([SequenceStep(s, r, list(range(len(r))))]).cpu().numpy()
+            engine.close_sequence(s)
+            tiny.assert_logits_close(got, want[i], dtype, f"windowed, whole, request {i}")
+        # all three in one batch: a prompt part, a second part, then single tokens to the end
+        slots = [engine.open_sequence() for _ in reqs]
+        cut1 = [300, 50, W]       # the third ends its first part exactly at the window's size
+        cut2 = [560, 80, 200]
+        rows = [[] for _ in reqs]
+
+        def run(spans):
+            steps = [SequenceStep(slots[i], reqs[i][a:b], list(range(b - a))) for i, a, b in spans]
+            out = engine.step(steps).cpu().numpy()
+            at = 0
+            for i, a, b in spans:
+                rows[i].append(out[at:at + b - a])
+                at += b - a
+
+        run([(i, 0, cut1[i]) for i in range(3)])
+        run([(i, cut1[i], cut2[i]) for i in range(3)])
+        at = list(cut2)
+        while any(at[i] < len(reqs[i]) for i in range(3)):
+            live = [i for i in range(3) if at[i] < len(reqs[i])]
+            run([(i, at[i], at[i] + 1) for i in live])
+            for i in live:
+                at[i] += 1
+        for i in range(3):
+            engine.close_sequence(slots[i])
+            tiny.assert_logits_close(np.concatenate(rows[i]), want[i], dtype,
+                                     f"windowed, in parts, request {i}")
+        engine.cache.table.check()
+        assert engine.cache.table.slots.held == 0
+        # a step that cannot fit is refused whole, before any portion ran
+        s = engine.open_sequence()
+        with pytest.raises(ValueError, match="positions"):
+            engine.step([SequenceStep(s, [1] * 641, [])])
+        assert engine.cache.length(s) == 0
+        engine.close_sequence(s)
+    finally:
+        unregister_architecture("ToyWindowForCausalLM")
+
+
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_single_token_steps_fold_the_norms_into_the_projections(tmp_path, monkeypatch, name):
     """In single-token steps the norm between two parts is work of the
