@@ -9,16 +9,23 @@ cache is sized for 4,096 tokens per sequence, and the timed steps run at a
 mean context of 3,072 tokens, the mean of decoding from 2,048 to 4,096.
 One JSON line is printed:
 
-  value     decoded tokens per second, timed on the device with CUDA events
-            (warm-up first; a step reads 6.4 GB of weights, far more than the
-            126 MB L2, so no L2 flush is needed between steps)
+  value     decoded tokens per second, timed on the device with CUDA events:
+            after the warm-up steps, BLOCKS blocks of --steps steps each are
+            timed one after another and the median block is reported (`steps`
+            and `ms_per_step` describe one block); a step reads 6.4 GB of
+            weights, far more than the 126 MB L2, so no L2 flush is needed
   e2e       the same through the Python entry point: token ids go in from
             pinned host memory and come back to the host every step
   prefill   one 2,048-token prompt in one step: tokens/s and the fraction of
             the bf16 tensor-core peak its FLOPs reach
   roofline  the decode step's bytes (every weight once, the live sequences'
             cache) / time, against the measured copy bandwidth
-  points    decode tokens/s at batch 1 and 64
+  points    decode tokens/s at batch 1 and 64, and the two other benchmark
+            configurations with their own workloads and rooflines:
+            llama_1b (16 layers; 32 prompts of 1..4096 tokens prefilled in one
+            step, 512 steps at temperature 1, context 8192) and llama_8b
+            (32 layers, separate head; 16 prompts of 1..8192 tokens, 256
+            greedy steps, context 16384)
 
 For --gpus N > 1 one line says that the library is single-GPU, exit code 2.
 """
@@ -38,30 +45,16 @@ sys.path.insert(0, ROOT)
 PUBLISHED_DECODE_B1 = 6.92  # tok/s, Apple M4 Pro (the reference's report.json)
 PUBLISHED_PREFILL_512 = 132.6
 
-CONFIG_3B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 28,
-    "hidden_size": 3072, "num_attention_heads": 24, "num_key_value_heads": 8, "head_dim": 128,
-    "intermediate_size": 8192, "vocab_size": 128256, "rms_norm_eps": 1e-5,
-    "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
-                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
-    "tie_word_embeddings": True, "max_position_embeddings": 131072,
-}
-FULL_LAYERS = 28
+BLOCKS = 5  # timed blocks of --steps decode steps; the median one is reported
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 
 
 def peaks():
     """(HBM GB/s, bf16 TFLOP/s burst, sustained, source)."""
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    try:
-        with open(path) as handle:
-            doc = json.load(handle)
-        return (float(doc["hbm_gbs"]), float(doc["bf16_tflops"]),
-                float(doc.get("bf16_tflops_sustained", doc["bf16_tflops"])), "measured")
-    except (OSError, KeyError, ValueError):
-        return 6650.0, 1590.0, 1400.0, "fallback"
+    from foundry_b200.bench.costs import load_peaks
+    got = load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+    return got["hbm_gbs"], got["bf16_tflops"], got["bf16_tflops_sustained"], got["source"]
 
 
 class ClockSampler:
@@ -107,23 +100,6 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def weight_and_cache_bytes(engine, context_lens) -> int:
-    """Bytes a decode step has to read: every weight it uses once, and the
-    keys and values of the live sequences."""
-    return engine.model.weight_bytes_read_per_step() + \
-        engine.cache.bytes_per_token() * int(sum(context_lens))
-
-
-def prefill_flops(cfg, tokens: int, layers: int) -> float:
-    """Products of a whole-prompt step: projections, causal attention, and the
-    output head on the one wanted row."""
-    h, i, v = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
-    q, kv, d, a = cfg.q_size, cfg.kv_size, cfg.head_dim, cfg.num_attention_heads
-    linear = 2.0 * tokens * (h * (q + 2 * kv) + q * h + 3 * h * i)
-    attention = 2.0 * 2.0 * a * d * tokens * (tokens + 1) / 2.0
-    return layers * (linear + attention) + 2.0 * h * v
-
-
 def fill(engine, batch: int, length: int, seed: int, chunk_tokens: int = 8192):
     """Open `batch` sequences and run `length` random tokens into each cache."""
     from foundry_b200.bench import SplitMix64, token_rows
@@ -136,53 +112,146 @@ def fill(engine, batch: int, length: int, seed: int, chunk_tokens: int = 8192):
     return slots
 
 
-def time_decode(engine, slots, steps: int, warmup: int, sampler=None):
-    """Device-timed decode steps (tokens stay on the device) and the launches made."""
+def median_block(blocks):
+    """The block of median duration among (ms per step, ...) tuples."""
+    return sorted(blocks, key=lambda blk: blk[0])[len(blocks) // 2]
+
+
+def time_decode(engine, slots, steps: int, warmup: int, blocks: int, sampler=None, sampling=None):
+    """Device-timed decode steps (tokens stay on the device): `blocks` blocks
+    of `steps` steps, each bracketed by CUDA events on the launching stream.
+    Returns [(ms per step, mean context lengths of the block)], the launches of
+    one block, the clock record."""
     import torch
     from foundry_b200.kernels import ops
-    session = engine.decode_session(slots)
+    session = engine.decode_session(slots, sampling) if sampling else engine.decode_session(slots)
+    session.set_tokens([1] * len(slots))
     for _ in range(warmup):
         session.step()
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = ops.launch_count()
     if sampler:
         sampler.start()
-    start.record()
-    for _ in range(steps):
-        session.step()
-    end.record()
-    torch.cuda.synchronize()
+    out, launches = [], 0
+    for _ in range(blocks):
+        before = [engine.cache.length(s) for s in slots]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = ops.launch_count()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(steps):
+            session.step()
+        end.record()
+        torch.cuda.synchronize()
+        launches = ops.launch_count() - launches0
+        out.append((start.elapsed_time(end) / steps, [c + steps / 2.0 for c in before]))
     clocks = sampler.stop() if sampler else None
-    ms = start.elapsed_time(end)
-    return ms / steps, ops.launch_count() - launches0, clocks, session
+    ops.raise_on_device_failure()
+    return out, launches, clocks
 
 
-def time_e2e(engine, slots, steps: int, warmup: int):
+def time_e2e(engine, slots, steps: int, warmup: int, blocks: int):
     """The public call a user makes for one decode step: host token ids in
-    (from pinned memory), host token ids out."""
+    (from pinned memory), host token ids out. Host clock, median block."""
     import torch
     session = engine.decode_session(slots)
     tokens = [1] * len(slots)
     for _ in range(warmup):
         tokens = session.step_host(tokens)
-    torch.cuda.synchronize()
-    started = time.perf_counter()
-    for _ in range(steps):
-        tokens = session.step_host(tokens)
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - started
-    return seconds / steps, session.h2d_bytes_per_step, session.d2h_bytes_per_step
+    out = []
+    for _ in range(blocks):
+        torch.cuda.synchronize()
+        started = time.perf_counter()
+        for _ in range(steps):
+            tokens = session.step_host(tokens)
+        torch.cuda.synchronize()
+        out.append(((time.perf_counter() - started) / steps,))
+    return median_block(out)[0], session.h2d_bytes_per_step, session.d2h_bytes_per_step
+
+
+def ragged_lengths(seed: int, count: int, longest: int):
+    """`count` prompt lengths uniform in [1, longest] from SplitMix64(seed)."""
+    from foundry_b200.bench import SplitMix64
+    rng = SplitMix64(seed)
+    return [1 + rng.below(longest) for _ in range(count)]
+
+
+def workload_point(name: str, preset_name: str, prompts: int, longest: int, seed: int,
+                   decode_steps: int, temperature: float, context: int, layers: int = 0) -> dict:
+    """One of the other benchmark configurations with its own workload:
+    `prompts` prompts of unequal lengths prefilled in ONE step (timed on the
+    device, after one untimed run of the same step), then `decode_steps`
+    single-token steps of all of them (greedy, or sampled at `temperature`),
+    with the decode step's bytes (weights once + the live cache at the middle
+    of the run) against the measured copy bandwidth and the prompt step's
+    operations against the measured tensor-core rate."""
+    import torch
+    from foundry_b200 import SamplingParams
+    from foundry_b200.bench import SplitMix64, token_rows
+    from foundry_b200.bench.costs import decode_step_bytes, step_flops
+    from foundry_b200.bench.presets import preset
+    from foundry_b200.config import resolve_architecture
+    from foundry_b200.engine import Engine, SequenceStep
+    doc = preset(preset_name)
+    full_layers = doc["num_hidden_layers"]
+    if layers:
+        doc["num_hidden_layers"] = layers
+    cfg = resolve_architecture(doc).parse_config(doc)
+    hbm_gbs, tflops_burst, _, source = peaks()
+    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=prompts * context,
+                                max_slots=prompts, norm_std=0.0)
+    lengths = ragged_lengths(seed, prompts, longest)
+    rng = SplitMix64(seed + 1000)
+    rows = [token_rows(rng, 1, n, 128000)[0] for n in lengths]
+    prefill_ms = None
+    for timed in (False, True):
+        slots = [engine.open_sequence() for _ in rows]
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([SequenceStep(s, r, [len(r) - 1]) for s, r in zip(slots, rows)])
+        b.record()
+        torch.cuda.synchronize()
+        prefill_ms = a.elapsed_time(b)
+        if not timed:
+            for s in slots:
+                engine.close_sequence(s)
+    flops = step_flops(engine.model, lengths, wanted_rows=prompts)
+    sampling = SamplingParams(temperature, seed) if temperature > 0 else None
+    blocks, launches, _ = time_decode(engine, slots, decode_steps, 3, 1, sampling=sampling)
+    ms, mean_ctx = blocks[0]
+    step_bytes = decode_step_bytes(engine, mean_ctx)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    for s in slots:
+        engine.close_sequence(s)
+    del engine
+    torch.cuda.empty_cache()
+    tokens = sum(lengths)
+    return {
+        "model": preset_name, "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+        "prompts": prompts, "prompt_tokens": tokens, "context": context,
+        "decode_steps": decode_steps, "temperature": temperature,
+        "prefill": {"value": tokens / (prefill_ms * 1e-3), "tokens": tokens, "ms": prefill_ms,
+                    "flops": flops, "frac": flops / (prefill_ms * 1e-3) / (tflops_burst * 1e12)},
+        "decode": {"value": prompts / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": launches,
+                   "mean_context": sum(mean_ctx) / len(mean_ctx)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": achieved / hbm_gbs, "bytes_per_step": step_bytes, "of": source},
+    }
 
 
 def run(args) -> dict:
     import torch
-    from foundry_b200.config import LlamaConfig
-    from foundry_b200.engine import Engine, SequenceStep
     from foundry_b200.bench import SplitMix64, token_rows
+    from foundry_b200.bench.costs import decode_step_bytes, step_flops
+    from foundry_b200.bench.presets import preset
+    from foundry_b200.config import resolve_architecture
+    from foundry_b200.engine import Engine, SequenceStep
 
-    layers = args.layers or FULL_LAYERS
-    cfg = LlamaConfig.parse({**CONFIG_3B, "num_hidden_layers": layers})
+    doc = preset("llama-3.2-3b")
+    full_layers = doc["num_hidden_layers"]
+    layers = args.layers or full_layers
+    doc["num_hidden_layers"] = layers
+    cfg = resolve_architecture(doc).parse_config(doc)
     hbm_gbs, tflops_burst, tflops_sustained, source = peaks()
     batch = args.batch
     max_batch = max(batch, 64 if not args.skip_points else batch)
@@ -205,36 +274,55 @@ def run(args) -> dict:
         if it >= 3:
             prefill_ms.append(a.elapsed_time(b))
     p_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
-    p_flops = prefill_flops(cfg, PREFILL_TOKENS, layers)
+    p_flops = step_flops(engine.model, [PREFILL_TOKENS])
     prefill = {"value": PREFILL_TOKENS / (p_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": p_ms,
                "frac": p_flops / (p_ms * 1e-3) / (tflops_burst * 1e12), "flops": p_flops,
                "peak_tflops": tflops_burst}
 
     # ----------------------------------------------------------------- decode
-    start_ctx = CONTEXT * 3 // 4 - (args.steps + args.warmup) // 2
+    # the timed blocks are centred on 3/4 of the context: the mean of decoding from
+    # a 2,048-token prompt to 4,096 tokens
+    blocks = max(1, args.blocks)
+    e2e_steps = max(8, args.steps // 2)
+    while blocks > 1 and CONTEXT * 3 // 4 + (blocks * args.steps) // 2 + blocks * e2e_steps + \
+            3 * args.warmup + 16 > CONTEXT:
+        blocks -= 1
+    start_ctx = max(1, CONTEXT * 3 // 4 - (blocks * args.steps + args.warmup) // 2)
     points = {}
 
-    def decode_at(b, steps, warmup, with_clocks):
-        slots = fill(engine, b, start_ctx, seed=10 + b)
+    def decode_at(b, steps, warmup, n_blocks, with_clocks):
+        # every point's timed steps are centred on the same context length
+        first = max(1, CONTEXT * 3 // 4 - (n_blocks * steps + warmup) // 2)
+        slots = fill(engine, b, first, seed=10 + b)
         sampler = ClockSampler() if with_clocks else None
-        ms, launches, clocks, session = time_decode(engine, slots, steps, warmup, sampler)
-        ctx_lens = [engine.cache.length(s) for s in slots]
-        result = (ms, launches, clocks, ctx_lens)
-        return slots, result
+        timed, launches, clocks = time_decode(engine, slots, steps, warmup, n_blocks, sampler)
+        return slots, timed, launches, clocks
 
-    slots, (ms, launches, clocks, ctx_lens) = decode_at(batch, args.steps, args.warmup, True)
-    mean_ctx = [c - args.steps / 2.0 for c in ctx_lens]
-    step_bytes = weight_and_cache_bytes(engine, mean_ctx)
+    slots, timed, launches, clocks = decode_at(batch, args.steps, args.warmup, blocks, True)
+    ms, mean_ctx = median_block(timed)
+    step_bytes = decode_step_bytes(engine, mean_ctx)
     achieved = step_bytes / (ms * 1e-3) / 1e9
-    e2e_s, h2d, d2h = time_e2e(engine, slots, max(8, args.steps // 2), args.warmup)
+    e2e_s, h2d, d2h = time_e2e(engine, slots, e2e_steps, args.warmup, blocks)
     for s in slots:
         engine.close_sequence(s)
     if not args.skip_points:
         for b in (1, 64):
-            pslots, (pms, _, _, _) = decode_at(b, max(8, args.steps // 2), args.warmup, False)
-            points[f"decode_b{b}"] = b / (pms * 1e-3)
+            pslots, ptimed, _, _ = decode_at(b, e2e_steps, args.warmup, 3, False)
+            points[f"decode_b{b}"] = b / (median_block(ptimed)[0] * 1e-3)
             for s in pslots:
                 engine.close_sequence(s)
+    del engine
+    torch.cuda.empty_cache()
+    if not args.skip_points and not args.skip_workloads:
+        # the two other benchmark configurations, each with its own workload
+        for key, spec in (("llama_1b", ("llama-3.2-1b", 32, 4096, 3, 512, 1.0, 8192)),
+                          ("llama_8b", ("llama-3.1-8b", 16, 8192, 4, 256, 0.0, 16384))):
+            point = workload_point(key, *spec)
+            points[key] = point
+            points[f"{key}_decode_tok_s"] = point["decode"]["value"]
+            points[f"{key}_decode_frac"] = point["roofline"]["frac"]
+            points[f"{key}_prefill_tok_s"] = point["prefill"]["value"]
+            points[f"{key}_prefill_frac"] = point["prefill"]["frac"]
 
     value = batch / (ms * 1e-3)
     return {
@@ -247,17 +335,20 @@ def run(args) -> dict:
                                   "prefill_over_132.6": prefill["value"] / PUBLISHED_PREFILL_512},
         "dtype": "bf16", "data": "synthetic: random token ids (SplitMix64), random-init weights N(0, 0.02)",
         "config": {
-            "model": "llama-3.2-3b-shape", "layers": layers, "layers_full": FULL_LAYERS,
+            "model": "llama-3.2-3b-shape", "layers": layers, "layers_full": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
             "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
             "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "global_batch": batch, "seq_len": CONTEXT, "context_start": start_ctx + args.warmup,
-            "context_end": start_ctx + args.warmup + args.steps, "prefill_tokens": PREFILL_TOKENS,
+            "context_end": start_ctx + args.warmup + blocks * args.steps,
+            "timed_blocks": blocks, "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "single-gpu", "l2": "inputs larger than L2 (6.4 GB of weights per step)",
             "peaks": source,
         },
+        "block_ms_per_step": [round(t, 4) for t, _ in timed],
         "e2e": {"value": batch / e2e_s, "unit": "tokens/s", "ms_per_step": e2e_s * 1e3,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "timed_blocks": blocks,
+                "steps_per_block": e2e_steps},
         "gpu_launches": launches,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
@@ -276,7 +367,11 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=0,
                         help="fewer layers than the configuration's 28 (both numbers are reported)")
+    parser.add_argument("--blocks", type=int, default=BLOCKS,
+                        help="timed blocks of --steps steps; the median block is reported")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--skip-workloads", action="store_true",
+                        help="leave out the 1B and 8B workload points")
     parser.add_argument("--no-graphs", action="store_true",
                         help="launch decode kernels one by one (for profilers)")
     args = parser.parse_args()

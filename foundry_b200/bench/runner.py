@@ -20,6 +20,7 @@ import torch
 from ..engine.context import SequenceStep
 from ..kernels import ops
 from ..sampling import SamplingParams
+from .costs import decode_step_bytes, load_peaks, roofline, step_flops
 from .rng import SplitMix64, token_rows
 from .stats import summarize
 
@@ -92,7 +93,7 @@ def _one_run(engine, cfg: BenchConfig, depth_ids, prompt_ids, start_ids) -> Dict
     return sample
 
 
-def run_bench(engine, cfg: BenchConfig) -> Dict:
+def run_bench(engine, cfg: BenchConfig, peaks: Optional[Dict] = None) -> Dict:
     if cfg.prompt_tokens == 0 and cfg.new_tokens == 0:
         raise ValueError("nothing to measure: prompt_tokens and new_tokens are both 0")
     vocab = engine.spec.vocab_size
@@ -135,9 +136,27 @@ def run_bench(engine, cfg: BenchConfig) -> Dict:
         }
         if cfg.profile == "kernels":
             profile_metrics["decode_gpu_busy_ns"] = js([p["gpu_busy_ns"] for p in decode_profiles])
-    # what a decode step has to read, and the share of the memory's rate it reached
-    step_bytes = engine.model.weight_bytes_read_per_step() + engine.cache.bytes_per_token() * \
-        cfg.batch_size * (cfg.depth + cfg.prompt_tokens + cfg.decode_step_count() / 2.0)
+    # what the steps have to move and to compute, and the share of the hardware's
+    # rates they reached (the mean step of all runs)
+    peaks = peaks or load_peaks()
+    decode_ns = [ns for r in runs for ns in r["decode_step_ns"]]
+    prompt_ns = [r["prompt_step_ns"] for r in runs if r["prompt_step_ns"]]
+    context = [cfg.depth + cfg.prompt_tokens + cfg.decode_step_count() / 2.0] * cfg.batch_size
+    step_bytes = decode_step_bytes(engine, context)
+    decode_model = {"bytes_read": step_bytes, "achieved_gb_per_s": None, "peak_gb_per_s":
+                    peaks["hbm_gbs"], "fraction_of_peak": None, "peaks": peaks["source"]}
+    if decode_ns:
+        line = roofline(step_bytes, summarize(decode_ns).mean * 1e-9, peaks["hbm_gbs"], "GB/s")
+        decode_model.update(achieved_gb_per_s=line["achieved"], fraction_of_peak=line["frac"])
+    prompt_model = None
+    if cfg.prompt_tokens:
+        flops = step_flops(engine.model, [cfg.prompt_tokens] * cfg.batch_size,
+                           [cfg.depth] * cfg.batch_size, wanted_rows=cfg.batch_size)
+        prompt_model = {"flops": flops, "achieved_tflop_per_s": None, "peak_tflop_per_s":
+                        peaks["bf16_tflops"], "fraction_of_peak": None, "peaks": peaks["source"]}
+        if prompt_ns:
+            line = roofline(flops, summarize(prompt_ns).mean * 1e-9, peaks["bf16_tflops"], "TFLOP/s")
+            prompt_model.update(achieved_tflop_per_s=line["achieved"], fraction_of_peak=line["frac"])
     return {
         "config": asdict(cfg),
         "depth_ids": depth_ids, "prompt_ids": prompt_ids, "start_ids": start_ids,
@@ -152,11 +171,8 @@ def run_bench(engine, cfg: BenchConfig) -> Dict:
             "output_tokens_per_s": js(output_rates),
             **profile_metrics,
         },
-        "decode_step_model": {
-            "bytes_read": step_bytes,
-            "achieved_gb_per_s": (step_bytes / (summarize([ns for r in runs for ns in r["decode_step_ns"]]).mean)
-                                  if any(r["decode_step_ns"] for r in runs) else None),
-        },
+        "decode_step_model": decode_model,
+        "prompt_step_model": prompt_model,
         "peak_memory_bytes": torch.cuda.max_memory_allocated(),
         "peak_memory_source": "torch.cuda.max_memory_allocated",
     }

@@ -16,7 +16,6 @@ The key set and the validation order follow the reference
 from __future__ import annotations
 
 import json
-import os
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Tuple
 

@@ -43,6 +43,7 @@ def registered_architectures() -> List[str]:
 
 def resolve_architecture(doc: Mapping[str, Any]) -> Architecture:
     """Pick the architecture a decoded config.json names."""
+    import foundry_b200.models  # noqa: F401  (registers the built-in architectures)
     archs = doc.get("architectures")
     if isinstance(archs, list):
         for name in archs:

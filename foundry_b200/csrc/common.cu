@@ -57,4 +57,4 @@ FB_API const char* fb_last_error() { return g_error; }
 
 // Bumped whenever an exported signature changes; the Python side refuses a
 // library of another version instead of calling it with the wrong arguments.
-FB_API int fb_abi_version() { return 1; }
+FB_API int fb_abi_version() { return 2; }

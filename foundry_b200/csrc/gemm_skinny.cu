@@ -82,6 +82,7 @@ struct RopeWrite {
   int ring_pages;           // pages per sequence of a windowed group, else 0
   int A, Kh, D;             // weight rows are A query, Kh key, Kh value heads of D
   int write_cache;          // 0: keys and values are not computed at all
+  int interleaved;          // rotation pairs are elements (2i, 2i + 1) instead of (i, i + rotary_dim / 2)
 };
 struct NoRope {};
 
@@ -152,7 +153,9 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   if (late_trigger && (int)(blockIdx.x + blockIdx.y * gridDim.x) >= early_from) fb_pdl_launch();
   int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);  // rows past N are discarded
   // rotary epilogue: this CTA's head, and its rows' first elements inside the head
-  int head = 0, e_lo = 0, e_hi = 0;
+  // (accumulator rows p and p + 8 are elements e_lo + p * e_step and e_hi + p * e_step
+  // of the head, a rotation pair with frequency f_lo + p where the CTA rotates)
+  int head = 0, e_lo = 0, e_hi = 0, e_step = 1, f_lo = 0;
   bool rotated = false;
   if constexpr (ROPE) {
     const int per_head = rw.D >> 4, half = rw.rotary_dim >> 1;
@@ -160,10 +163,16 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
     const int c = blockIdx.x - head * per_head;
     if (head >= rw.A && !rw.write_cache) return;  // keys and values are not wanted
     rotated = c < (half >> 3) && head < rw.A + rw.Kh;
-    if (c < (half >> 3)) { e_lo = 8 * c; e_hi = e_lo + half; }
-    else { e_lo = rw.rotary_dim + 16 * (c - (half >> 3)); e_hi = e_lo + 8; }
-    r0 = head * rw.D + e_lo + g;
-    r1 = head * rw.D + e_hi + g;
+    if (c < (half >> 3)) {
+      f_lo = 8 * c;
+      if (rw.interleaved) { e_lo = 16 * c; e_hi = e_lo + 1; e_step = 2; }
+      else { e_lo = 8 * c; e_hi = e_lo + half; }
+    } else {
+      e_lo = rw.rotary_dim + 16 * (c - (half >> 3));
+      e_hi = e_lo + 8;
+    }
+    r0 = head * rw.D + e_lo + g * e_step;
+    r1 = head * rw.D + e_hi + g * e_step;
   }
   // gridDim.y CTAs share a row group's K; each writes its own float32 plane
   const int chunks = (K + CHUNK - 1) / CHUNK;
@@ -359,7 +368,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   float* out_f = reinterpret_cast<float*>(out) + (size_t)blockIdx.y * plane_stride;
   __nv_bfloat16* out_h = reinterpret_cast<__nv_bfloat16*>(out);
   if constexpr (ROPE) {
-    // rows p and p + 8 are elements e_lo + p and e_hi + p of the head
+    // rows p and p + 8 are elements e_lo + p * e_step and e_hi + p * e_step of the head
     for (int idx = threadIdx.x; idx < 8 * T; idx += WARPS * 32) {
       const int p = idx & 7, tok = idx >> 3;
       const int seq = rw.seq_of_token[tok];
@@ -376,7 +385,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
       const int pos = rw.positions[tok];
       if (rotated) {
         float sn, cs;
-        sincosf((float)pos * rw.inv_freq[e_lo + p], &sn, &cs);
+        sincosf((float)pos * rw.inv_freq[f_lo + p], &sn, &cs);
         const float y1 = x1 * cs - x2 * sn;
         x2 = x2 * cs + x1 * sn;
         x1 = y1;
@@ -393,8 +402,8 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
               (long long)(head - rw.A - (key ? 0 : rw.Kh)) * rw.head_stride +
               (long long)(pos % FB_PAGE) * rw.D;
       }
-      dst[e_lo + p] = __float2bfloat16_rn(x1);
-      dst[e_hi + p] = __float2bfloat16_rn(x2);
+      dst[e_lo + p * e_step] = __float2bfloat16_rn(x1);
+      dst[e_hi + p * e_step] = __float2bfloat16_rn(x2);
     }
   } else if constexpr (SINK) {
     // 16 consecutive lanes hold a token's 16 rows of this CTA
@@ -588,7 +597,9 @@ FB_API int fb_gemm_skinny_max_shares() { return FB_SKINNY_MAX_SHARES; }
 // q_out [T, A * D], rotated keys and the values into the cache pages of each
 // token's position (page_table[seq, position / FB_PAGE], modulo ring_pages when
 // that is > 0). Tokens with seq_of_token < 0 are padding and write nothing;
-// with write_cache == 0 only the queries are computed. late_trigger: whether the
+// with write_cache == 0 only the queries are computed. interleaved: the rotation
+// pairs elements (2i, 2i + 1) of the rotary part instead of (i, i + rotary_dim / 2).
+// late_trigger: whether the
 // kernel behind this one (the attention) may have its blocks placed as this
 // one's main loops end. scale_*: as in fb_gemm_skinny.
 FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long long ldw, int T,
@@ -597,7 +608,7 @@ FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long
                                int rotary_dim, void* q_out, long long q_stride, void* k_cache,
                                void* v_cache, long long page_stride, long long head_stride,
                                int ring_pages, int A, int Kh, int D, int write_cache,
-                               const void* next, long long next_bytes, int warps,
+                               int interleaved, const void* next, long long next_bytes, int warps,
                                int late_trigger, const float* scale_ss, int scale_count,
                                int scale_stride, int scale_dim, float scale_eps,
                                cudaStream_t stream) {
@@ -615,6 +626,7 @@ FB_API int fb_gemm_skinny_rope(const void* x, long long ldx, const void* w, long
   rw.k_cache = (__nv_bfloat16*)k_cache; rw.v_cache = (__nv_bfloat16*)v_cache;
   rw.page_stride = page_stride; rw.head_stride = head_stride; rw.ring_pages = ring_pages;
   rw.A = A; rw.Kh = Kh; rw.D = D; rw.write_cache = write_cache;
+  rw.interleaved = interleaved ? 1 : 0;
   const RowScale scale{scale_ss, scale_count, scale_stride,
                        scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps};
   return launch_skinny(x, ldx, w, ldw, q_out, q_stride, 0, T, (A + 2 * Kh) * D, K, 2, next,

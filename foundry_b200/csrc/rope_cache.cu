@@ -5,7 +5,9 @@
 //   angle[p, i] = p * inv_freq[i], the position taken as a 32-bit float and the
 //   product rounded once to 32 bits (src/models/llama/rotary_emb.rs:113-133);
 //   rotate_half(x) = cat(-x[D/2:], x[:D/2]); x' = x*cos + rotate_half(x)*sin,
-//   so element i pairs with i + D/2 (rotary_emb.rs:62-85);
+//   so element i pairs with i + D/2 (rotary_emb.rs:62-85); the pairing is a
+//   parameter: `interleaved` turns elements (2i, 2i + 1) by frequency i instead,
+//   the other convention in use for this encoding;
 //   cache write K[slot, :, p, :] = k', V[...] = v (src/nn/kv_cache.rs:73-74).
 // The reference rounds cos and sin to 16 bits in a table; here they are
 // computed in 32-bit from the angle, in the kernel.
@@ -30,7 +32,7 @@ __global__ void rope_kv_write_kernel(const TS* src, long long src_stride, int pl
                                      const float* __restrict__ inv_freq, int rotary_dim,
                                      T* __restrict__ k_cache, T* __restrict__ v_cache,
                                      long long page_stride, long long head_stride, int ring_pages,
-                                     int A, int Kh, int D, int write_cache) {
+                                     int A, int Kh, int D, int write_cache, int interleaved) {
   fb_pdl_launch();
   fb_pdl_wait();
   __shared__ float s_cos[128], s_sin[128];  // rotary_dim / 2 <= 128 (head sizes up to 256)
@@ -88,17 +90,19 @@ __global__ void rope_kv_write_kernel(const TS* src, long long src_stride, int pl
     if (idx < n_rot) {
       const int h = idx / half, i = idx - h * half;
       const float s = s_sin[i], c = s_cos[i];
+      // the pair that frequency i turns: (i, i + half), or (2i, 2i + 1) when interleaved
+      const int e1 = interleaved ? 2 * i : i, e2 = interleaved ? 2 * i + 1 : i + half;
       float x1, x2;
-      load2(h * D + i, h * D + i + half, x1, x2);
+      load2(h * D + e1, h * D + e2, x1, x2);
       const float y1 = x1 * c - x2 * s;
       const float y2 = x2 * c + x1 * s;
       if (h < A) {
-        qrow[h * D + i] = fb_from_float<T>(y1);
-        qrow[h * D + i + half] = fb_from_float<T>(y2);
+        qrow[h * D + e1] = fb_from_float<T>(y1);
+        qrow[h * D + e2] = fb_from_float<T>(y2);
       } else {
         T* dst = k_cache + cache_row + (long long)(h - A) * head_stride;
-        dst[i] = fb_from_float<T>(y1);
-        dst[i + half] = fb_from_float<T>(y2);
+        dst[e1] = fb_from_float<T>(y1);
+        dst[e2] = fb_from_float<T>(y2);
       }
     } else if (idx < n_rot + n_val) {
       const int j = idx - n_rot;
@@ -195,13 +199,14 @@ __global__ void rope_kv_write_bf16_kernel(__nv_bfloat16* __restrict__ qkv, long 
 }
 
 // src_dtype / planes: see the kernel. dtype is the element type of q_out and the cache.
+// interleaved: 0 pairs element i with i + rotary_dim / 2, 1 pairs 2i with 2i + 1.
 FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride, int planes,
                             long long plane_stride, void* q_out, int dtype, long long q_stride,
                             const int* positions, const int* seq_of_token, const int* page_table,
                             int max_pages, const float* inv_freq, int rotary_dim, void* k_cache,
                             void* v_cache, long long page_stride, long long head_stride,
                             int ring_pages, int T, int A, int Kh, int D, int write_cache,
-                            cudaStream_t stream) {
+                            int interleaved, cudaStream_t stream) {
   FB_REQUIRE(T >= 0 && A > 0 && Kh > 0 && D > 0, "rope_kv_write: bad sizes T=%d A=%d Kh=%d D=%d",
              T, A, Kh, D);
   FB_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 2 == 0,
@@ -223,7 +228,7 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   int per_token = T >= 256 ? 1 : (work + 255) / 256;
   if (per_token > 16) per_token = 16;
   dim3 grid(T, per_token);
-  if (dtype == FB_BF16 && src_dtype == FB_BF16 && planes == 1 && src == q_out &&
+  if (!interleaved && dtype == FB_BF16 && src_dtype == FB_BF16 && planes == 1 && src == q_out &&
       rotary_dim == D && D % 16 == 0 && src_stride % 8 == 0 && ((uintptr_t)src % 16) == 0 &&
       page_stride % 8 == 0 && head_stride % 8 == 0 && ((uintptr_t)k_cache % 16) == 0 &&
       ((uintptr_t)v_cache % 16) == 0) {
@@ -240,7 +245,7 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   fb_launch(rope_kv_write_kernel<TS, TT>, dim3(grid), dim3(128), 0, stream,                                        \
       (const TS*)src, src_stride, planes, plane_stride, (TT*)q_out, q_stride, positions,        \
       seq_of_token, page_table, max_pages, inv_freq, rotary_dim, (TT*)k_cache, (TT*)v_cache,    \
-      page_stride, head_stride, ring_pages, A, Kh, D, write_cache)
+      page_stride, head_stride, ring_pages, A, Kh, D, write_cache, interleaved ? 1 : 0)
   if (dtype == FB_F32) {
     FB_ROPE_LAUNCH(float, float);
   } else if (dtype == FB_BF16 && src_dtype == FB_BF16) {

@@ -80,11 +80,18 @@ class Engine:
                     max_tokens: int = 8192, max_slots: int = 256, std: float = 0.02,
                     norm_std: float = 0.0) -> "Engine":
         """Random weights made on the device (no folder): for measurements at
-        sizes whose files would take long to write."""
+        sizes whose files would take long to write. `config` is a decoded
+        config.json document, or a typed configuration that can write one
+        (`to_json`); the architecture is the one the document names."""
+        from collections.abc import Mapping
         from ..config.registry import resolve_architecture
         from ..weights.random_init import random_tensors
         import foundry_b200.models  # noqa: F401
-        arch = resolve_architecture(config.to_json())
+        if isinstance(config, Mapping):
+            arch = resolve_architecture(config)
+            config = arch.parse_config(config)
+        else:
+            arch = resolve_architecture(config.to_json())
         engine = cls(arch.build_spec(config), config, dtype, device, max_tokens, max_slots)
         expected = engine.model.expected_tensors()
         store = torch.bfloat16 if engine.dtype == torch.bfloat16 else torch.float32

@@ -25,7 +25,7 @@ from typing import List, Optional
 
 CSRC = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "csrc"))
 LIB_NAME = "libfoundry_b200.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

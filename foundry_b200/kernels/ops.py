@@ -33,7 +33,7 @@ _SIGNATURES = {
     "fb_cast": [c_void_p, c_int, c_void_p, c_int, c_ll, c_void_p],
     "fb_rope_kv_write": [c_void_p, c_int, c_ll, c_int, c_ll, c_void_p, c_int, c_ll, c_void_p,
                          c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_ll,
-                         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "fb_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int,
                      c_int, c_void_p],
     "fb_attention_simt": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p,
@@ -55,8 +55,8 @@ _SIGNATURES = {
                            c_ll, c_int, c_int, c_void_p],
     "fb_gemm_skinny_rope": [c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_int, c_void_p, c_ll, c_void_p, c_void_p,
-                            c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int,
-                            c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+                            c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll,
+                            c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "fb_attention_prefill": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                              c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
@@ -389,9 +389,11 @@ def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor,
                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                   num_heads: int, num_kv_heads: int, head_dim: int, ring_pages: int = 0,
                   write_cache: bool = True, q_out: Optional[torch.Tensor] = None,
-                  dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                  dtype: Optional[torch.dtype] = None, pairing: str = "half") -> torch.Tensor:
     """Rotate the query heads of the fused projection output; rotate the key
-    heads into the cache pages and copy the value heads there. `qkv` is a
+    heads into the cache pages and copy the value heads there. `pairing`:
+    frequency i turns elements (i, i + rotary_dim / 2) ("half") or (2i, 2i + 1)
+    ("interleaved") of the rotary part. `qkv` is a
     tensor (queries are then rotated in place unless `q_out` is given) or
     split-K `Planes`, which are summed on the way (`q_out` of `dtype` is made).
     `k_cache`/`v_cache` are one cache entry's views [pages, kv_heads, PAGE,
@@ -428,8 +430,19 @@ def rope_kv_write(qkv, positions: torch.Tensor, seq_of_token: torch.Tensor,
           _dev(seq_of_token, "seq_of_token", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1],
           _dev(inv_freq, "inv_freq", torch.float32), rotary_dim, kp, vp, page_stride, head_stride,
-          ring_pages, T, num_heads, num_kv_heads, head_dim, 1 if write_cache else 0, _stream())
+          ring_pages, T, num_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
+          _pairing_code(pairing), _stream())
     return q_out
+
+
+PAIRINGS = {"half": 0, "interleaved": 1}
+
+
+def _pairing_code(pairing: str) -> int:
+    try:
+        return PAIRINGS[pairing]
+    except KeyError:
+        raise KernelError(f"rotation pairing {pairing!r}: choose one of {sorted(PAIRINGS)}") from None
 
 
 def _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, dtype) -> None:
@@ -460,7 +473,19 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
     return out
 
 
-SM_COUNT = 148  # B200: the grid sizes below aim at one CTA per SM
+_SM_OF_DEVICE = {}
+
+
+def sm_count() -> int:
+    """SMs of the current device (asked once per device): the plans below size
+    their grids to cover the SMs once."""
+    device = torch.cuda.current_device()
+    count = _SM_OF_DEVICE.get(device)
+    if count is None:
+        count = _SM_OF_DEVICE[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return count
+
+
 # many token rows: one CTA per SM walks the tiles, two accumulators in tensor memory
 PERSISTENT = _os.environ.get("FOUNDRY_B200_PERSISTENT", "1") != "0"
 # two SMs on one 256-row tile (tcgen05 cta_group::2) for more than 128 token rows
@@ -487,8 +512,8 @@ def _pair_scratch(device):
             raise KernelError("the paired product's workspace must be made before a stream "
                               "capture: run the step once before capturing it")
         got = _PAIR_SCRATCH[key] = (
-            torch.empty((SM_COUNT // 2) * 256 * 256, dtype=torch.float32, device=device),
-            torch.zeros((SM_COUNT // 2) * 8, dtype=torch.int32, device=device))
+            torch.empty((sm_count() // 2) * 256 * 256, dtype=torch.float32, device=device),
+            torch.zeros((sm_count() // 2) * 8, dtype=torch.int32, device=device))
     return got
 
 
@@ -599,7 +624,8 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
                      rotary_dim: int, k_cache: Optional[torch.Tensor],
                      v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int,
                      head_dim: int, ring_pages: int = 0, write_cache: bool = True,
-                     then_reads: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     then_reads: Optional[torch.Tensor] = None,
+                     pairing: str = "half") -> torch.Tensor:
     """The fused q/k/v projection of up to 16 tokens, rotated and stored by the
     product's epilogue: returns the rotated queries [T, heads * head_dim]; the
     rotated keys and the values go into the cache pages (`rope_kv_write` has
@@ -631,7 +657,7 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
           _dev(page_table, "page_table", torch.int32), page_table.shape[1],
           _dev(inv_freq, "inv_freq", torch.float32) if rotary_dim else 0, rotary_dim,
           q_out.data_ptr(), q_out.stride(0), kp, vp, page_stride, head_stride, ring_pages,
-          num_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
+          num_heads, num_kv_heads, head_dim, 1 if write_cache else 0, _pairing_code(pairing),
           *_prefetch_range(then_reads), skinny_plan(w.shape[0], K, False)[1],
           1 if page_table.shape[1] <= ROPE_TRIGGER_PAGES else 0, *scale, _stream(),
           tag=("m{} k{} n{}", T, K, w.shape[0]))
@@ -655,8 +681,8 @@ def skinny_plan(N: int, K: int, planes_ok: bool):
     if override:
         return override if planes_ok else (1, override[1])
     groups = (N + 15) // 16
-    if planes_ok and groups < SM_COUNT:
-        return max(1, min(SM_COUNT // groups, (K + 63) // 64 // 8)), 0
+    if planes_ok and groups < sm_count():
+        return max(1, min(sm_count() // groups, (K + 63) // 64 // 8)), 0
     return 1, 0
 
 
@@ -768,10 +794,10 @@ def _one_tile_plan(M: int, N: int, K: int):
     30, q/k/v 23 against 25; the gate/up product has too many tiles for it)."""
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     kblocks = (K + 63) // 64
-    splits = max(1, min(kblocks // 4, SM_COUNT // tiles))
+    splits = max(1, min(kblocks // 4, sm_count() // tiles))
     per = (kblocks + splits - 1) // splits
     splits = (kblocks + per - 1) // per  # no empty share
-    return splits, tiles * splits <= SM_COUNT and per <= 64
+    return splits, tiles * splits <= sm_count() and per <= 64
 
 
 def prompt_tile_width(M: int, N: int) -> int:
@@ -785,7 +811,7 @@ def prompt_tile_width(M: int, N: int) -> int:
     tiles_a = (M + 127) // 128
     best, best_cost = 256, None
     for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
-        rounds = (tiles_a * ((N + bn - 1) // bn) + SM_COUNT - 1) // SM_COUNT
+        rounds = (tiles_a * ((N + bn - 1) // bn) + sm_count() - 1) // sm_count()
         cost = rounds * (bn + 8)  # + a fixed cost per tile
         if best_cost is None or cost < best_cost:
             best, best_cost = bn, cost
@@ -801,7 +827,7 @@ def prompt_plan(M: int, N: int):
     hardly depends on the width between 176 and 256)."""
     if PAIRED and PERSISTENT and N >= 128:
         blocks = (M + 255) // 256
-        pairs = SM_COUNT // 2
+        pairs = sm_count() // 2
         best, best_rounds = 256, None
         for bn in (256, 240, 224, 208, 192, 176, 160, 144, 128):
             rounds = (blocks * ((N + bn - 1) // bn) + pairs - 1) // pairs
@@ -967,7 +993,7 @@ def decode_plan(pairs: int, pages: int):
     are one cluster; a long context with few pairs takes several clusters, whose
     results meet in the workspace (a warp walks a page in 0.6 us whatever else
     runs, so a range's length is what a short batch waits for)."""
-    room = 2 * SM_COUNT // max(pairs, 1)
+    room = 2 * sm_count() // max(pairs, 1)
     if room >= 16 and pages >= 160:
         # clusters of 8 while a CTA keeps 4 pages or more; the second merge costs
         # 3 to 4 us, which pays from about 10 K tokens on (batch 1 at 16 K tokens:

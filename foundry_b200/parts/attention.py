@@ -47,6 +47,7 @@ class GQAAttention(Part):
         self.qkv = Linear(hidden_size, [("q_proj", self.q_size), ("k_proj", self.kv_size),
                                         ("v_proj", self.kv_size)], dtype=dtype, device=device)
         self.o = Linear(self.q_size, [("o_proj", hidden_size)], dtype=dtype, device=device)
+        self.pairing = "half"
         if position_encoding is None:
             self.rotary_dim = 0
             self.inv_freq = torch.zeros(0, dtype=torch.float32, device=device)
@@ -54,6 +55,7 @@ class GQAAttention(Part):
         else:
             enc = POSITION_ENCODINGS.build(position_encoding, dtype=dtype, device=device)
             self.rotary_dim, self.inv_freq, factor = enc.rotary_dim, enc.inv_freq, enc.attention_factor
+            self.pairing = getattr(enc, "pairing", "half")
         self.scale = factor / math.sqrt(head_dim)
 
     # ----------------------------------------------------------------- setup
@@ -87,7 +89,8 @@ class GQAAttention(Part):
             q = ops.gemm_skinny_rope(x, self.qkv.weight, ctx.positions, ctx.seq_of_token, table,
                                      self.inv_freq, self.rotary_dim, cache.k, cache.v,
                                      self.num_heads, self.num_kv_heads, self.head_dim,
-                                     ring_pages=cache.group.ring_pages, write_cache=cache.writes)
+                                     ring_pages=cache.group.ring_pages, write_cache=cache.writes,
+                                     pairing=self.pairing)
         else:
             x = ops.plain(x)
             qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
@@ -95,7 +98,7 @@ class GQAAttention(Part):
                                   self.rotary_dim, cache.k, cache.v, self.num_heads,
                                   self.num_kv_heads, self.head_dim,
                                   ring_pages=cache.group.ring_pages, write_cache=cache.writes,
-                                  dtype=x.dtype)
+                                  dtype=x.dtype, pairing=self.pairing)
         attn = torch.empty((x.shape[0], self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(ctx, q, attn, table, cache.k, cache.v, self.num_heads, self.num_kv_heads,
                       self.head_dim, self.scale, window=cache.group.window,

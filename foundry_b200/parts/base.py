@@ -15,7 +15,8 @@ Part (all kinds)
 Norm
     add_norm(resid, delta, out)    resid += delta (float32, in place); out = norm(resid)
 PositionEncoding
-    inv_freq: float32 [rotary_dim / 2] on the device; rotary_dim; attention_factor
+    inv_freq: float32 [rotary_dim / 2] on the device; rotary_dim; attention_factor;
+    optionally pairing = "half" (default) | "interleaved"
 Mixer
     cache_request() -> KVRequest | StateRequest | None
     forward(ctx, x, cache_view) -> y      x, y: [tokens, hidden] in the activation dtype

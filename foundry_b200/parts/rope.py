@@ -1,8 +1,10 @@
 """Rotary position encodings: the frequency vector is the part.
 
 The rotation itself runs inside the mixer's kernel, which takes the inverse
-frequencies, the rotary width and the pairing (element i with i + width/2) as
-parameters; a variant of the encoding is another frequency vector.
+frequencies, the rotary width and the pairing as parameters (`pairing = "half"`:
+frequency i turns elements i and i + width/2, the reference's; "interleaved":
+elements 2i and 2i + 1); a variant of the encoding is another frequency vector
+and, if it pairs otherwise, another `pairing` attribute.
 
 inv_freq[j] = 1 / theta^(2j / D), j = 0 .. D/2, in 32-bit
 (src/models/llama/rotary_emb.rs:135-160). The "llama3" scaling
@@ -49,6 +51,7 @@ def llama3_inv_freq(head_dim: int, theta: float, factor: float, low_freq_factor:
 
 class _Rotary(Part):
     attention_factor = 1.0
+    pairing = "half"  # src/models/llama/rotary_emb.rs:76-85 (rotate_half)
 
     def _finish(self, inv_freq: np.ndarray, device: torch.device) -> None:
         self.rotary_dim = 2 * int(inv_freq.shape[0])

@@ -47,9 +47,11 @@ def random_tensors(expected: Mapping[str, "ExpectedTensor"], seed: int, *,
 
 def write_model_folder(directory: str, config, seed: int, *,
                        dtype: torch.dtype = torch.bfloat16, std: float = 0.02,
-                       norm_std: float = 0.1) -> str:
+                       norm_std: float = 0.1, device: str = "cpu") -> str:
     """Write `config.json` and `model.safetensors` for `config`
-    (a typed configuration of a registered architecture) and return the folder."""
+    (a typed configuration of a registered architecture) and return the folder.
+    `device`: where the numbers are drawn (a CUDA device draws billions of them
+    in seconds; its stream differs from the CPU's for the same seed)."""
     from ..config.registry import resolve_architecture
     from ..engine.model import expected_tensors
     import foundry_b200.models  # noqa: F401
@@ -58,7 +60,11 @@ def write_model_folder(directory: str, config, seed: int, *,
     arch = resolve_architecture(doc)
     spec = arch.build_spec(config)
     os.makedirs(directory, exist_ok=True)
-    tensors = random_tensors(expected_tensors(spec), seed, dtype=dtype, std=std, norm_std=norm_std)
+    tensors = {}
+    for name, want in expected_tensors(spec).items():  # one at a time: the draw is freed at once
+        drawn = random_tensors({name: want}, seed, dtype=dtype, std=std, norm_std=norm_std,
+                               device=device)
+        tensors[name] = drawn[name].cpu()
     save_file(tensors, os.path.join(directory, SINGLE_FILE), metadata={"format": "pt"})
     with open(os.path.join(directory, CONFIG_FILE), "w") as handle:
         json.dump(doc, handle, indent=2)

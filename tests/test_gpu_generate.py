@@ -407,6 +407,45 @@ def test_command_line_bench_writes_a_report(tiny_folders, tmp_path):
     assert report["metadata"]["model_parameter_count"] > 0
 
 
+def test_command_line_with_a_named_configuration_and_random_weights(tmp_path):
+    """`--config NAME --random-weights SEED` stands in for a folder in both
+    subcommands; the tokens are those of the same engine built in this process,
+    and the report holds the step's bytes and operations with their fractions."""
+    import foundry_b200 as fb
+    from foundry_b200.bench.presets import preset
+    want = fb.Engine.from_random(preset("tiny-a"), 3, dtype="float32", max_tokens=256,
+                                 max_slots=2).generate([[5, 17, 3], [9]], 5, eos_token_id=[])
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "run", "--config",
+                           "tiny-a", "--random-weights", "3", "--prompt-ids", "5,17,3",
+                           "--prompt-ids", "9", "--max-new-tokens", "5", "--dtype", "float32",
+                           "--ignore-eos", "--max-seq-len", "100"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [json.loads(line) for line in proc.stdout.split()] == want.token_ids
+    for bad in (["--config", "tiny-a"], ["--config", "no-such", "--random-weights", "1"],
+                ["--model", "x", "--config", "tiny-a", "--random-weights", "1"]):
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "run", *bad,
+                               "--prompt-ids", "1", "--max-new-tokens", "1"],
+                              capture_output=True, text=True, timeout=600)
+        assert proc.returncode != 0 and "Traceback" not in proc.stderr, proc.stderr[-500:]
+    peaks = tmp_path / "peaks.json"
+    peaks.write_text(json.dumps({"hbm_gbs": 6000.0, "bf16_tflops": 1500.0}))
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "foundry"), "bench", "--config",
+                           "tiny-b", "--random-weights", "1", "--prompt-tokens", "40",
+                           "--new-tokens", "4", "--runs", "2", "--batch-size", "2", "--context",
+                           "128", "--peaks", str(peaks), "--out", str(tmp_path)],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    report = json.loads((tmp_path / "report.json").read_text())
+    decode, prompt = report["decode_step_model"], report["prompt_step_model"]
+    assert decode["peaks"] == "measured" and decode["peak_gb_per_s"] == 6000.0
+    assert decode["bytes_read"] > 0 and 0 < decode["fraction_of_peak"] < 1
+    assert abs(decode["fraction_of_peak"] - decode["achieved_gb_per_s"] / 6000.0) < 1e-9
+    assert prompt["flops"] > 0 and 0 < prompt["fraction_of_peak"] < 1
+    assert report["metadata"]["model_parameter_count"] == 457824 + 0 or \
+        report["metadata"]["model_parameter_count"] > 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decoding_across_a_page_table_growth(tmp_path, dtype):
     """A sequence that grows from 8 to 9 pages while another stays short: the

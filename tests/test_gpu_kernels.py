@@ -433,12 +433,18 @@ def test_gemm_with_silu_mul_epilogue(ops, M):
 
 
 # ------------------------------------------------------------- rope + cache
-def plain_rope(x, pos, inv_freq, rotary_dim):
-    """x [heads, D] float64; pairs (i, i + rotary_dim/2); angle as a 32-bit product."""
+def plain_rope(x, pos, inv_freq, rotary_dim, pairing="half"):
+    """x [heads, D] float64; frequency i turns the pair (i, i + rotary_dim/2), or
+    (2i, 2i + 1) when interleaved; angle as a 32-bit product."""
     half = rotary_dim // 2
     angle = (np.float32(pos) * inv_freq.astype(np.float32)).astype(np.float64)
     c, s = torch.from_numpy(np.cos(angle)), torch.from_numpy(np.sin(angle))
     y = x.clone()
+    if pairing == "interleaved":
+        a, b = x[:, 0:rotary_dim:2], x[:, 1:rotary_dim:2]
+        y[:, 0:rotary_dim:2] = a * c - b * s
+        y[:, 1:rotary_dim:2] = b * c + a * s
+        return y
     y[:, :half] = x[:, :half] * c - x[:, half:rotary_dim] * s
     y[:, half:rotary_dim] = x[:, half:rotary_dim] * c + x[:, :half] * s
     return y
@@ -447,9 +453,11 @@ def plain_rope(x, pos, inv_freq, rotary_dim):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("A,Kh,D,rot", [(4, 2, 16, 16), (6, 3, 32, 32), (3, 1, 48, 32), (8, 2, 128, 128)])
 @pytest.mark.parametrize("source", ["tensor", "planes"])
-def test_rope_kv_write(ops, dtype, A, Kh, D, rot, source):
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+def test_rope_kv_write(ops, dtype, A, Kh, D, rot, source, pairing):
     """Positions far apart (a 32-bit angle matters at 100k), a padding token,
-    pages scattered; queries in place or from split planes; partial rotary width."""
+    pages scattered; queries in place or from split planes; partial rotary
+    width; both ways of pairing the rotated elements."""
     positions = [0, 1, 63, 64, 100000, 7]
     seqs = [0, 0, 1, 1, 2, -1]
     T = len(positions)
@@ -466,17 +474,18 @@ def test_rope_kv_write(ops, dtype, A, Kh, D, rot, source):
             torch.tensor(seqs, dtype=torch.int32, device=DEV), table.to(DEV),
             torch.from_numpy(inv_freq).to(DEV), rot, k_cache, v_cache, A, Kh, D)
     if source == "tensor":
-        q = ops.rope_kv_write(qkv, *args)
+        q = ops.rope_kv_write(qkv, *args, pairing=pairing)
         assert q.data_ptr() == qkv.data_ptr()  # rotated in place
     else:
         parts = torch.stack([qkv.float() * 0.25, qkv.float() * 0.5, qkv.float() * 0.25])
-        q = ops.rope_kv_write(ops.Planes(parts.contiguous()), *args, dtype=dtype)
+        q = ops.rope_kv_write(ops.Planes(parts.contiguous()), *args, dtype=dtype, pairing=pairing)
     a, r = (1e-6, 1e-6) if dtype == torch.float32 else (2e-2, 8e-3)
     for t in range(T - 1):
         row = ref[t].view(A + 2 * Kh, D)
-        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot), a, r)
+        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot, pairing), a, r)
         page = int(table[seqs[t], positions[t] // 64])
-        close(k_cache[page, :, positions[t] % 64], plain_rope(row[A:A + Kh], positions[t], inv_freq, rot), a, r)
+        close(k_cache[page, :, positions[t] % 64],
+              plain_rope(row[A:A + Kh], positions[t], inv_freq, rot, pairing), a, r)
         close(v_cache[page, :, positions[t] % 64], row[A + Kh:], a, r)
     # nothing else was written, and the padding token wrote nothing
     written = {(int(table[seqs[t], positions[t] // 64]), positions[t] % 64) for t in range(T - 1)}
@@ -489,10 +498,11 @@ def test_rope_kv_write(ops, dtype, A, Kh, D, rot, source):
 @pytest.mark.parametrize("A,Kh,D,rot", [(4, 2, 16, 16), (6, 3, 32, 32), (3, 1, 48, 32), (8, 2, 128, 128),
                                         (2, 2, 64, 0), (5, 1, 80, 48)])
 @pytest.mark.parametrize("T", [6, 13])
-def test_gemm_skinny_rope(ops, A, Kh, D, rot, T):
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+def test_gemm_skinny_rope(ops, A, Kh, D, rot, T, pairing):
     """Projection, rotation and cache write in one kernel against the plain
     formulas: far positions, a padding token, scattered pages, partial and
-    absent rotation; without cache writes only the queries appear."""
+    absent rotation, both pairings; without cache writes only the queries appear."""
     K = 264
     positions = ([0, 1, 63, 64, 100000, 7] + list(range(200, 200 + T)))[:T]
     seqs = ([0, 0, 1, 1, 2, -1] + [0] * T)[:T]
@@ -510,17 +520,18 @@ def test_gemm_skinny_rope(ops, A, Kh, D, rot, T):
             torch.tensor(seqs, dtype=torch.int32, device=DEV), table.to(DEV),
             torch.from_numpy(inv_freq).to(DEV), rot)
     q = ops.gemm_skinny_rope(x, w, *args, k_cache, v_cache, A, Kh, D,
-                             then_reads=rnd(8, 64, dtype=torch.bfloat16))
+                             then_reads=rnd(8, 64, dtype=torch.bfloat16), pairing=pairing)
     a, r = 2e-2, 8e-3
     written = set()
     for t in range(T):
         if seqs[t] < 0:
             continue
         row = ref[t].view(A + 2 * Kh, D)
-        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot), a, r)
+        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot, pairing), a, r)
         page = int(table[seqs[t], positions[t] // 64])
         written.add((page, positions[t] % 64))
-        close(k_cache[page, :, positions[t] % 64], plain_rope(row[A:A + Kh], positions[t], inv_freq, rot), a, r)
+        close(k_cache[page, :, positions[t] % 64],
+              plain_rope(row[A:A + Kh], positions[t], inv_freq, rot, pairing), a, r)
         close(v_cache[page, :, positions[t] % 64], row[A + Kh:], a, r)
     mask = torch.ones(n_pages, 64, dtype=torch.bool)
     for p, rr in written:
@@ -531,14 +542,15 @@ def test_gemm_skinny_rope(ops, A, Kh, D, rot, T):
     qkv = torch.empty(T, width, dtype=torch.bfloat16, device=DEV)
     ops.gemm_skinny(x, w, qkv)
     k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
-    q2 = ops.rope_kv_write(qkv, *args, k2, v2, A, Kh, D)
+    q2 = ops.rope_kv_write(qkv, *args, k2, v2, A, Kh, D, pairing=pairing)
     live = [t for t in range(T) if seqs[t] >= 0]
     close(q[live], q2[live].double(), a, r)
     close(k_cache, k2.double(), a, r)
     close(v_cache, v2.double(), a, r)
     # reading another layer's cache: no key or value is computed or stored
     k_cache.zero_(), v_cache.zero_()
-    q3 = ops.gemm_skinny_rope(x, w, *args, k_cache, v_cache, A, Kh, D, write_cache=False)
+    q3 = ops.gemm_skinny_rope(x, w, *args, k_cache, v_cache, A, Kh, D, write_cache=False,
+                              pairing=pairing)
     assert torch.equal(q3[live], q[live])
     assert float(k_cache.float().abs().max()) == 0.0 and float(v_cache.float().abs().max()) == 0.0
 

@@ -53,8 +53,9 @@ def test_rms_norm_part(dtype):
     want = plain.rms_norm(r0.double().cpu() + delta.double().cpu(), w.double(), 1e-6)
     assert out.dtype == dtype
     assert_close(out, want, dtype)
-    assert part.expected_tensors("x.norm") == {"x.norm.weight": part.expected_tensors("x.norm")["x.norm.weight"]}
-    assert part.expected_tensors("x.norm")["x.norm.weight"].shape == (96,)
+    listed = part.expected_tensors("x.norm")
+    assert list(listed) == ["x.norm.weight"] and tuple(listed["x.norm.weight"].shape) == (96,)
+    assert not listed["x.norm.weight"].integer
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -314,9 +315,11 @@ def test_a_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype)
         MIXERS.unregister("toy_running_mean")
 
 
-def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_path):
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
+def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_path, pairing):
     """Two more parts defined here and plugged in by name: a position encoding
-    that rotates only half of each head with linearly scaled frequencies, and a
+    that rotates only half of each head with linearly scaled frequencies (its
+    pairs being elements i and i + width/2, or 2i and 2i + 1), and a
     feed-forward with a squared-ReLU and two token-routed experts (routing in
     32-bit). The attention part, the block and the engine are used unchanged."""
     import foundry_b200 as fb
@@ -330,7 +333,8 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
     class HalfRotary(Part):
         attention_factor = 1.0
 
-        def __init__(self, head_dim, theta, scale, *, dtype=None, device=None):
+        def __init__(self, head_dim, theta, scale, pairing, *, dtype=None, device=None):
+            self.pairing = pairing
             self.rotary_dim = head_dim // 2
             inv = (1.0 / (theta ** (np.arange(0, self.rotary_dim, 2, dtype=np.float32) / self.rotary_dim))
                    / np.float32(scale)).astype(np.float32)
@@ -371,28 +375,35 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
     register_position_encoding("toy_half_rotary", HalfRotary, replace=True)
     register_feed_forward("toy_routed_relu2", RoutedRelu2, replace=True)
 
-    def build_spec(config):
+    def build_spec(config, routed=True, name="Toy2ForCausalLM"):
         from foundry_b200.models.llama import build_llama_spec
         base = build_llama_spec(config)
         layers = []
         for layer in base.layers:
             mixer = PartSpec("gqa_attention", {**layer.mixer.params, "position_encoding": PartSpec(
-                "toy_half_rotary", {"head_dim": config.head_dim, "theta": 10000.0, "scale": 2.0})})
+                "toy_half_rotary", {"head_dim": config.head_dim, "theta": 10000.0, "scale": 2.0,
+                                    "pairing": pairing})})
             ff = PartSpec("toy_routed_relu2", {"hidden_size": config.hidden_size,
                                                "intermediate_size": 48, "experts": 2})
-            layers.append(replace(layer, mixer=mixer, feed_forward=ff))
-        return replace(base, architecture="Toy2ForCausalLM", layers=tuple(layers))
+            layers.append(replace(layer, mixer=mixer, feed_forward=ff if routed else layer.feed_forward))
+        return replace(base, architecture=name, layers=tuple(layers))
 
     register_architecture(Architecture("Toy2ForCausalLM", "llama",
                                        lambda d: LlamaConfig.parse({**d, "architectures": ["Toy2ForCausalLM"]}),
                                        build_spec), replace=True)
+    # the same position encoding with the ordinary feed-forward: for the 16-bit run,
+    # in which a routed toy could send a token to the other expert on a near tie
+    register_architecture(Architecture("Toy3ForCausalLM", "llama",
+                                       lambda d: LlamaConfig.parse({**d, "architectures": ["Toy3ForCausalLM"]}),
+                                       lambda c: build_spec(c, routed=False, name="Toy3ForCausalLM")),
+                          replace=True)
     try:
         cfg_doc = {**tiny.CONFIGS["tiny_b"], "architectures": ["Toy2ForCausalLM"], "num_hidden_layers": 2}
         folder = fb.write_model_folder(str(tmp_path / "toy2"), LlamaConfig.parse(cfg_doc), 8, std=0.1)
         cfg, w = plain.read_model(folder)
         assert "model.layers.0.mlp.experts.1.down.weight" in w and "model.layers.0.mlp.router.weight" in w
 
-        def plain_forward(tokens):
+        def plain_forward(tokens, w=w, routed=True):
             S, A, K, D = len(tokens), cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
             x = w["model.embed_tokens.weight"][torch.as_tensor(tokens)]
             rot = D // 2
@@ -400,8 +411,13 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
             ang = (np.arange(S, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float64)
             cos, sin = torch.from_numpy(np.cos(ang)), torch.from_numpy(np.sin(ang))
 
-            def rope(t):  # [S, heads, D]: pairs (i, i + rot/2) inside the first `rot` elements
-                a, b = t[..., :rot // 2], t[..., rot // 2:rot]
+            def rope(t):  # [S, heads, D]: the pairs lie inside the first `rot` elements
+                if pairing == "interleaved":  # (2i, 2i + 1)
+                    a, b = t[..., 0:rot:2], t[..., 1:rot:2]
+                    turned = torch.stack([a * cos[:, None] - b * sin[:, None],
+                                          b * cos[:, None] + a * sin[:, None]], -1)
+                    return torch.cat([turned.reshape(*t.shape[:-1], rot), t[..., rot:]], -1)
+                a, b = t[..., :rot // 2], t[..., rot // 2:rot]  # (i, i + rot/2)
                 return torch.cat([a * cos[:, None] - b * sin[:, None], b * cos[:, None] + a * sin[:, None],
                                   t[..., rot:]], -1)
             for i in range(2):
@@ -417,6 +433,9 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
                     att[:, a_] = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, a_ // (A // K)]
                 h = x + att.reshape(S, A * D) @ w[f"{p}.self_attn.o_proj.weight"].T
                 n = plain.rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+                if not routed:
+                    x = h + plain.mlp(n, w, f"{p}.mlp")
+                    continue
                 gate = torch.softmax(n @ w[f"{p}.mlp.router.weight"].T, -1)
                 choice = gate.argmax(-1)
                 y = torch.zeros_like(h)
@@ -437,8 +456,24 @@ def test_a_toy_position_encoding_and_feed_forward_are_registered_and_run(tmp_pat
         engine.close_sequence(slot)
         got = np.concatenate(got)
         tiny.assert_logits_close(got, want, "float32", "toy position encoding and feed-forward")
+
+        # the position encoding alone in both dtypes: in 16 bits single-token steps
+        # rotate in the q/k/v product's epilogue, prompts in the rotary kernel
+        doc3 = {**cfg_doc, "architectures": ["Toy3ForCausalLM"]}
+        folder3 = fb.write_model_folder(str(tmp_path / "toy3"), LlamaConfig.parse(doc3), 9, std=0.1)
+        _, w3 = plain.read_model(folder3)
+        want = plain_forward(tokens, w3, routed=False)
+        for dtype in ("float32", "bfloat16"):
+            engine = fb.Engine.from_folder(folder3, dtype=dtype, max_tokens=512, max_slots=2)
+            slot = engine.open_sequence()
+            got = [engine.step([SequenceStep(slot, tokens[:30], list(range(30)))]).cpu().numpy()]
+            for t in tokens[30:]:
+                got.append(engine.step([SequenceStep(slot, [t], [0])]).cpu().numpy())
+            engine.close_sequence(slot)
+            tiny.assert_logits_close(np.concatenate(got), want, dtype, f"toy position encoding, {dtype}")
     finally:
         unregister_architecture("Toy2ForCausalLM")
+        unregister_architecture("Toy3ForCausalLM")
         POSITION_ENCODINGS.unregister("toy_half_rotary")
         FEED_FORWARDS.unregister("toy_routed_relu2")
 

@@ -51,20 +51,31 @@ CONFIG = CONFIGS["3b"]
 LENGTHS = (3, 500, 2048)
 
 
-class PlainWide:
-    """The plain model for wide matrices: layer weights in float64, the
-    embedding and the head as stored (rows widened when used)."""
+class WidenedOnUse(dict):
+    """Tensors kept as stored and widened to float64 each time one is read."""
 
-    def __init__(self, folder):
+    def __getitem__(self, name):
+        return dict.__getitem__(self, name).to(torch.float64)
+
+
+class PlainWide:
+    """The plain model for wide matrices: layer weights in float64 (or, with
+    `widen_on_use`, as stored and widened when a layer reads them: 28 layers in
+    float64 would be 22 GB), the embedding and the head as stored (rows widened
+    when used)."""
+
+    def __init__(self, folder, widen_on_use=False):
         from safetensors import safe_open
         with open(os.path.join(folder, "config.json")) as handle:
             self.cfg = json.load(handle)
-        self.w, self.table = {}, {}
+        self.w, self.table = (WidenedOnUse() if widen_on_use else {}), {}
         with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as handle:
             for name in handle.keys():
                 t = handle.get_tensor(name)
                 if name in ("model.embed_tokens.weight", "lm_head.weight"):
                     self.table[name] = t
+                elif widen_on_use:
+                    dict.__setitem__(self.w, name, t)
                 else:
                     self.w[name] = t.to(torch.float64)
 
@@ -97,12 +108,13 @@ def assert_close(got, want, dtype, what):
         assert err <= 5e-2 * scale, f"{what}: max |diff| {err:.3e} (scale {scale:.2f})"
 
 
-def write_folder(tmp_path_factory, name):
+def write_folder(tmp_path_factory, name, layers=2):
     import foundry_b200 as fb
     from foundry_b200.config import LlamaConfig
     folder = str(tmp_path_factory.mktemp(f"wide_{name}") / "model")
-    # N(0, 0.02) weights, norm weights 1 + N(0, 0.1)
-    fb.write_model_folder(folder, LlamaConfig.parse(CONFIGS[name]), 2, std=0.02)
+    # N(0, 0.02) weights, norm weights 1 + N(0, 0.1); drawn on the GPU (seconds, not minutes)
+    fb.write_model_folder(folder, LlamaConfig.parse({**CONFIGS[name], "num_hidden_layers": layers}),
+                          2, std=0.02, device="cuda:0")
     return folder
 
 
@@ -144,6 +156,36 @@ def test_benchmark_widths_on_an_unequal_batch(wide, dtype):
         assert_close(np.concatenate(pieces[i]), w, dtype, f"sequence {i}")
     from foundry_b200.kernels import ops
     assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.slow
+def test_the_benchmark_model_at_its_full_depth_in_float32(tmp_path_factory):
+    """All 28 layers of the 3B configuration in 32 bits on the unequal batch's
+    two short sequences (3 and 500 tokens in one step): what 28 layers make of
+    the float32 kernels' rounding, against the float64 plain model. The 2,048-
+    token sequence stays with the two-layer test: 28 layers of it in float64 on
+    the CPU would take many minutes."""
+    import foundry_b200 as fb
+    from foundry_b200.engine import SequenceStep
+    folder = write_folder(tmp_path_factory, "3b", layers=28)
+    model = PlainWide(folder, widen_on_use=True)
+    rng = np.random.default_rng(13)
+    seqs = [[int(t) for t in rng.integers(0, 128000, size=n)] for n in (3, 500)]
+    rows = [[0, 2], [0, 250, 499]]
+    want = [model.logits_at(s, r) for s, r in zip(seqs, rows)]
+    del model
+    engine = fb.Engine.from_folder(folder, dtype="float32", max_tokens=1024, max_slots=2)
+    slots = [engine.open_sequence() for _ in seqs]
+    got = engine.step([SequenceStep(s, q, r) for s, q, r in zip(slots, seqs, rows)]).cpu().numpy()
+    at = 0
+    for i, w in enumerate(want):
+        g = got[at:at + len(rows[i])]
+        at += len(rows[i])
+        scale = max(1.0, float(np.abs(w).max()))
+        err = float(np.abs(g - w).max())
+        assert np.isfinite(g).all()
+        # 28 layers of float32 sums against float64: within 1e-3 of the logit scale
+        assert err <= 1e-3 * scale, f"sequence {i}: max |diff| {err:.3e} (scale {scale:.2f})"
 
 
 # ------------------------------------------------------------------ 1B and 8B

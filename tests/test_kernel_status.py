@@ -57,3 +57,22 @@ def test_a_recorded_failure_raises_once_and_names_the_place(record, kernel, role
 def test_a_library_without_the_record_is_tolerated(monkeypatch):
     monkeypatch.setattr(ops, "_MIRROR", [None])
     ops.raise_on_device_failure()
+
+
+def test_every_ctypes_signature_matches_its_c_declaration():
+    """The launchers are called through ctypes with hand-written argument
+    lists; a list that is one entry short shows only as a wrong value on the
+    GPU. Compared here with the `extern "C"` declarations in the sources."""
+    import glob
+    import os
+    import re
+    from foundry_b200.kernels import library
+    source = "".join(open(path).read() for path in glob.glob(os.path.join(library.CSRC, "*.cu")))
+    for name, signature in ops._SIGNATURES.items():
+        found = re.search(r"FB_API int " + name + r"\((.*?)\)\s*\{", source, re.S)
+        assert found, f"{name} has no declaration"
+        declared = [a for a in found.group(1).split(",") if a.strip()]
+        assert len(declared) == len(signature), f"{name}: {len(declared)} declared, {len(signature)} listed"
+        for arg, ctype in zip(declared, signature):
+            pointer = "*" in arg or "cudaStream_t" in arg
+            assert pointer == (ctype is ctypes.c_void_p), f"{name}: {arg.strip()} listed as {ctype}"
