@@ -134,7 +134,9 @@ __global__ void rope_kv_write_kernel(const TS* src, long long src_stride, int pl
 // The common prompt case, vectorised: bfloat16 source rotated in place, no
 // planes, rotary width == head size, head size a multiple of 16. A thread moves
 // 8 consecutive elements of the first half and the 8 they pair with (16 bytes
-// each way), or 16 consecutive value elements.
+// each way), or, with interleaved pairs, 8 consecutive elements that are four
+// pairs of their own; or 8 consecutive value elements.
+template <bool INTERLEAVED>
 __global__ void rope_kv_write_bf16_kernel(__nv_bfloat16* __restrict__ qkv, long long stride,
                                           const int* __restrict__ positions,
                                           const int* __restrict__ seq_of_token,
@@ -163,7 +165,7 @@ __global__ void rope_kv_write_bf16_kernel(__nv_bfloat16* __restrict__ qkv, long 
     const int page = page_table[(size_t)seq * max_pages + lp];
     cache_row = (long long)page * page_stride + (long long)(pos % FB_PAGE) * D;
   }
-  const int groups = half / 8;                       // 8-element groups per half head
+  const int groups = (INTERLEAVED ? D : half) / 8;   // work items per rotated head
   const int n_rot = (A + (write_cache ? Kh : 0)) * groups;
   const int n_val = write_cache ? Kh * (D / 8) : 0;  // 8-element groups of the value heads
   for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n_rot + n_val;
@@ -171,24 +173,38 @@ __global__ void rope_kv_write_bf16_kernel(__nv_bfloat16* __restrict__ qkv, long 
     if (idx < n_rot) {
       const int h = idx / groups, i0 = (idx - h * groups) * 8;
       __nv_bfloat16* x = row + (size_t)h * D + i0;
-      const uint4 lo = *reinterpret_cast<const uint4*>(x);
-      const uint4 hi = *reinterpret_cast<const uint4*>(x + half);
-      const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
-      uint4 olo, ohi;
-      __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&olo);
-      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ohi);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 a = __bfloat1622float2(l2[e]), b = __bfloat1622float2(h2[e]);
-        const float c0 = s_cos[i0 + 2 * e], s0 = s_sin[i0 + 2 * e];
-        const float c1 = s_cos[i0 + 2 * e + 1], s1 = s_sin[i0 + 2 * e + 1];
-        ol[e] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
-        oh[e] = __floats2bfloat162_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
-      }
       __nv_bfloat16* dst = h < A ? x : k_cache + cache_row + (long long)(h - A) * head_stride + i0;
-      *reinterpret_cast<uint4*>(dst) = olo;
-      *reinterpret_cast<uint4*>(dst + half) = ohi;
+      if constexpr (INTERLEAVED) {
+        const uint4 in = *reinterpret_cast<const uint4*>(x);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&in);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {  // elements i0 + 2e, i0 + 2e + 1 turn by frequency i0 / 2 + e
+          const float2 a = __bfloat1622float2(p2[e]);
+          const float c = s_cos[(i0 >> 1) + e], sn = s_sin[(i0 >> 1) + e];
+          o2[e] = __floats2bfloat162_rn(a.x * c - a.y * sn, a.y * c + a.x * sn);
+        }
+        *reinterpret_cast<uint4*>(dst) = o;
+      } else {
+        const uint4 lo = *reinterpret_cast<const uint4*>(x);
+        const uint4 hi = *reinterpret_cast<const uint4*>(x + half);
+        const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+        uint4 olo, ohi;
+        __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&olo);
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ohi);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 a = __bfloat1622float2(l2[e]), b = __bfloat1622float2(h2[e]);
+          const float c0 = s_cos[i0 + 2 * e], s0 = s_sin[i0 + 2 * e];
+          const float c1 = s_cos[i0 + 2 * e + 1], s1 = s_sin[i0 + 2 * e + 1];
+          ol[e] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+          oh[e] = __floats2bfloat162_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+        }
+        *reinterpret_cast<uint4*>(dst) = olo;
+        *reinterpret_cast<uint4*>(dst + half) = ohi;
+      }
     } else {
       const int j = idx - n_rot;
       const int h = j / (D / 8), i0 = (j - h * (D / 8)) * 8;
@@ -228,17 +244,23 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
   int per_token = T >= 256 ? 1 : (work + 255) / 256;
   if (per_token > 16) per_token = 16;
   dim3 grid(T, per_token);
-  if (!interleaved && dtype == FB_BF16 && src_dtype == FB_BF16 && planes == 1 && src == q_out &&
+  if (dtype == FB_BF16 && src_dtype == FB_BF16 && planes == 1 && src == q_out &&
       rotary_dim == D && D % 16 == 0 && src_stride % 8 == 0 && ((uintptr_t)src % 16) == 0 &&
       page_stride % 8 == 0 && head_stride % 8 == 0 && ((uintptr_t)k_cache % 16) == 0 &&
       ((uintptr_t)v_cache % 16) == 0) {
     const int vec_work = (A + 2 * Kh) * D / 16;
     int blocks_y = T >= 256 ? 1 : (vec_work + 127) / 128;
     if (blocks_y > 16) blocks_y = 16;
-    fb_launch(rope_kv_write_bf16_kernel, dim3(T, blocks_y), dim3(128), 0, stream,
-              (__nv_bfloat16*)q_out, src_stride, positions, seq_of_token, page_table, max_pages,
-              inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_stride,
-              head_stride, ring_pages, A, Kh, D, write_cache);
+    if (interleaved)
+      fb_launch(rope_kv_write_bf16_kernel<true>, dim3(T, blocks_y), dim3(128), 0, stream,
+                (__nv_bfloat16*)q_out, src_stride, positions, seq_of_token, page_table, max_pages,
+                inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_stride,
+                head_stride, ring_pages, A, Kh, D, write_cache);
+    else
+      fb_launch(rope_kv_write_bf16_kernel<false>, dim3(T, blocks_y), dim3(128), 0, stream,
+                (__nv_bfloat16*)q_out, src_stride, positions, seq_of_token, page_table, max_pages,
+                inv_freq, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_stride,
+                head_stride, ring_pages, A, Kh, D, write_cache);
     return fb_check_launch("rope_kv_write");
   }
 #define FB_ROPE_LAUNCH(TS, TT)                                                                  \

@@ -46,6 +46,9 @@ class StepContext:
     is_decode: bool  # every sequence brings exactly one token
     max_q_len: int
     max_kv_len: int
+    # Whether the sequences' lengths differ much (a hint for kernels that share work
+    # among sequences; in a replayed step it is fixed when the step is captured)
+    unequal_lengths: bool = False
     # In a replayed prompt step: an upper bound of the number of query blocks of
     # 64 rows over all sequences (the attention's grid), else None
     query_blocks_bound: Optional[int] = None
@@ -141,6 +144,15 @@ def plan_step(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: i
     return StepPlan(token_ids, positions, seq_of, want_rows, slots, cu, kv_lens, tables)
 
 
+def lengths_are_unequal(lengths: Sequence[int]) -> bool:
+    """Whether the longest of several sequences is well beyond their mean (a
+    quarter more, and at least four pages)."""
+    if len(lengths) < 2:
+        return False
+    mean = sum(lengths) / len(lengths)
+    return max(lengths) > 1.25 * mean and max(lengths) - mean >= 256
+
+
 def build_context(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_size: int,
                   device: torch.device, max_positions: Optional[int] = None,
                   plan: Optional[StepPlan] = None) -> StepContext:
@@ -164,7 +176,8 @@ def build_context(cache: SequenceCache, steps: Sequence[SequenceStep], vocab_siz
         token_ids=part[0], positions=part[1], seq_of_token=part[2], want_rows=part[3],
         slots=part[4], cu_tokens=part[5], kv_lens=part[6],
         slots_host=plan.slots, cu_tokens_host=plan.cu, kv_lens_host=plan.kv_lens,
-        is_decode=all(n == 1 for n in lens), max_q_len=max(lens), max_kv_len=max(plan.kv_lens))
+        is_decode=all(n == 1 for n in lens), max_q_len=max(lens), max_kv_len=max(plan.kv_lens),
+        unequal_lengths=lengths_are_unequal(plan.kv_lens))
     for i, (group, width, _) in enumerate(plan.tables):
         ctx._tables[id(group)] = part[7 + i].view(n_seqs, width)
     return ctx

@@ -25,7 +25,7 @@ import torch
 from ..cache.pages import PAGE
 from ..kernels import ops
 from ..sampling.params import SamplingParams
-from .context import StepContext
+from .context import StepContext, lengths_are_unequal
 from .staging import StagingRing
 
 
@@ -40,8 +40,8 @@ class DecodeRunner:
     """Fixed buffers and the captured graph for `bucket` rows and page tables
     `width` pages wide."""
 
-    def __init__(self, engine, bucket: int, width: int):
-        self.engine, self.bucket, self.width = engine, bucket, width
+    def __init__(self, engine, bucket: int, width: int, unequal: bool = False):
+        self.engine, self.bucket, self.width, self.unequal = engine, bucket, width, unequal
         dev = engine.device
         groups = engine.cache.groups
         b = bucket
@@ -65,7 +65,7 @@ class DecodeRunner:
             n_tokens=b, n_seqs=b, n_want=b, token_ids=part[0], positions=part[1],
             seq_of_token=part[2], want_rows=part[3], slots=part[4], cu_tokens=part[5],
             kv_lens=part[6], slots_host=None, cu_tokens_host=None, kv_lens_host=None,
-            is_decode=True, max_q_len=1, max_kv_len=width * PAGE)
+            is_decode=True, max_q_len=1, max_kv_len=width * PAGE, unequal_lengths=unequal)
         for i, group in enumerate(groups):
             self.ctx._tables[id(group)] = part[7 + i].view(b, width)
         self.h_tables = [self.h[7 + i].reshape(b, width) for i in range(len(groups))]
@@ -164,13 +164,15 @@ class DecodeSession:
         for g in cache.groups:
             need = max(need, max(len(g.pages.pages(s)) for s in self.slots))
         bucket = bucket_of(n)
+        unequal = lengths_are_unequal(lengths)
         runner = self.runner
-        if runner is None or runner.bucket != bucket or runner.width < need:
-            width = 8
+        if runner is None or runner.bucket != bucket or runner.width < need \
+                or runner.unequal != unequal:
+            width = 8 if runner is None or runner.bucket != bucket else runner.width
             while width < need:
                 width *= 2
             previous = runner
-            runner = self.runner = engine.decode_runner(bucket, width)
+            runner = self.runner = engine.decode_runner(bucket, width, unequal)
             if previous is not None and previous is not runner and previous.bucket == bucket:
                 # tokens that stay on the device (`step`) move on with the session
                 runner.ctx.token_ids.copy_(previous.next_tokens)

@@ -224,10 +224,13 @@ class Engine:
                        counts: Optional[Sequence[int]] = None) -> "DecodeSession":
         return DecodeSession(self, slots, sampling, keys, counts)
 
-    def decode_runner(self, bucket: int, width: int) -> "DecodeRunner":
-        key = (bucket, width)
+    def decode_runner(self, bucket: int, width: int, unequal: bool = False) -> "DecodeRunner":
+        """The captured step for `bucket` rows, page tables `width` pages wide, and
+        sequences of about equal or of unequal lengths (the attention shares its
+        work differently)."""
+        key = (bucket, width) if not unequal else (bucket, width, "unequal")
         if key not in self._runners:
-            self._runners[key] = DecodeRunner(self, bucket, width)
+            self._runners[key] = DecodeRunner(self, bucket, width, unequal)
         return self._runners[key]
 
     def graph_pool(self):

@@ -66,8 +66,14 @@ _SIGNATURES = {
     "fb_attention_tc_status": [c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
-                            c_void_p],
+                            c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_ll, c_void_p],
+    "fb_gemm_rows": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int,
+                     c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
+                     c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                     c_void_p, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int,
+                     c_int, c_int, c_int, c_void_p],
+    "fb_gemm_rows_status": [c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
 }
@@ -607,6 +613,15 @@ def gemm_skinny_residual(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink,
     return NormPending(sink, values, shares)
 
 
+def qkv_rows_rope_fusable(x, w: torch.Tensor, rotary_dim: int, head_dim: int,
+                          k_cache: Optional[torch.Tensor], pairing: str) -> bool:
+    """Whether `gemm_rows_rope` takes this projection: 17 to 256 bfloat16 token
+    rows and a rotation of adjacent features."""
+    return (FUSE_QKV_ROPE and rows_usable(x, w) and pairing == "interleaved"
+            and rotary_dim % 4 == 0 and head_dim % 4 == 0
+            and (k_cache is None or k_cache.dtype == torch.bfloat16))
+
+
 def qkv_rope_fusable(x: torch.Tensor, w: torch.Tensor, rotary_dim: int, head_dim: int,
                      k_cache: Optional[torch.Tensor]) -> bool:
     """Whether `gemm_skinny_rope` takes this projection: bfloat16, few token
@@ -664,6 +679,113 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
     return q_out
 
 
+# ----------------------------------------------- 17 .. 256 token rows (tcgen05)
+# Token rows up to which the product that shares a weight tile's K among the CTAs
+# of a cluster and sums in the kernel is taken (csrc/gemm_rows_tcgen05.cu);
+# ROWS_MAX = 0 keeps the one-tile product with float32 planes. Measured on the 3B
+# decode step (8 layers, both forms in one run): 32 rows 0.840 -> 0.752 ms, 64 rows
+# at 512 tokens of context 1.066 -> 0.986, at 3,072 tokens 1.800 -> 1.753; at 128
+# rows the one-tile product stays ahead (1.348 against 1.413: this kernel then has
+# three shared-memory stages). The kernel itself takes up to 256 rows.
+# ROWS_SPLITS overrides the CTAs per weight tile (0: the launcher's choice).
+ROWS_SPLITS = int(_os.environ.get("FOUNDRY_B200_ROWS_SPLITS", "0"))
+ROWS_MAX = int(_os.environ.get("FOUNDRY_B200_ROWS_MAX", "64"))
+def rows_usable(x, w) -> bool:
+    """Whether the few-rows tcgen05 product takes this projection."""
+    values = x.values if isinstance(x, RowScaled) else x
+    return (SKINNY_ROWS < values.shape[0] <= ROWS_MAX and values.dtype == torch.bfloat16
+            and w.dtype == torch.bfloat16 and _tc_usable(values, w, values))
+
+
+def _gemm_rows(x, w, epilogue: int, out=None, sink: Optional[ResidualSink] = None,
+               sink_out=None, rope=None) -> None:
+    """The launcher's face; `x` may be a `RowScaled`."""
+    scale = _NO_SCALE
+    if isinstance(x, RowScaled):
+        scale, x = x.scale_args(), x.values
+    M, K = x.shape
+    N = w.shape[0]
+    out_args = (0, 0, 0)
+    if out is not None:
+        out_args = (_dev(out, "out", contiguous=False), _rows(out, "out"),
+                    1 if out.dtype == torch.float32 else 0)
+    sink_args = (0, 0, 0, 0, 0, 0, 0)
+    if sink is not None:
+        values, shares = sink_out
+        sink_args = (_dev(sink.resid, "resid", torch.float32, contiguous=False),
+                     _rows(sink.resid, "resid"), _dev(sink.gamma, "gamma", torch.float32),
+                     values.data_ptr(), values.stride(0), shares.data_ptr(), shares.stride(0))
+    rope_args = (0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0)
+    if rope is not None:
+        rope_args = rope
+    _call("fb_gemm_rows", _dev(x, "x", torch.bfloat16, contiguous=False), _rows(x, "x"), M,
+          _dev(w, "w", torch.bfloat16, contiguous=False), _rows(w, "w"), N, K, *out_args, epilogue,
+          *scale, *sink_args, *rope_args, ROWS_SPLITS, _stream(),
+          tag=("m{} k{} n{} e{}", M, K, N, epilogue))
+
+
+def gemm_rows(x, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+              out_dtype: Optional[torch.dtype] = None, silu_mul: bool = False) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T for 17 to 256 token rows (any count up to
+    256 works); with `silu_mul` the weight rows are (gate, up) pairs and out is
+    [M, N / 2]. `x` may be a `RowScaled`."""
+    M, N = x.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype or torch.bfloat16,
+                          device=w.device)
+    if tuple(out.shape) != (M, N // 2 if silu_mul else N) or out.stride(1) != 1:
+        raise KernelError(f"gemm_rows: out is {tuple(out.shape)} for x {tuple(x.shape)}, w {tuple(w.shape)}")
+    _gemm_rows(x, w, 1 if silu_mul else 0, out=out)
+    return out
+
+
+def gemm_rows_residual(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink) -> NormPending:
+    """The same product in front of a norm: sink.resid += x w^T in the epilogue,
+    which also leaves resid * gamma in bfloat16 and each weight tile's share of
+    the rows' sums of squares (see `gemm_skinny_residual`)."""
+    M, N = x.shape[0], w.shape[0]
+    if tuple(sink.resid.shape) != (M, N) or tuple(sink.gamma.shape) != (N,):
+        raise KernelError(f"gemm_rows_residual: resid {tuple(sink.resid.shape)}, gamma "
+                          f"{tuple(sink.gamma.shape)} for a product of {(M, N)}")
+    values = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+    shares = torch.empty(((N + 127) // 128, (M + 31) // 32 * 32), dtype=torch.float32, device=w.device)
+    _gemm_rows(x, w, 2, sink=sink, sink_out=(values, shares))
+    return NormPending(sink, values, shares)
+
+
+def gemm_rows_rope(x, w: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   page_table: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int,
+                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                   num_heads: int, num_kv_heads: int, head_dim: int, ring_pages: int = 0,
+                   write_cache: bool = True) -> torch.Tensor:
+    """The fused q/k/v projection of 17 to 256 tokens, rotated and stored by the
+    product's epilogue (see `gemm_skinny_rope`). The rotation pairs ADJACENT
+    features (frequency i turns features 2i and 2i + 1 of a head): the caller's
+    weight rows are laid out for the "interleaved" pairing."""
+    M, K = x.shape
+    rows = (num_heads + 2 * num_kv_heads) * head_dim
+    if w.shape != (rows, K):
+        raise KernelError(f"gemm_rows_rope: w is {tuple(w.shape)} for {num_heads}+2x{num_kv_heads} "
+                          f"heads of {head_dim} and K={K}")
+    if positions.numel() != M or seq_of_token.numel() != M or inv_freq.numel() * 2 != rotary_dim:
+        raise KernelError("gemm_rows_rope: positions / seq_of_token / inv_freq do not fit")
+    q_out = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=w.device)
+    kp = vp = page_stride = head_stride = 0
+    if write_cache:
+        _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
+        page_stride, head_stride = k_cache.stride(0), k_cache.stride(1)
+        kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
+    else:
+        w = w[:num_heads * head_dim]  # keys and values are another layer's: not computed
+    rope = (_dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+            _dev(page_table, "page_table", torch.int32), page_table.shape[1],
+            _dev(inv_freq, "inv_freq", torch.float32) if rotary_dim else 0, rotary_dim,
+            q_out.data_ptr(), q_out.stride(0), kp, vp, page_stride, head_stride, ring_pages,
+            num_heads, num_kv_heads, head_dim)
+    _gemm_rows(x, w, 3, rope=rope)
+    return q_out
+
+
 FUSE_QKV_ROPE = _os.environ.get("FOUNDRY_B200_FUSE_QKV_ROPE", "1") != "0"
 ROPE_TRIGGER_PAGES = 64  # page-table width up to which the q/k/v product triggers its successor
 # the projections around a norm take the norm over (see `ResidualSink`, `RowScaled`)
@@ -713,9 +835,11 @@ if _os.environ.get("FOUNDRY_B200_PDL", "1") == "0":
     set_dependent_launch(False)
 
 
-_STATUS_READERS = ("fb_gemm_tc_status", "fb_gemm_tc_pair_status", "fb_attention_tc_status")
+_STATUS_READERS = ("fb_gemm_tc_status", "fb_gemm_tc_pair_status", "fb_attention_tc_status",
+                   "fb_gemm_rows_status")
 # kernel codes of the host-visible failure record (FB_STATUS_KERNEL in csrc)
-_STATUS_KERNELS = {1: "tcgen05 product", 2: "paired tcgen05 product", 3: "tcgen05 prompt attention"}
+_STATUS_KERNELS = {1: "tcgen05 product", 2: "paired tcgen05 product", 3: "tcgen05 prompt attention",
+                   4: "tcgen05 product for few token rows"}
 _STATUS_ROLES = {1: "tile loads", 2: "matrix instructions", 3: "epilogue",
                  20: "shared-memory alignment"}
 _MIRROR = []
@@ -866,7 +990,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         return out if out is not None else torch.empty((0, N), dtype=out_dtype, device=x.device)
     values = x.values if isinstance(x, RowScaled) else x
     usable = _tc_usable(values, w, out if out is not None else values)
-    if not (usable and M <= SKINNY_ROWS):
+    if not (usable and (M <= SKINNY_ROWS or rows_usable(x, w))):
         x = plain(x)
     if not usable:
         if out is None:
@@ -885,6 +1009,12 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_skinny(x, w, out, then_reads=then_reads, warps=warps)
+    if rows_usable(x, w) and (out is None or out.stride(1) == 1):
+        if (residual is not None and NORM_FUSION and out is None
+                and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
+            return gemm_rows_residual(x, w, residual)
+        return gemm_rows(x, w, out, out_dtype)
+    x = plain(x)
     splits, fits = _one_tile_plan(M, N, K)
     if M > 128 and not (fits and M <= ONE_TILE_ROWS):
         if out is None:
@@ -928,6 +1058,8 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
     if M == 0:
         return out
     usable = _tc_usable(x.values if isinstance(x, RowScaled) else x, w_pairs, out)
+    if usable and rows_usable(x, w_pairs):
+        return gemm_rows(x, w_pairs, out, silu_mul=True)
     if not (usable and M <= SKINNY_ROWS):
         x = plain(x)
     if not usable:
@@ -963,8 +1095,16 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
         return attention_simt(q, out, ctx.positions, ctx.seq_of_token, page_table, k_cache,
                               v_cache, num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
     if ctx.is_decode:
-        splits, stages = decode_plan(ctx.n_seqs * num_kv_heads,
-                                     (ctx.max_kv_len + PAGE - 1) // PAGE)
+        pairs, pages = ctx.n_seqs * num_kv_heads, (ctx.max_kv_len + PAGE - 1) // PAGE
+        splits, stages = decode_plan(pairs, pages)
+        if getattr(ctx, "unequal_lengths", False) and splits < UNEQUAL_SPLITS and pages >= 16:
+            # many sequences of unequal lengths: ranges by the longest one's pages, merged
+            # through the workspace (CTAs with empty ranges leave at once instead of
+            # waiting in a cluster)
+            return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache,
+                                    v_cache, num_heads, num_kv_heads, head_dim, scale,
+                                    min(UNEQUAL_SPLITS, pages // 4), stages, then_reads=then_reads,
+                                    cluster=1, balanced=True)
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                                 num_heads, num_kv_heads, head_dim, scale, splits, stages,
                                 then_reads=then_reads)
@@ -1002,6 +1142,9 @@ def decode_plan(pairs: int, pages: int):
     return max(1, min(DECODE_CLUSTER_MAX, pages, room)), 3
 
 
+# Ranges per sequence when a step says that its sequences' lengths are unequal
+# (`ctx.unequal_lengths`) and the plan above would give each sequence fewer.
+UNEQUAL_SPLITS = int(_os.environ.get("FOUNDRY_B200_UNEQUAL_SPLITS", "4"))
 TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prompt-attention kernel
 PREFILL_TC = _os.environ.get("FOUNDRY_B200_PREFILL_TC", "1") != "0"
 
@@ -1048,14 +1191,16 @@ DECODE_CLUSTER = _os.environ.get("FOUNDRY_B200_DECODE_CLUSTER", "1") != "0"
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
                      num_kv_heads, head_dim, scale, splits, stages: int = 3,
                      then_reads: Optional[torch.Tensor] = None,
-                     cluster: Optional[int] = None) -> torch.Tensor:
+                     cluster: Optional[int] = None, balanced: bool = False) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
     over `splits` CTAs per (sequence, kv head). `cluster` of them (by default as
     many as divide `splits`, up to 8) form a thread-block cluster and merge their
     partial results through each other's shared memory; the clusters' results
     (or, without clusters, every CTA's) go to a workspace, and the CTA that
     finishes a pair last merges them. `then_reads`: weights to ask into L2 for
-    the kernel that follows (see `gemm_skinny`)."""
+    the kernel that follows (see `gemm_skinny`). `balanced`: a range is 1/splits
+    of the LONGEST sequence's pages for every sequence, so that in a batch of
+    unequal lengths no CTA walks a long sequence alone."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
     n = kv_lens.numel()
     if cluster is None:
@@ -1074,7 +1219,7 @@ def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, n
           _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
-          head_dim, float(scale), splits, stages, cluster,
+          head_dim, float(scale), splits, stages, cluster, 1 if balanced else 0,
           0 if ws_o is None else ws_o.data_ptr(), 0 if ws_ml is None else ws_ml.data_ptr(),
           0 if counters is None else counters.data_ptr(), *_prefetch_range(then_reads),
           _stream())

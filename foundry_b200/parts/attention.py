@@ -65,6 +65,28 @@ class GQAAttention(Part):
     def load(self, prefix: str, fetch: Fetch) -> None:
         self.qkv.load(prefix, fetch)
         self.o.load(prefix, fetch)
+        if self.rotary_dim and self.pairing == "half":
+            # Store the rows of every query and key head so that the two features a
+            # frequency turns are neighbours (2i, 2i + 1) instead of half a rotary width
+            # apart: the product kernels then rotate in their epilogue by exchanging
+            # values between neighbouring lanes. Scores are dot products over a head's
+            # features, so any order serves as long as queries and keys share it; values
+            # and the output projection are untouched.
+            self.qkv.weight = self.qkv.weight.index_select(0, self._neighbour_order()).contiguous()
+            self.pairing = "interleaved"
+
+    def _neighbour_order(self) -> torch.Tensor:
+        """Row order of the fused q/k/v matrix with rotation partners adjacent."""
+        half = self.rotary_dim // 2
+        within = []
+        for i in range(half):
+            within += [i, i + half]
+        within += list(range(self.rotary_dim, self.head_dim))
+        order = []
+        for head in range(self.num_heads + self.num_kv_heads):
+            order += [head * self.head_dim + e for e in within]
+        order += list(range(len(order), len(order) + self.kv_size))  # the value heads as they are
+        return torch.tensor(order, dtype=torch.long, device=self.qkv.weight.device)
 
     def cache_request(self) -> KVRequest:
         return KVRequest(self.num_kv_heads, self.head_dim, self.window)
@@ -91,6 +113,13 @@ class GQAAttention(Part):
                                      self.num_heads, self.num_kv_heads, self.head_dim,
                                      ring_pages=cache.group.ring_pages, write_cache=cache.writes,
                                      pairing=self.pairing)
+        elif ops.qkv_rows_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k,
+                                       self.pairing):
+            # up to a few hundred tokens: the same on the tcgen05 product
+            q = ops.gemm_rows_rope(x, self.qkv.weight, ctx.positions, ctx.seq_of_token, table,
+                                   self.inv_freq, self.rotary_dim, cache.k, cache.v,
+                                   self.num_heads, self.num_kv_heads, self.head_dim,
+                                   ring_pages=cache.group.ring_pages, write_cache=cache.writes)
         else:
             x = ops.plain(x)
             qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes

@@ -470,6 +470,7 @@ def test_decoding_across_a_page_table_growth(tmp_path, dtype):
                            SequenceStep(b, [short_tokens[20 + i]], [0])]).cpu().numpy()
         rows_a.append(out[0:1])
         rows_b.append(out[1:2])
-    assert engine._session.runner.width == 16 and (2, 8) in engine._runners  # both graphs were used
+    assert engine._session.runner.width == 16 and \
+        any(key[:2] == (2, 8) for key in engine._runners)  # both graphs were used
     tiny.assert_logits_close(np.concatenate(rows_a), want_long[500:540], dtype, "long sequence")
     tiny.assert_logits_close(np.concatenate(rows_b), want_short[20:60], dtype, "short sequence")

@@ -309,6 +309,22 @@ def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, sp
         assert float(out[-1].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("lens_kv,A,Kh,D", [([1000, 3, 64, 300, 129, 1], 12, 4, 128),
+                                            ([70, 2000, 500, 65], 16, 2, 64), ([33, 190, 900], 6, 3, 32)])
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_attention_single_tokens_of_unequal_lengths(ops, lens_kv, A, Kh, D, splits):
+    """Ranges cut by the longest sequence's pages: short sequences leave most
+    CTAs without a range, the longest uses them all; merged through the workspace."""
+    lens_q = [1] * len(lens_kv)
+    case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, torch.bfloat16, seed=6, sharp=True)
+    for _ in range(2):  # the counters are back at zero for the second call
+        out = torch.full_like(case["q"], 5.0)
+        ops.attention_decode(case["q"], out, case["cu"], case["kv"], case["table"], case["k"],
+                             case["v"], A, Kh, D, 1.0 / math.sqrt(D), splits, 3, cluster=1,
+                             balanced=True)
+        close(out, want, 3e-2, 1e-2)
+
+
 def test_attention_picks_out_a_far_key(ops):
     """One key among a thousand matches the query; the output must be that
     key's value, whichever kernel runs."""
@@ -810,4 +826,153 @@ def test_gemm_tensor_core_persistent(ops, bn, rows_a, rows_b, K):
     ops.gemm_tc(a, b, act, rows_b // 2, 1, bn, epilogue=1, persistent=True, constant_operand=2)
     g, u = want[:, 0::2], want[:, 1::2]
     close(act, g / (1 + torch.exp(-g)) * u, 3e-2, 1e-2)
+    assert ops.gemm_tc_status() == 0
+
+
+# ------------------------------------------- 17 .. 256 token rows on tcgen05
+ROWS_SHAPES = [(3072, 3072), (5120, 3072), (384, 8192), (200, 264), (130, 64), (2048, 2048),
+               (16384, 2048), (1000, 4104)]
+
+
+@pytest.mark.parametrize("M", [17, 32, 33, 64, 100, 128, 129, 256])
+@pytest.mark.parametrize("N,K", ROWS_SHAPES)
+def test_gemm_rows(ops, M, N, K):
+    """The few-rows product: weight tiles whose K several CTAs of a cluster share
+    (summed in the kernel), tiles one CTA computes alone, ragged N and K; twice
+    in a row, bit for bit the same both times; float32 and bfloat16 outputs."""
+    x = rnd(M, K, dtype=torch.bfloat16, scale=0.5)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=1)
+    want = x.double() @ w.double().T
+    first = ops.gemm_rows(x, w, out_dtype=torch.float32)
+    close(first, want, 2e-3, 1e-4)
+    again = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    ops.gemm_rows(x, w, again)
+    assert torch.equal(first, again)
+    half = torch.full((M, N + 8), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_rows(x, w, half[:, :N])  # rows of a wider tensor
+    close(half[:, :N], want, 3e-2, 1e-2)
+    assert float(half[:, N:].float().min()) == 7.0
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 5, 8])
+def test_gemm_rows_every_cluster_size(ops, monkeypatch, splits):
+    """K shared by 1 to 8 CTAs of a cluster, more tokens than CTAs and fewer."""
+    monkeypatch.setattr(ops, "ROWS_SPLITS", splits)
+    for M, N, K in ((70, 300, 1024), (19, 128, 520), (256, 200, 4096)):
+        x = rnd(M, K, dtype=torch.bfloat16, scale=0.5)
+        w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=1)
+        close(ops.gemm_rows(x, w, out_dtype=torch.float32), x.double() @ w.double().T, 2e-3, 1e-4)
+    assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M", [20, 64, 200])
+def test_gemm_rows_with_silu_mul_epilogue(ops, monkeypatch, M):
+    monkeypatch.setattr(ops, "ROWS_MAX", 256)  # the dispatcher below takes this kernel for all M here
+    K, I = 264, 1000
+    x = rnd(M, K, dtype=torch.bfloat16, scale=0.5)
+    gate, up = rnd(I, K, dtype=torch.bfloat16, scale=0.3, seed=1), rnd(I, K, dtype=torch.bfloat16, scale=0.3, seed=2)
+    pairs = torch.stack([gate, up], 1).reshape(2 * I, K).contiguous()
+    out = torch.full((M, I), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_rows(x, pairs, out, silu_mul=True)
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    close(out, g / (1 + torch.exp(-g)) * u, 3e-2, 1e-2)
+    # the dispatcher takes the same kernel for these row counts
+    out2 = torch.empty_like(out)
+    ops.gemm_bf16_silu_mul(x, pairs, out2)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("M,H,K", [(17, 96, 72), (40, 200, 264), (64, 3072, 520), (130, 2048, 8192)])
+def test_gemm_rows_takes_the_norm_over(ops, monkeypatch, M, H, K):
+    """As test_gemm_skinny_takes_the_norm_over, for 17 to 256 rows: the product in
+    front of a norm adds into the residual rows, leaves resid * gamma and each
+    weight tile's share of the sums of squares; the products behind the norm
+    (plain, SiLU-mul, rotary) apply 1 / sqrt(mean + eps) to their sums."""
+    monkeypatch.setattr(ops, "ROWS_MAX", 256)  # through the dispatcher at every M here
+    eps = 3e-5
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(H, K, dtype=torch.bfloat16, scale=0.2, seed=1)
+    resid0 = rnd(M, H, seed=2) * 3.0
+    resid0[0] *= 40.0  # rows of very different scale
+    gamma = (1.0 + 0.3 * rnd(H, seed=3)).contiguous()
+    resid = resid0.clone()
+    sink = ops.ResidualSink(resid, gamma, eps)
+    pending = ops.gemm_bf16(x, w, residual=sink)
+    assert isinstance(pending, ops.NormPending)
+    want_resid = resid0.double() + x.double() @ w.double().T
+    close(resid, want_resid, 2e-3, 1e-5)
+    # bfloat16 of a float32 sum: half a unit in the last place of the rounded value,
+    # plus what the float32 sum itself is off the float64 one
+    close(pending.values, resid.double() * gamma.double(), 1e-6, 2.0 ** -8)
+    assert pending.shares.shape[0] == (H + 127) // 128
+    close(pending.shares[:, :M].sum(0), (want_resid ** 2).sum(1), 1e-3, 1e-4)
+    scaled = ops.add_rmsnorm(resid, pending, gamma, eps, None)
+    assert isinstance(scaled, ops.RowScaled)
+    normed = want_resid / torch.sqrt((want_resid ** 2).mean(1, keepdim=True) + eps) * gamma.double()
+    close(scaled.materialize(), normed, 2e-2, 8e-3)
+    # a plain product and a SiLU-mul product behind the norm, against the products of
+    # the rounded values the kernels read
+    rstd = 1.0 / torch.sqrt((resid.double() ** 2).mean(1, keepdim=True) + eps)
+    w2 = rnd(264, H, dtype=torch.bfloat16, scale=0.1, seed=5)
+    close(ops.gemm_bf16(scaled, w2, out_dtype=torch.float32),
+          (pending.values.double() @ w2.double().T) * rstd, 2e-3, 1e-4)
+    pairs = rnd(400, H, dtype=torch.bfloat16, scale=0.1, seed=6)
+    hidden = torch.empty(M, 200, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16_silu_mul(scaled, pairs, hidden)
+    gu = (pending.values.double() @ pairs.double().T) * rstd
+    close(hidden, gu[:, 0::2] / (1 + torch.exp(-gu[:, 0::2])) * gu[:, 1::2], 1e-3, 1e-2)
+    # the sink must belong to the norm that takes the result
+    with pytest.raises(ops.KernelError, match="another"):
+        ops.add_rmsnorm(resid0.clone(), pending, gamma, eps, None)
+
+
+@pytest.mark.parametrize("A,Kh,D,rot", [(4, 2, 16, 16), (6, 3, 32, 32), (3, 1, 48, 32), (8, 2, 128, 128),
+                                        (2, 2, 64, 0), (32, 8, 64, 64)])
+@pytest.mark.parametrize("T", [17, 70])
+def test_gemm_rows_rope(ops, A, Kh, D, rot, T):
+    """Projection, rotation of adjacent feature pairs and cache write in the
+    few-rows product's epilogue: far positions, padding tokens, scattered pages,
+    partial and absent rotation, a row-scaled input; without cache writes only
+    the queries are computed. Against the plain formulas and the separate kernels."""
+    K = 264
+    positions = ([0, 1, 63, 64, 100000, 7] + list(range(200, 200 + T)))[:T]
+    seqs = ([0, 0, 1, 1, 2, -1] + [0] * T)[:T]
+    seqs[-1] = -1
+    width = (A + 2 * Kh) * D
+    n_pages = 1600
+    table = torch.zeros(3, 1563, dtype=torch.int32)
+    table[0, 0], table[1, 0], table[1, 1], table[2, 100000 // 64] = 5, 9, 2, 11
+    table[0, 3], table[0, 4] = 17, 23  # positions 200.. of sequence 0
+    inv_freq = (10000.0 ** (-np.arange(0, rot, 2, dtype=np.float32) / max(rot, 1))).astype(np.float32)
+    x, w = rnd(T, K, dtype=torch.bfloat16), rnd(width, K, dtype=torch.bfloat16, scale=0.1, seed=4)
+    ref = (x.double() @ w.double().T).cpu()
+    k_cache = torch.zeros(n_pages, Kh, 64, D, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    args = (torch.tensor(positions, dtype=torch.int32, device=DEV),
+            torch.tensor(seqs, dtype=torch.int32, device=DEV), table.to(DEV),
+            torch.from_numpy(inv_freq).to(DEV), rot)
+    q = ops.gemm_rows_rope(x, w, *args, k_cache, v_cache, A, Kh, D)
+    a, r = 2e-2, 8e-3
+    written = set()
+    for t in range(T):
+        if seqs[t] < 0:
+            continue
+        row = ref[t].view(A + 2 * Kh, D)
+        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot, "interleaved"), a, r)
+        page = int(table[seqs[t], positions[t] // 64])
+        written.add((page, positions[t] % 64))
+        close(k_cache[page, :, positions[t] % 64],
+              plain_rope(row[A:A + Kh], positions[t], inv_freq, rot, "interleaved"), a, r)
+        close(v_cache[page, :, positions[t] % 64], row[A + Kh:], a, r)
+    mask = torch.ones(n_pages, 64, dtype=torch.bool)
+    for p, rr in written:
+        mask[p, rr] = False
+    for cache in (k_cache, v_cache):
+        assert float(cache.float().abs().sum(dim=(1, 3)).cpu()[mask].max()) == 0.0
+    live = [t for t in range(T) if seqs[t] >= 0]
+    # reading another layer's cache: no key or value is computed or stored
+    k_cache.zero_(), v_cache.zero_()
+    q3 = ops.gemm_rows_rope(x, w, *args, k_cache, v_cache, A, Kh, D, write_cache=False)
+    assert torch.equal(q3[live], q[live])
+    assert float(k_cache.float().abs().max()) == 0.0 and float(v_cache.float().abs().max()) == 0.0
     assert ops.gemm_tc_status() == 0

@@ -247,7 +247,7 @@ def test_the_other_benchmark_widths(twin, dtype):
     run([(4 + j, n, [n - 1]) for j, n in enumerate(late)])
     for _ in range(SINGLE_24):
         run([(i, 1, [0]) for i in range(len(seqs))])
-    assert max(b for b, _ in engine._runners) == 32  # 24 rows ran in the 32-row bucket
+    assert max(key[0] for key in engine._runners) == 32  # 24 rows ran in the 32-row bucket
     for i, (rows, logits) in want.items():
         assert_close(np.concatenate(got[i]), logits, dtype, f"{name} sequence {i}")
     assert ops.gemm_tc_status() == 0
