@@ -231,6 +231,38 @@ FB_API int fb_apply_row_scale(const void* values, long long ld, const float* sha
   return fb_check_launch("apply_row_scale");
 }
 
+// Every token's 1 / sqrt(mean square + eps) from the shares of its sum of squares
+// that the product in front of a norm left: out[t] for t < T. For products of many
+// rows, whose epilogues would otherwise add the shares up again for every tile.
+__global__ void row_scales_kernel(const float* shares, int count, int stride, float inv_dim,
+                                  float eps, float* __restrict__ out, int T) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float sum = 0.f;
+  int c = 0;
+  for (; c + 8 <= count; c += 8) {  // eight loads on their way together, added in order
+    float part[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) part[e] = __ldcg(shares + (size_t)(c + e) * stride + t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum += part[e];
+  }
+  for (; c < count; ++c) sum += __ldcg(shares + (size_t)c * stride + t);
+  out[t] = 1.0f / sqrtf(sum * inv_dim + eps);
+}
+
+FB_API int fb_row_scales(const float* shares, int count, int stride, int dim, float eps,
+                         float* out, int T, cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && count > 0 && stride >= T && dim > 0 && eps > 0.f,
+             "row_scales: bad sizes T=%d count=%d stride=%d", T, count, stride);
+  if (T == 0) return 0;
+  fb_launch(row_scales_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, shares, count, stride,
+            1.0f / (float)dim, eps, out, T);
+  return fb_check_launch("row_scales");
+}
+
 // ------------------------------------------------------------- SiLU(g) * u
 // gate_up is [T, 2I]. Plain layout: columns [0, I) hold the gate, [I, 2I) the
 // up projection. Interleaved layout: column 2i holds gate i, column 2i+1 up i

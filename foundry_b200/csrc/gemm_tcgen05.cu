@@ -151,6 +151,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float* out_f = (float*)p.out + (long long)split * p.split_stride;
       __nv_bfloat16* out_h = (__nv_bfloat16*)p.out;
       constexpr int CHUNK = (BN % 32 == 0) ? 32 : 16;
+      const float scale = token_scale(p, i_global);
+      float ss = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN; c += CHUNK) {
         float v[CHUNK];
@@ -173,8 +175,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < CHUNK; ++e) v[e] = 0.f;
         }
-        store_chunk<CHUNK>(p, v, i_global, (long long)tile_b * BN + c, lane, out_f, out_h);
+        ss += finish_chunk<CHUNK>(p, v, scale, i_global, (long long)tile_b * BN + c, lane, out_f, out_h);
       }
+      finish_tile(p, ss, i_global, tile_b);
     }
   }
   // ------------------------------------------------------------------ teardown
@@ -329,6 +332,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
       if (!ok) break;
       tc_fence_after();
       const long long i_global = (long long)ta * BM + quarter * 32 + lane;
+      const float scale = token_scale(p, i_global);
+      float ss = 0.f;
 #pragma unroll 1
       for (int c = 0; c < BN; c += CHUNK) {
         float v[CHUNK];
@@ -347,8 +352,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
           for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
         }
-        store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+        ss += finish_chunk<CHUNK>(p, v, scale, i_global, (long long)tb * BN + c, lane, out_f, out_h);
       }
+      finish_tile(p, ss, i_global, tb);
       // this warp has read its lanes of the accumulator: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -414,6 +420,10 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 // `workspace` of `workspace_bytes` and `counters` (zero between calls, 8 per
 // tile of a round); without them every tile is computed whole. A share keeps at
 // least `share_min_kblocks` K blocks of 64 (0: the default, 32).
+// scale_*: the row scale of an input that is a norm's output without it
+// (scale_ss null: none); epilogue 2: resid / gamma / xg / ss_out as in
+// fb_gemm_skinny_residual, ss_out being [ceil(rows_b / bn), ss_stride]. Both need
+// tokens as the A rows and one split.
 // epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
 // pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
 // dimension must be 1 and then indexes pairs.
@@ -422,7 +432,10 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
                       int out_f32, int bn, int splits, long long split_stride, int epilogue,
                       int constant_operand, int persistent, void* workspace,
                       long long workspace_bytes, int* counters, int counters_len,
-                      int share_min_kblocks, cudaStream_t stream) {
+                      int share_min_kblocks, const float* scale_ss, int scale_count,
+                      int scale_stride, int scale_dim, float scale_eps, float* resid,
+                      long long ldr, const float* gamma, void* xg, long long ldxg, float* ss_out,
+                      int ss_stride, cudaStream_t stream) {
   FB_REQUIRE(rows_a > 0 && rows_b > 0 && K > 0, "gemm_tc: bad sizes %d x %d x %d", rows_a, rows_b, K);
   FB_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0,
              "gemm_tc: K and the row strides must be multiples of 8 elements (16 bytes), got K=%d "
@@ -430,10 +443,16 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   FB_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)b % 16) == 0,
              "gemm_tc: operands must start on 16-byte boundaries");
   FB_REQUIRE(splits >= 1 && (splits == 1 || out_f32), "gemm_tc: split-K needs a float32 output");
-  FB_REQUIRE(epilogue == 0 || (epilogue == 1 && splits == 1 && !out_f32 &&
-                               (stride_a == 1 || stride_b == 1)),
+  FB_REQUIRE(epilogue == 0 || epilogue == 2 ||
+                 (epilogue == 1 && splits == 1 && !out_f32 && (stride_a == 1 || stride_b == 1)),
              "gemm_tc: the SiLU-mul epilogue needs one split, a bf16 output and features on a "
              "unit stride");
+  FB_REQUIRE((epilogue != 2 && scale_ss == nullptr) || (splits == 1 && stride_b == 1),
+             "gemm_tc: the row scale and the residual epilogue need tokens as the A rows "
+             "(stride_b == 1) and one split");
+  FB_REQUIRE(epilogue != 2 || (resid && gamma && xg && ss_out && ss_stride >= rows_a &&
+                               ldr >= rows_b && ldxg >= rows_b),
+             "gemm_tc: the residual epilogue lacks an argument or a stride is too small");
   const int total_kb = (K + BK - 1) / BK;
   FB_REQUIRE(splits <= total_kb, "gemm_tc: %d splits for %d K blocks", splits, total_kb);
   bind_status_mirror(stream);
@@ -445,6 +464,9 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   p.constant_operand = constant_operand;
   p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = total_kb; p.partial = nullptr;
   p.tail_counters = nullptr;
+  p.rows = FbRowExtras{scale_ss, scale_count, scale_stride,
+                       scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps, resid, ldr, gamma,
+                       (__nv_bfloat16*)xg, ldxg, ss_out, ss_stride};
   if (persistent == 2) {
     // two SMs per tile (gemm_tcgen05_pair.cu)
     FB_REQUIRE(splits == 1, "gemm_tc: the paired form takes one split");

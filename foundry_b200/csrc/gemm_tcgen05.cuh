@@ -8,6 +8,25 @@
 
 #include "tcgen05.cuh"
 
+// What a product whose A rows are tokens (stride_b == 1) may do beyond storing:
+// apply the row scale of an input that is a norm's output without it, and, in
+// front of a norm (epilogue 2), add its result to the float32 residual rows,
+// leave resid * gamma in bfloat16 and every token's share of the sum of squares
+// over this tile's features (gemm_skinny.cu has the same two for few rows).
+struct FbRowExtras {
+  const float* scale_ss;  // [scale_count, scale_stride] shares of the tokens' sums of squares;
+                          // with scale_count == 0: the tokens' scales themselves; null: none
+  int scale_count, scale_stride;
+  float scale_inv_dim, scale_eps;
+  float* resid;           // [rows_a, rows_b] float32, row stride ldr
+  long long ldr;
+  const float* gamma;     // [rows_b]
+  __nv_bfloat16* xg;      // [rows_a, rows_b], row stride ldxg
+  long long ldxg;
+  float* ss_out;          // [feature tiles, ss_stride]
+  int ss_stride;
+};
+
 struct FbGemmParams {
   int rows_a, rows_b, K;
   int kblocks_per_split;      // K blocks of BK each CTA of a tile walks
@@ -16,7 +35,9 @@ struct FbGemmParams {
   void* out;
   int out_f32;                // 1: float32 output, 0: bfloat16
   int constant_operand;       // 1: A holds constants (weights), 2: B does, 0: neither
-  int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs
+  int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs;
+                              // 2: residual add in front of a norm (`rows`)
+  FbRowExtras rows;
   // paired form only: the tiles of the last, partly filled round are shared along K
   int full_tiles;             // tiles [0, full_tiles) are computed whole
   int tail_splits;            // K shares of every later tile (1: whole too)
@@ -131,6 +152,82 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const float (&v
       }
     }
   }
+}
+
+// 1 / sqrt(mean square + eps) of token `i` from the shares the product in front left.
+__device__ __forceinline__ float token_scale(const GemmParams& p, long long i) {
+  if (p.rows.scale_ss == nullptr || i >= p.rows_a) return 1.f;
+  if (p.rows.scale_count == 0) return __ldcg(p.rows.scale_ss + i);
+  float sum = 0.f;
+  for (int c = 0; c < p.rows.scale_count; ++c)
+    sum += __ldcg(p.rows.scale_ss + (size_t)c * p.rows.scale_stride + i);
+  return 1.0f / sqrtf(sum * p.rows.scale_inv_dim + p.rows.scale_eps);
+}
+
+// Epilogue 2 for CHUNK consecutive features (j0 ..) of token i: resid += v,
+// xg = bf16(resid * gamma); returns the chunk's sum of resid^2.
+template <int CHUNK>
+__device__ __forceinline__ float sink_chunk(const GemmParams& p, const float (&v)[CHUNK],
+                                            long long i, long long j0) {
+  if (i >= p.rows_a) return 0.f;
+  float* rp = p.rows.resid + i * p.rows.ldr + j0;
+  __nv_bfloat16* xp = p.rows.xg + i * p.rows.ldxg + j0;
+  const float* gp = p.rows.gamma + j0;
+  float ss = 0.f;
+  const bool vec = j0 + CHUNK <= p.rows_b && (((uintptr_t)rp | (uintptr_t)gp) % 16) == 0 &&
+                   ((uintptr_t)xp % 8) == 0;
+  if (vec) {
+    float4 old[CHUNK / 4];
+#pragma unroll
+    for (int e = 0; e < CHUNK / 4; ++e) old[e] = __ldcg(reinterpret_cast<const float4*>(rp) + e);
+#pragma unroll
+    for (int e = 0; e < CHUNK / 4; ++e) {
+      const float4 g = *(reinterpret_cast<const float4*>(gp) + e);
+      float4 r;
+      r.x = old[e].x + v[4 * e]; r.y = old[e].y + v[4 * e + 1];
+      r.z = old[e].z + v[4 * e + 2]; r.w = old[e].w + v[4 * e + 3];
+      *(reinterpret_cast<float4*>(rp) + e) = r;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(r.x * g.x, r.y * g.y);
+      const __nv_bfloat162 hi = __floats2bfloat162_rn(r.z * g.z, r.w * g.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *(reinterpret_cast<uint2*>(xp) + e) = pk;
+      ss += (r.x * r.x + r.y * r.y) + (r.z * r.z + r.w * r.w);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < CHUNK; ++e) {
+      if (j0 + e < p.rows_b) {
+        const float r = __ldcg(rp + e) + v[e];
+        rp[e] = r;
+        xp[e] = __float2bfloat16_rn(r * gp[e]);
+        ss += r * r;
+      }
+    }
+  }
+  return ss;
+}
+
+// A chunk of a tile's epilogue with the row extras: scale, then sink or store.
+// Returns what the chunk adds to the token's sum of squares (epilogue 2, else 0).
+template <int CHUNK>
+__device__ __forceinline__ float finish_chunk(const GemmParams& p, float (&v)[CHUNK], float scale,
+                                              long long i_global, long long j0, int lane,
+                                              float* out_f, __nv_bfloat16* out_h) {
+  if (p.rows.scale_ss != nullptr) {
+#pragma unroll
+    for (int e = 0; e < CHUNK; ++e) v[e] *= scale;
+  }
+  if (p.epilogue == 2) return sink_chunk<CHUNK>(p, v, i_global, j0);
+  store_chunk<CHUNK>(p, v, i_global, j0, lane, out_f, out_h);
+  return 0.f;
+}
+// After a tile's last chunk: the token's share over this tile's features.
+__device__ __forceinline__ void finish_tile(const GemmParams& p, float ss, long long i_global,
+                                            int tile_b) {
+  if (p.epilogue == 2 && i_global < p.rows_a)
+    p.rows.ss_out[(size_t)tile_b * p.rows.ss_stride + i_global] = ss;
 }
 
 // ------------------------------------------------------------- host: tensor maps

@@ -296,6 +296,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       // kernel's own: per (tile, share, CTA, warp) a block of BN / 4 groups of 32
       // float4, group g holding columns 4g..4g+3 of the warp's 32 rows, so that a warp
       // writes and later reads 512 contiguous bytes per instruction.
+      const float scale = token_scale(p, i_global);
+      float ss = 0.f;
       float4* mine = w.share < 0 ? nullptr
                                  : reinterpret_cast<float4*>(p.partial) +
                                        (((size_t)(w.tail_tile * p.tail_splits + w.share) * 8 +
@@ -319,13 +321,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int e = 0; e < 16; ++e) v[e] = __uint_as_float(r[e]);
         }
         if (mine == nullptr) {
-          store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+          ss += finish_chunk<CHUNK>(p, v, scale, i_global, (long long)tb * BN + c, lane, out_f, out_h);
         } else {
 #pragma unroll
           for (int e = 0; e < CHUNK; e += 4)
             mine[(size_t)((c + e) / 4) * 32] = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
         }
       }
+      if (mine == nullptr) finish_tile(p, ss, i_global, tb);
       // this warp has read its lanes of the accumulator: tell the leader's MMA warp
       tc_fence_before();
       __syncwarp();
@@ -372,8 +375,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                 }
               }
             }
-            store_chunk<CHUNK>(p, v, i_global, (long long)tb * BN + c, lane, out_f, out_h);
+            ss += finish_chunk<CHUNK>(p, v, scale, i_global, (long long)tb * BN + c, lane, out_f, out_h);
           }
+          finish_tile(p, ss, i_global, tb);
           if (lane == 0) *counter = 0;  // as the next call expects it
         }
       }

@@ -1,10 +1,11 @@
 """Short prompt steps as replayed CUDA graphs.
 
 A prompt step of the 3B model is some 230 kernel launches; from Python that is
-about 4 ms of host time, more than the GPU needs for a prompt of up to about a
-hundred tokens (measured: 20 tokens 4.0 -> 2.3 ms, 128 tokens 4.0 -> 2.65 ms;
-from 300 tokens on the GPU is the slower side: replayed, 300 to 1,000 tokens
-gained 1 to 4 %). So steps of up to `PROMPT_GRAPH_TOKENS` tokens run like the
+4 to 5 ms of host time, more than the GPU needs for a prompt of up to a few
+hundred tokens (measured: 20 tokens 4.0 -> 2.3 ms, 128 tokens 4.0 -> 2.65 ms,
+129 tokens 4.6 -> 3.6 ms, 300 tokens 4.6 -> 4.4 ms, 512 tokens 4.7 -> 4.5 ms;
+at 1,000 tokens 7.1 -> 6.8 ms, where the buffers a captured step keeps are no
+longer worth it). So steps of up to `PROMPT_GRAPH_TOKENS` tokens run like the
 single-token steps (decode.py): padded up to a bucket (tokens, sequences,
 page-table width, wanted rows), described by fixed device buffers that one copy
 from pinned memory refreshes, captured once per bucket and replayed.
@@ -35,7 +36,7 @@ from .decode import bucket_of
 from .staging import StagingRing
 
 # steps of more tokens than this run as plain launches (0: always plain)
-PROMPT_GRAPH_TOKENS = int(os.environ.get("FOUNDRY_B200_PROMPT_GRAPH_TOKENS", "128"))
+PROMPT_GRAPH_TOKENS = int(os.environ.get("FOUNDRY_B200_PROMPT_GRAPH_TOKENS", "512"))
 MAX_RUNNERS = 24  # buckets kept; the least recently used one goes first
 
 

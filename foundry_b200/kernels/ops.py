@@ -42,7 +42,8 @@ _SIGNATURES = {
     "fb_sum_planes": [c_void_p, c_int, c_ll, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int,
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
-                   c_int, c_void_p],
+                   c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
+                   c_void_p, c_ll, c_void_p, c_int, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_tc_pair_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
@@ -74,6 +75,7 @@ _SIGNATURES = {
                      c_void_p, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int,
                      c_int, c_int, c_int, c_void_p],
     "fb_gemm_rows_status": [c_void_p],
+    "fb_row_scales": [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p],
     "fb_select_tokens": [c_void_p, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                          c_int, c_void_p, c_void_p, c_void_p],
 }
@@ -261,6 +263,7 @@ class RowScaled:
 
     def __init__(self, values: torch.Tensor, shares: torch.Tensor, eps: float):
         self.values, self.shares, self.eps = values, shares, float(eps)
+        self._scales = None
 
     @property
     def shape(self):
@@ -278,6 +281,18 @@ class RowScaled:
         """(shares, count, stride, dim, eps) as the kernels take them."""
         return (self.shares.data_ptr(), self.shares.shape[0], self.shares.stride(0),
                 self.values.shape[1], self.eps)
+
+    def scales_args(self):
+        """The same for kernels that take the tokens' scales themselves (a count
+        of 0): one small kernel adds the shares up once, where the epilogues of
+        a product of many rows would do it again for every tile."""
+        if self._scales is None:
+            T = self.values.shape[0]
+            self._scales = torch.empty(T, dtype=torch.float32, device=self.values.device)
+            _call("fb_row_scales", self.shares.data_ptr(), self.shares.shape[0],
+                  self.shares.stride(0), self.values.shape[1], self.eps, self._scales.data_ptr(),
+                  T, _stream())
+        return (self._scales.data_ptr(), 0, 0, self.values.shape[1], self.eps)
 
     def materialize(self) -> torch.Tensor:
         T, H = self.values.shape
@@ -523,13 +538,27 @@ def _pair_scratch(device):
     return got
 
 
-def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, stride_b: int,
+def gemm_tc(a, b: torch.Tensor, out: Optional[torch.Tensor], stride_a: int, stride_b: int,
             bn: int, splits: int = 1, split_stride: int = 0, epilogue: int = 0,
-            constant_operand: int = 0, persistent: int = 0) -> None:
+            constant_operand: int = 0, persistent: int = 0,
+            sink: Optional[ResidualSink] = None, sink_out=None) -> None:
     """Tensor-core product D[i,j] = sum_k a[i,k] b[j,k] written to
-    out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu."""
+    out[i*stride_a + j*stride_b (+ split*split_stride)]; see csrc/gemm_tcgen05.cu.
+    With tokens as the rows of `a` (stride_b == 1, one split): `a` may be a
+    `RowScaled`, and `sink` (with `sink_out` = (values, shares)) makes the
+    epilogue add into the residual rows in front of a norm instead of storing."""
+    scale = _NO_SCALE
+    if isinstance(a, RowScaled):
+        scale, a = a.scales_args(), a.values
     if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
         raise KernelError("gemm_tc takes bfloat16 operands")
+    sink_args = (0, 0, 0, 0, 0, 0, 0)
+    if sink is not None:
+        values, shares = sink_out
+        sink_args = (_dev(sink.resid, "resid", torch.float32, contiguous=False),
+                     _rows(sink.resid, "resid"), _dev(sink.gamma, "gamma", torch.float32),
+                     values.data_ptr(), values.stride(0), shares.data_ptr(), shares.stride(0))
+        epilogue, out = 2, values  # `out` only names a buffer for the argument checks
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"gemm_tc writes float32 or bfloat16, not {out.dtype}")
     scratch = (0, 0, 0, 0)
@@ -540,7 +569,8 @@ def gemm_tc(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, stride_a: int, 
           _dev(b, "b", contiguous=False), _rows(b, "b"), b.shape[0], a.shape[1],
           _dev(out, "out", contiguous=False), stride_a, stride_b,
           1 if out.dtype == torch.float32 else 0, bn, splits, split_stride, epilogue,
-          constant_operand, int(persistent), *scratch, PAIR_SHARE_MIN_KBLOCKS, _stream(),
+          constant_operand, int(persistent), *scratch, PAIR_SHARE_MIN_KBLOCKS, *scale, *sink_args,
+          _stream(),
           tag=("a{} b{} k{} tile{} splits{}", a.shape[0], b.shape[0], a.shape[1], bn, splits))
 
 
@@ -790,6 +820,12 @@ FUSE_QKV_ROPE = _os.environ.get("FOUNDRY_B200_FUSE_QKV_ROPE", "1") != "0"
 ROPE_TRIGGER_PAGES = 64  # page-table width up to which the q/k/v product triggers its successor
 # the projections around a norm take the norm over (see `ResidualSink`, `RowScaled`)
 NORM_FUSION = _os.environ.get("FOUNDRY_B200_NORM_FUSION", "1") != "0"
+# ... up to this many token rows. The products whose rows are tokens (more than 64)
+# can do the same in their epilogue, and lose by it: a thread of their epilogue owns
+# a token, so a warp's read-modify-write of the float32 residual touches 32 rows
+# 12 KB apart with 16 bytes each (2,048-token prompt of the 3B shape: 12.1 -> 15.9 ms,
+# 512 tokens 4.7 -> 6.0 ms). The norm stays a kernel of its own there.
+NORM_FUSION_ROWS = int(_os.environ.get("FOUNDRY_B200_NORM_FUSION_ROWS", "64"))
 
 
 def skinny_plan(N: int, K: int, planes_ok: bool):
@@ -990,9 +1026,8 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         return out if out is not None else torch.empty((0, N), dtype=out_dtype, device=x.device)
     values = x.values if isinstance(x, RowScaled) else x
     usable = _tc_usable(values, w, out if out is not None else values)
-    if not (usable and (M <= SKINNY_ROWS or rows_usable(x, w))):
-        x = plain(x)
     if not usable:
+        x = plain(x)
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         return gemm_simt(x, w, out)
@@ -1014,24 +1049,30 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
                 and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
             return gemm_rows_residual(x, w, residual)
         return gemm_rows(x, w, out, out_dtype)
-    x = plain(x)
     splits, fits = _one_tile_plan(M, N, K)
-    if M > 128 and not (fits and M <= ONE_TILE_ROWS):
+    many = M > 128 and not (fits and M <= ONE_TILE_ROWS)
+    if many or splits == 1:
+        # tokens are the rows of the tensor-core tile and nothing is split: the epilogue
+        # applies a deferred row scale, and in front of a norm adds into the residual
+        bn, form = prompt_plan(M, N) if many else (128, 0)
+        if (residual is not None and NORM_FUSION and M <= NORM_FUSION_ROWS and out is None
+                and tuple(residual.resid.shape) == (M, N) and not isinstance(x, RowScaled)):
+            values = torch.empty((M, N), dtype=torch.bfloat16, device=w.device)
+            shares = torch.empty(((N + bn - 1) // bn, (M + 31) // 32 * 32), dtype=torch.float32,
+                                 device=w.device)
+            gemm_tc(x, w, None, N, 1, bn, constant_operand=2, persistent=form, sink=residual,
+                    sink_out=(values, shares))
+            return NormPending(residual, values, shares)
         if out is None:
-            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        bn, form = prompt_plan(M, N)
+            out = torch.empty((M, N), dtype=out_dtype, device=w.device)
         gemm_tc(x, w, out, out.stride(0), 1, bn, constant_operand=2, persistent=form)
         return out
-    # 17..128 rows (and more, while one round of tiles covers them): the tokens are the
-    # (partly empty) 128-row operand, so that a thread of the epilogue owns a token's
-    # consecutive features and stores them as vectors; with the weights as the row
-    # operand ("swapped") the same product was 2.5 us a call slower, all of it in the
-    # scalar stores
-    if splits == 1:
-        if out is None:
-            out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        gemm_tc(x, w, out, out.stride(0), 1, 128, constant_operand=2)
-        return out
+    # 17..128 rows (and more, while one round of tiles covers them) with K split over
+    # CTAs: the tokens are the (partly empty) 128-row operand, so that a thread of the
+    # epilogue owns a token's consecutive features and stores them as vectors; with
+    # the weights as the row operand ("swapped") the same product was 2.5 us a call
+    # slower, all of it in the scalar stores
+    x = plain(x)
     planes = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
     gemm_tc(x, w, planes, N, 1, 128, splits, M * N, constant_operand=2)
     if allow_planes and out is None:
@@ -1060,9 +1101,8 @@ def gemm_bf16_silu_mul(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor
     usable = _tc_usable(x.values if isinstance(x, RowScaled) else x, w_pairs, out)
     if usable and rows_usable(x, w_pairs):
         return gemm_rows(x, w_pairs, out, silu_mul=True)
-    if not (usable and M <= SKINNY_ROWS):
-        x = plain(x)
     if not usable:
+        x = plain(x)
         tmp = torch.empty((M, two_i), dtype=torch.bfloat16, device=x.device)
         gemm_simt(x, w_pairs, tmp)
         return silu_mul(tmp, out, interleaved=True)

@@ -121,7 +121,7 @@ class GQAAttention(Part):
                                    self.num_heads, self.num_kv_heads, self.head_dim,
                                    ring_pages=cache.group.ring_pages, write_cache=cache.writes)
         else:
-            x = ops.plain(x)
+            # (a row-scaled input stays so: the tcgen05 products apply the scale)
             qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes
             q = ops.rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, self.inv_freq,
                                   self.rotary_dim, cache.k, cache.v, self.num_heads,

@@ -273,7 +273,7 @@ def test_padding_changes_no_result(tiny_folders):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_short_prompt_steps_replayed_equal_plain_launches(tiny_folders, dtype):
-    """Prompt steps of up to 128 tokens run as replayed graphs over padded
+    """Prompt steps of up to 512 tokens run as replayed graphs over padded
     buckets. The same steps launched plainly give the same logits bit for bit:
     one bucket used three times with other lengths, sequence counts and wanted
     places (the second and third use replay the graph of the first), a
@@ -288,7 +288,8 @@ def test_short_prompt_steps_replayed_equal_plain_launches(tiny_folders, dtype):
               [(70, [69]), (30, [0, 29, 5])],
               [(5, [4])],                              # a small bucket
               [(16, []), (3, [])],                     # nothing wanted
-              [(64, [63]), (64, [0]), (1, [0])]]       # 129 tokens: launched plainly in both
+              [(64, [63]), (64, [0]), (1, [0])],       # 129 tokens -> the 256-token bucket
+              [(240, [239]), (240, [0, 239]), (40, [39])]]  # 520 tokens: launched plainly in both
     results = []
     for graphs in (True, False):
         engine = engine_for(tiny_folders[name], dtype, max_slots=4, max_tokens=1024)
@@ -309,9 +310,10 @@ def test_short_prompt_steps_replayed_equal_plain_launches(tiny_folders, dtype):
         if graphs:
             keys = set(engine._prompts._runners)
             # rounds 2 and 3 replayed one graph; the seven-token steps of all rounds share theirs
-            assert {(128, 2, 8, 4, True), (128, 2, 8, 4, False)} <= keys and len(keys) <= 7, keys
+            assert {(128, 2, 8, 4, True), (128, 2, 8, 4, False)} <= keys and len(keys) <= 9, keys
+            assert any(k[0] == 256 for k in keys), keys
         results.append(out)
-    assert prompt_graphs.PROMPT_GRAPH_TOKENS == 128
+    assert prompt_graphs.PROMPT_GRAPH_TOKENS == 512
     for a, b in zip(*results):
         assert a.shape == b.shape and torch.equal(a, b)
 

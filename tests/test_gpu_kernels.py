@@ -976,3 +976,49 @@ def test_gemm_rows_rope(ops, A, Kh, D, rot, T):
     assert torch.equal(q3[live], q[live])
     assert float(k_cache.float().abs().max()) == 0.0 and float(v_cache.float().abs().max()) == 0.0
     assert ops.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("M,H,K", [(100, 200, 264), (128, 3072, 520), (300, 2048, 1024), (700, 3072, 8192),
+                                   (2048, 3072, 3072), (2500, 1000, 264)])
+def test_gemm_many_rows_takes_the_norm_over(ops, monkeypatch, M, H, K):
+    monkeypatch.setattr(ops, "NORM_FUSION_ROWS", 1 << 20)  # off by default for these row counts
+    _many_rows_norm(ops, M, H, K)
+
+
+def _many_rows_norm(ops, M, H, K):
+    """The products whose rows are tokens (one tile per CTA without K shares, one
+    CTA per SM, two SMs per tile, the shared last round): in front of a norm they
+    add into the residual rows and leave resid * gamma and each feature tile's share
+    of the sums of squares; behind the norm they apply 1 / sqrt(mean + eps) in their
+    epilogue, the plain product and the SiLU-mul product alike."""
+    eps = 3e-5
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(H, K, dtype=torch.bfloat16, scale=0.2, seed=1)
+    resid0 = rnd(M, H, seed=2) * 3.0
+    resid0[0] *= 40.0
+    gamma = (1.0 + 0.3 * rnd(H, seed=3)).contiguous()
+    resid = resid0.clone()
+    pending = ops.gemm_bf16(x, w, residual=ops.ResidualSink(resid, gamma, eps))
+    if not isinstance(pending, ops.NormPending):
+        # K shared among CTAs as float32 planes: the norm stays a kernel of its own
+        assert ops._one_tile_plan(M, H, K)[0] > 1
+        return
+    want_resid = resid0.double() + x.double() @ w.double().T
+    close(resid, want_resid, 4e-3, 1e-5)
+    close(pending.values, resid.double() * gamma.double(), 1e-6, 2.0 ** -8)
+    close(pending.shares[:, :M].sum(0), (want_resid ** 2).sum(1), 1e-3, 1e-4)
+    scaled = ops.add_rmsnorm(resid, pending, gamma, eps, None)
+    assert isinstance(scaled, ops.RowScaled)
+    rstd = 1.0 / torch.sqrt((resid.double() ** 2).mean(1, keepdim=True) + eps)
+    w2 = rnd(264, H, dtype=torch.bfloat16, scale=0.1, seed=5)
+    many = M > 128 and not (ops._one_tile_plan(M, 264, H)[1] and M <= ops.ONE_TILE_ROWS)
+    if many or ops._one_tile_plan(M, 264, H)[0] == 1:
+        inputs = pending.values.double() * rstd  # the scale is applied in the epilogue
+    else:
+        inputs = scaled.materialize().double()   # K is shared as planes: the scaled tensor is made first
+    close(ops.gemm_bf16(scaled, w2, out_dtype=torch.float32), inputs @ w2.double().T, 4e-3, 1e-4)
+    pairs = rnd(400, H, dtype=torch.bfloat16, scale=0.1, seed=6)
+    hidden = torch.empty(M, 200, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_bf16_silu_mul(scaled, pairs, hidden)
+    gu = (pending.values.double() @ pairs.double().T) * rstd
+    close(hidden, gu[:, 0::2] / (1 + torch.exp(-gu[:, 0::2])) * gu[:, 1::2], 2e-3, 1e-2)
+    assert ops.gemm_tc_status() == 0
