@@ -180,8 +180,11 @@ FB_API int fb_add_rmsnorm(float* resid, const void* delta, int delta_dtype, int 
     const int groups = H / 4;
     // few rows: wide blocks make a row's latency short; many rows: narrower blocks
     // with more loads in flight per thread keep more rows resident per SM
+    // (the block width decides the order of a row's sum: "many" begins above 512 rows,
+    // the largest step that is also run padded to a bucket, so that a step and its
+    // padded form take the same width)
     int threads = groups <= 128 ? 128 : groups <= 512 ? 256 : groups <= 1024 ? 512 : 1024;
-    if (T >= 512 && groups <= 1024) threads = groups <= 512 ? 128 : 256;
+    if (T > 512 && groups <= 1024) threads = groups <= 512 ? 128 : 256;
     const int items = (groups + threads - 1) / threads;
 #define FB_NORM_LAUNCH(N)                                                                     \
     FB_DISPATCH_DTYPE(delta_dtype, TD, FB_DISPATCH_DTYPE(out_dtype, TO, (                     \
