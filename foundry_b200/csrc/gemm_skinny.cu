@@ -125,7 +125,7 @@ constexpr int MODE_SINK = 2;   // add into the residual rows in front of a norm
 // of 8 tokens ran three CTAs to an SM and took 3 us longer; capped to 96 (five
 // CTAs) its 1,024 CTAs run as 740 and a thin 284, which was slower too. With 16
 // tokens the cap holds only because x is fetched one chunk ahead instead of all
-// chunks at once (batch 16: 3.05 -> 2.85 ms a step).
+// chunks at once.
 constexpr int min_blocks(int warps) { return 16 / warps; }
 template <int NT, int WARPS, int UNROLL, int MODE>
 __global__ void __launch_bounds__(WARPS * 32, min_blocks(WARPS))
@@ -149,7 +149,7 @@ gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx,
   // (a thin last round, SMs with one CTA of two) goes to blocks that ask for their
   // first weights while this kernel still streams. The other CTAs say so when their
   // main loop is through (below). Measured on the 3B decode step at batch 8 with
-  // the last half round starting so: 2.02 -> 1.93 ms (a whole round: 1.96).
+  // the last half round starting so, that was the fastest (a whole round and a quarter lost).
   if (late_trigger && (int)(blockIdx.x + blockIdx.y * gridDim.x) >= early_from) fb_pdl_launch();
   int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);  // rows past N are discarded
   // rotary epilogue: this CTA's head, and its rows' first elements inside the head

@@ -435,7 +435,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
   // when a share still has `share_min_kblocks` K blocks: measured at 2,048 rows, a
   // unit costs a few microseconds beside its K loop and the last share's warp
   // adds the sum and the stores, so sharing paid at K = 8,192 in three shares
-  // (92.5 -> 78.6 us) and did not at K = 3,072 (16 or 12 blocks a share).
+  // and did not at K = 3,072 (16 or 12 blocks a share).
   const int total = tiles_a * tiles_b;
   const int nkb = (p.K + BK - 1) / BK;
   GemmParams q = p;

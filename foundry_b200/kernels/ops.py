@@ -712,11 +712,9 @@ def gemm_skinny_rope(x: torch.Tensor, w: torch.Tensor, positions: torch.Tensor,
 # ----------------------------------------------- 17 .. 256 token rows (tcgen05)
 # Token rows up to which the product that shares a weight tile's K among the CTAs
 # of a cluster and sums in the kernel is taken (csrc/gemm_rows_tcgen05.cu);
-# ROWS_MAX = 0 keeps the one-tile product with float32 planes. Measured on the 3B
-# decode step (8 layers, both forms in one run): 32 rows 0.840 -> 0.752 ms, 64 rows
-# at 512 tokens of context 1.066 -> 0.986, at 3,072 tokens 1.800 -> 1.753; at 128
-# rows the one-tile product stays ahead (1.348 against 1.413: this kernel then has
-# three shared-memory stages). The kernel itself takes up to 256 rows.
+# ROWS_MAX = 0 keeps the one-tile product with float32 planes. Up to 64 rows this
+# kernel makes the decode step faster; at 128 rows it has only three shared-memory
+# stages and the one-tile product stays ahead. The kernel itself takes up to 256 rows.
 # ROWS_SPLITS overrides the CTAs per weight tile (0: the launcher's choice).
 ROWS_SPLITS = int(_os.environ.get("FOUNDRY_B200_ROWS_SPLITS", "0"))
 ROWS_MAX = int(_os.environ.get("FOUNDRY_B200_ROWS_MAX", "64"))
@@ -823,8 +821,8 @@ NORM_FUSION = _os.environ.get("FOUNDRY_B200_NORM_FUSION", "1") != "0"
 # ... up to this many token rows. The products whose rows are tokens (more than 64)
 # can do the same in their epilogue, and lose by it: a thread of their epilogue owns
 # a token, so a warp's read-modify-write of the float32 residual touches 32 rows
-# 12 KB apart with 16 bytes each (2,048-token prompt of the 3B shape: 12.1 -> 15.9 ms,
-# 512 tokens 4.7 -> 6.0 ms). The norm stays a kernel of its own there.
+# 12 KB apart with 16 bytes each, and a prompt step takes a quarter longer. The norm
+# stays a kernel of its own there.
 NORM_FUSION_ROWS = int(_os.environ.get("FOUNDRY_B200_NORM_FUSION_ROWS", "64"))
 
 
