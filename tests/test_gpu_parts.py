@@ -119,6 +119,54 @@ def test_attention_part_alone_in_two_cuttings(name, dtype):
     assert_close(got, torch.cat(want), dtype, scale=float(torch.cat(want).abs().max()))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_block_part_alone(name, dtype):
+    """The arrangement of a layer's parts, built from its description alone and
+    run on residual rows of its own: x + mixer(norm(x)), then + feed-forward(norm(.)),
+    against the plain decoder layer; whole sequences, then the same with the last
+    tokens one by one (where the norms ride on the projections)."""
+    from foundry_b200.cache import SequenceCache
+    from foundry_b200.config import LlamaConfig
+    from foundry_b200.models.llama import build_llama_spec
+    from foundry_b200.parts import BLOCKS
+    cfg = tiny.CONFIGS[name]
+    spec = build_llama_spec(LlamaConfig.parse(cfg))
+    layer = spec.layers[1]
+    block = BLOCKS.build(layer.block, layer=layer, dtype=dtype, device=DEV)
+    torch.manual_seed(3)
+    w = {k: ((1.0 + 0.1 * torch.randn(*e.shape)) if len(e.shape) == 1 else 0.1 * torch.randn(*e.shape)).to(dtype)
+         for k, e in block.expected_tensors().items()}
+    assert all(k.startswith("model.layers.1.") for k in w)
+    block.load(block.prefix, lambda n: w[n].to(DEV))
+    cache = SequenceCache({0: block.cache_request()}, 512, 4, dtype, DEV)
+    H = cfg["hidden_size"]
+    lens = [37, 5, 66]
+    xs = [torch.randn(n, H) for n in lens]
+    wd = {k: v.double() for k, v in w.items()}
+    want = [plain.decoder_layer(x.double(), wd, 1, cfg, list(range(len(x)))) for x in xs]
+
+    def run(ctx, rows):
+        resid = torch.cat(rows).to(DEV).float().contiguous()
+        delta = block.forward(ctx, resid, None, cache.view(0, True))
+        from foundry_b200.kernels import ops
+        if isinstance(delta, ops.Planes):
+            delta = delta.sum(dtype)
+        return resid.double().cpu() + delta.double().cpu()  # the block returns its last part un-added
+
+    slots = [cache.open_sequence() for _ in lens]
+    head = [n - 3 for n in lens]
+    got = [list(torch.split(run(make_ctx(cache, slots, [[0] * h for h in head]),
+                                [x[:h] for x, h in zip(xs, head)]), head))]
+    for step in range(3):
+        out = run(make_ctx(cache, slots, [[0]] * len(lens)),
+                  [x[h + step:h + step + 1] for x, h in zip(xs, head)])
+        got.append(list(torch.split(out, [1] * len(lens))))
+    for i in range(len(lens)):
+        whole = torch.cat([piece[i] for piece in got])
+        assert_close(whole, want[i], dtype, scale=float(want[i].abs().max()))
+
+
 def test_position_encoding_parts_follow_the_reference_bands():
     """llama3 scaling at D = 128, theta = 5e5, factor 32: the three frequencies
     the reference pins (j = 0 unscaled, j = 32 blended, j = 63 divided;
