@@ -126,7 +126,6 @@ struct AttnParams {
   int splits;    // CTAs per (sequence, kv head)
   int cluster;   // of which this many merge inside a thread-block cluster (1: none)
   int parts;     // partial results per pair that meet in the workspace: splits / cluster
-  int balanced;  // 1: ranges are 1/splits of the LONGEST sequence's pages for every sequence
   float* ws_o;   // [n_seqs, Kh, parts, 16, D]
   float* ws_ml;  // [n_seqs, Kh, parts, 16, 2]
   int* counters; // [n_seqs, Kh]: CTAs that have delivered; zero between calls
@@ -460,25 +459,7 @@ attn_decode_kernel(const AttnParams p) {
   const int token = p.cu_tokens[seq];
   const int kv_len = p.kv_lens[seq];
   const int n_pages = (kv_len + FB_PAGE - 1) / FB_PAGE;
-  // A range is 1/splits of this sequence's pages; or, for batches of unequal
-  // lengths, 1/splits of the longest sequence's pages for every sequence: a short
-  // sequence then takes few CTAs (the others find their range empty and leave),
-  // the longest takes them all, and no CTA walks more than its share of the
-  // longest while the rest of the GPU idles.
-  int span = n_pages;
-  if (p.balanced) {
-    __shared__ int s_longest;
-    if (threadIdx.x == 0) s_longest = 0;
-    __syncthreads();
-    int longest = 0;
-    for (int i = threadIdx.x; i < p.n_seqs; i += THREADS) longest = max(longest, p.kv_lens[i]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
-    if (lane == 0) atomicMax(&s_longest, longest);
-    __syncthreads();
-    span = (s_longest + FB_PAGE - 1) / FB_PAGE;
-  }
-  const int per = (span + p.splits - 1) / p.splits;
+  const int per = (n_pages + p.splits - 1) / p.splits;  // a range: 1/splits of the pages
   const int pg0 = split * per;
   const int pg1 = min(n_pages, pg0 + per);
   const int fresh = max(kv_len - (p.cu_tokens[seq + 1] - token), 0) / FB_PAGE;
@@ -872,9 +853,7 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
 // all of them without clusters) meet in the workspaces, which must hold
 // n_seqs*Kh*parts*16*D and n_seqs*Kh*parts*32 floats, with `counters` of
 // n_seqs*Kh ints that are zero when the call starts (the kernel leaves them zero
-// again); with one part per pair they are not used and may be null. `balanced`:
-// every sequence's ranges are 1/splits of the longest sequence's pages (see the
-// kernel), for batches of unequal lengths. `stages`
+// again); with one part per pair they are not used and may be null. `stages`
 // (2 or 3) is the number of page buffers per CTA. A sequence with kv_lens == 0
 // is padding: its output rows are zeros.
 FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
@@ -882,7 +861,7 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
                                int max_pages, const void* k_cache, const void* v_cache,
                                long long page_stride, long long head_stride, int n_seqs, int A,
                                int Kh, int D, float scale, int splits, int stages, int cluster,
-                               int balanced, float* ws_o, float* ws_ml, int* counters,
+                               float* ws_o, float* ws_ml, int* counters,
                                const void* next, long long next_bytes, cudaStream_t stream) {
   FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
              "attention_decode: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
@@ -906,7 +885,6 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.page_stride = page_stride; p.head_stride = head_stride;
   p.n_seqs = n_seqs; p.A = A; p.Kh = Kh; p.scale_log2 = scale * LOG2E;
   p.splits = splits; p.cluster = cluster; p.parts = parts;
-  p.balanced = balanced ? 1 : 0;
   p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
   p.next = next; p.next_bytes = next_bytes;
   FB_REQUIRE(stages == 2 || stages == 3, "attention_decode: %d page buffers (2 or 3)", stages);
@@ -995,5 +973,5 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, 3, 1, 0, ws_o, ws_ml, counters, nullptr, 0, stream);
+                             D, scale, splits, 3, 1, ws_o, ws_ml, counters, nullptr, 0, stream);
 }

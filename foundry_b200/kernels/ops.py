@@ -67,7 +67,7 @@ _SIGNATURES = {
     "fb_attention_tc_status": [c_void_p],
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_ll, c_void_p],
     "fb_gemm_rows": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int,
                      c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
@@ -1134,15 +1134,8 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
                               v_cache, num_heads, num_kv_heads, head_dim, scale, window, ring_pages)
     if ctx.is_decode:
         pairs, pages = ctx.n_seqs * num_kv_heads, (ctx.max_kv_len + PAGE - 1) // PAGE
-        splits, stages = decode_plan(pairs, pages)
-        if getattr(ctx, "unequal_lengths", False) and splits < UNEQUAL_SPLITS and pages >= 16:
-            # many sequences of unequal lengths: ranges by the longest one's pages, merged
-            # through the workspace (CTAs with empty ranges leave at once instead of
-            # waiting in a cluster)
-            return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache,
-                                    v_cache, num_heads, num_kv_heads, head_dim, scale,
-                                    min(UNEQUAL_SPLITS, pages // 4), stages, then_reads=then_reads,
-                                    cluster=1, balanced=True)
+        splits, stages = decode_plan(pairs, pages, head_dim,
+                                     getattr(ctx, "unequal_lengths", False))
         return attention_decode(q, out, ctx.cu_tokens, ctx.kv_lens, page_table, k_cache, v_cache,
                                 num_heads, num_kv_heads, head_dim, scale, splits, stages,
                                 then_reads=then_reads)
@@ -1162,27 +1155,42 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, page_table: torch.Tensor,
                              num_heads, num_kv_heads, head_dim, scale, blocks)
 
 
-def decode_plan(pairs: int, pages: int):
+# Seconds a warp of the decode kernel takes for its 16 keys of a page (a chain of
+# dependent instructions, whatever the head size or the load of the GPU), and the
+# bytes a second that the cache streams at when enough CTAs ask: with these two a
+# plan can tell whether a CTA that walks a whole sequence alone keeps up with memory.
+DECODE_PAGE_SECONDS = 0.63e-6
+DECODE_STREAM_BYTES_PER_SECOND = 6.5e12
+
+
+def decode_plan(pairs: int, pages: int, head_dim: int = 128, unequal: bool = False):
     """(splits, page buffers) of decode attention for `pairs` (sequence, kv head)
-    pairs of up to `pages` cache pages, as measured on B200 with head size 128.
-    Three page buffers per CTA (two pages on their way while one is multiplied),
-    of which two CTAs fit an SM; ranges are split while all CTAs stay resident at
-    once (a second round of CTAs cost 10 us a call). Up to eight CTAs of a pair
-    are one cluster; a long context with few pairs takes several clusters, whose
-    results meet in the workspace (a warp walks a page in 0.6 us whatever else
-    runs, so a range's length is what a short batch waits for)."""
-    room = 2 * sm_count() // max(pairs, 1)
+    pairs of up to `pages` cache pages, as measured on B200. Three page buffers per
+    CTA (two pages on their way while one is multiplied); 2 CTAs of head size 128
+    fit an SM, 4 of 64 or less. Ranges are split while all CTAs stay resident at
+    once (a second round of CTAs cost 10 us a call), at most eightfold (one
+    cluster). Sequences of equal lengths are not split at all once their pairs
+    are many enough for memory to be the limit: a CTA walks a page in
+    DECODE_PAGE_SECONDS, so `pairs` CTAs ask for pairs * page bytes in that time,
+    and where that exceeds what memory delivers, more CTAs only add merges
+    (batch 16 of 8 kv heads of 128: 32.9 us unsplit, 34.6 in two ranges). With
+    unequal lengths the longest sequence's CTA is what the batch waits for, and
+    ranges are split as far as residency allows (32 sequences of 400 to 4,000
+    tokens, 8 kv heads of 64: 48.7 us unsplit, 34.6 in two ranges). A long context
+    with few pairs takes several clusters, whose results meet in the workspace."""
+    resident = sm_count() * min(4, 256 // max(head_dim, 1))
+    room = resident // max(pairs, 1)
     if room >= 16 and pages >= 160:
         # clusters of 8 while a CTA keeps 4 pages or more; the second merge costs
         # 3 to 4 us, which pays from about 10 K tokens on (batch 1 at 16 K tokens:
         # 26.7 us with 8 shares, 19.4 with 32; at 4 K: 10.6 against 12.9)
         return min(room // 8 * 8, max(16, pages // 4 // 8 * 8)), 3
+    page_bytes = 2 * PAGE * head_dim * 2  # keys and values of one kv head
+    if not unequal and pairs * page_bytes >= DECODE_PAGE_SECONDS * DECODE_STREAM_BYTES_PER_SECOND:
+        return 1, 3
     return max(1, min(DECODE_CLUSTER_MAX, pages, room)), 3
 
 
-# Ranges per sequence when a step says that its sequences' lengths are unequal
-# (`ctx.unequal_lengths`) and the plan above would give each sequence fewer.
-UNEQUAL_SPLITS = int(_os.environ.get("FOUNDRY_B200_UNEQUAL_SPLITS", "4"))
 TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prompt-attention kernel
 PREFILL_TC = _os.environ.get("FOUNDRY_B200_PREFILL_TC", "1") != "0"
 
@@ -1229,16 +1237,14 @@ DECODE_CLUSTER = _os.environ.get("FOUNDRY_B200_DECODE_CLUSTER", "1") != "0"
 def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, num_heads,
                      num_kv_heads, head_dim, scale, splits, stages: int = 3,
                      then_reads: Optional[torch.Tensor] = None,
-                     cluster: Optional[int] = None, balanced: bool = False) -> torch.Tensor:
+                     cluster: Optional[int] = None) -> torch.Tensor:
     """Tensor-core attention for one token per sequence, the cache range split
     over `splits` CTAs per (sequence, kv head). `cluster` of them (by default as
     many as divide `splits`, up to 8) form a thread-block cluster and merge their
     partial results through each other's shared memory; the clusters' results
     (or, without clusters, every CTA's) go to a workspace, and the CTA that
     finishes a pair last merges them. `then_reads`: weights to ask into L2 for
-    the kernel that follows (see `gemm_skinny`). `balanced`: a range is 1/splits
-    of the LONGEST sequence's pages for every sequence, so that in a batch of
-    unequal lengths no CTA walks a long sequence alone."""
+    the kernel that follows (see `gemm_skinny`)."""
     _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
     n = kv_lens.numel()
     if cluster is None:
@@ -1257,7 +1263,7 @@ def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, n
           _dev(cu_tokens, "cu_tokens", torch.int32), _dev(kv_lens, "kv_lens", torch.int32),
           _dev(page_table, "page_table", torch.int32), page_table.shape[1], k_cache.data_ptr(),
           v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1), n, num_heads, num_kv_heads,
-          head_dim, float(scale), splits, stages, cluster, 1 if balanced else 0,
+          head_dim, float(scale), splits, stages, cluster,
           0 if ws_o is None else ws_o.data_ptr(), 0 if ws_ml is None else ws_ml.data_ptr(),
           0 if counters is None else counters.data_ptr(), *_prefetch_range(then_reads),
           _stream())

@@ -313,15 +313,14 @@ def test_attention_tensor_cores_single_tokens(ops, lens_q, lens_kv, A, Kh, D, sp
                                             ([70, 2000, 500, 65], 16, 2, 64), ([33, 190, 900], 6, 3, 32)])
 @pytest.mark.parametrize("splits", [2, 4, 8])
 def test_attention_single_tokens_of_unequal_lengths(ops, lens_kv, A, Kh, D, splits):
-    """Ranges cut by the longest sequence's pages: short sequences leave most
-    CTAs without a range, the longest uses them all; merged through the workspace."""
+    """Every sequence's own pages cut into ranges: the short ones leave CTAs without
+    a range (one page, eight ranges); merged through the workspace and in clusters."""
     lens_q = [1] * len(lens_kv)
     case, want = make_paged_case(lens_q, lens_kv, A, Kh, D, torch.bfloat16, seed=6, sharp=True)
-    for _ in range(2):  # the counters are back at zero for the second call
+    for cluster in (1, 1, None):  # the counters are back at zero for the second call
         out = torch.full_like(case["q"], 5.0)
         ops.attention_decode(case["q"], out, case["cu"], case["kv"], case["table"], case["k"],
-                             case["v"], A, Kh, D, 1.0 / math.sqrt(D), splits, 3, cluster=1,
-                             balanced=True)
+                             case["v"], A, Kh, D, 1.0 / math.sqrt(D), splits, 3, cluster=cluster)
         close(out, want, 3e-2, 1e-2)
 
 
