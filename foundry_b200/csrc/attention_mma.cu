@@ -534,10 +534,15 @@ attn_decode_kernel(const AttnParams p) {
     // iteration for a trip to L2.
     const int refill_page = next_page;
     if (pg + ST < pg1) next_page = pages[pg + ST];
-    if (pg + ST - 1 < pg1)  // refill the buffer that the previous iteration finished with
-      load_rows((pg - pg0 + ST - 1) % ST, refill_page);
-    cp_async_commit();
-    cp_async_wait<ST - 1>();  // all but the newest ST - 1 groups: page `pg` has landed
+    // The buffer that the previous iteration finished with is refilled once this
+    // page's score products have been issued: a warp issues in order, and the
+    // copies' address arithmetic then runs while the tensor cores work instead of
+    // in front of them.
+    auto refill = [&]() {
+      if (pg + ST - 1 < pg1) load_rows((pg - pg0 + ST - 1) % ST, refill_page);
+      cp_async_commit();
+    };
+    cp_async_wait<ST - 2>();  // all but the newest ST - 2 groups: page `pg` has landed
     if (pg == pg0) __syncthreads();  // the queries came from all warps
     else __syncwarp();               // the page's rows from this warp's lanes
     if (pg == pg0) {
@@ -568,20 +573,28 @@ attn_decode_kernel(const AttnParams p) {
       const __nv_bfloat16* tK = sK + st * 64 * D;
       const __nv_bfloat16* tV = sV + st * 64 * D;
       if constexpr (NARROW) {
-        // S^T [16 keys, 8 queries]: two accumulators take alternate k steps
-        float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+        // S^T [16 keys, 8 queries]: up to four accumulators take the k steps in
+        // turn, so that no product waits for more than one before it
+        constexpr int NS = KT >= 4 ? 4 : KT;
+        float sp[NS][4];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) sp[i][0] = sp[i][1] = sp[i][2] = sp[i][3] = 0.f;
 #pragma unroll
         for (int k = 0; k < KT; ++k) {
           uint32_t a[4];
           ldsm_x4(a, smem_u32(tK + Swz<D>::off(warp * 16 + (lane & 15), k * 16 + (lane >> 4) * 8)));
-          if (k & 1) mma_bf16(s2, a, qf[k][0], qf[k][1]);
-          else mma_bf16(s, a, qf[k][0], qf[k][1]);
+          mma_bf16(sp[k % NS], a, qf[k][0], qf[k][1]);
         }
+        refill();
         // s[e]: key g + 8 (e >> 1), query 2t + (e & 1)
+        float s[4];
         float mx[2] = {m[0], m[1]};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = (s[e] + s2[e]) * p.scale_log2;
+          float v = sp[0][e];
+#pragma unroll
+          for (int i = 1; i < NS; ++i) v += sp[i][e];
+          v *= p.scale_log2;
           if (key0 + g + (e >> 1) * 8 >= kv_len) v = -INFINITY;
           s[e] = v;
           mx[e & 1] = fmaxf(mx[e & 1], v);
@@ -602,11 +615,10 @@ attn_decode_kernel(const AttnParams p) {
           s[e] = pv;
           sum[e & 1] += pv;
         }
+        // l stays this lane's share of the sum (its own keys); the lanes' shares
+        // meet once, after the last page
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 4);
-          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 8);
-          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 16);
           l[r] = l[r] * corr[r] + sum[r];
           m[r] = mx[r];
         }
@@ -638,6 +650,7 @@ attn_decode_kernel(const AttnParams p) {
           mma_bf16(s[0], qf[k], b[0], b[1]);
           mma_bf16(s[1], qf[k], b[2], b[3]);
         }
+        refill();
         float mx[2] = {m[0], m[1]};
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -667,9 +680,7 @@ attn_decode_kernel(const AttnParams p) {
           }
         }
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-          sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        for (int r = 0; r < 2; ++r) {  // l: this lane's share of the sum, as in the narrow form
           l[r] = l[r] * corr[r] + sum[r];
           m[r] = mx[r];
         }
@@ -692,10 +703,24 @@ attn_decode_kernel(const AttnParams p) {
           mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
         }
       }
+    } else {
+      refill();
     }
   }
   cp_async_wait<0>();
   fb_prefetch_l2_slice(p.next, p.next_bytes);
+  // the lanes' shares of the sums meet: over the keys' lanes (g in the narrow form, t in the wide)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if constexpr (NARROW) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 4);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 8);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 16);
+    } else {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+  }
   __syncthreads();  // all warps are through with the page buffers
 
   // merge the four warps' (m, l, O) through shared memory (the page buffers are free now)

@@ -1188,7 +1188,8 @@ def decode_plan(pairs: int, pages: int, head_dim: int = 128, unequal: bool = Fal
     page_bytes = 2 * PAGE * head_dim * 2  # keys and values of one kv head
     if not unequal and pairs * page_bytes >= DECODE_PAGE_SECONDS * DECODE_STREAM_BYTES_PER_SECOND:
         return 1, 3
-    return max(1, min(DECODE_CLUSTER_MAX, pages, room)), 3
+    splits = max(1, min(DECODE_CLUSTER_MAX, pages, room))
+    return 1 << (splits.bit_length() - 1), 3  # clusters of 3, 5, 6 or 7 were slower than the power of two below
 
 
 TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prompt-attention kernel
