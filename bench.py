@@ -151,7 +151,11 @@ def time_decode(engine, slots, steps: int, warmup: int, blocks: int, sampler=Non
 
 def time_e2e(engine, slots, steps: int, warmup: int, blocks: int):
     """The public call a user makes for one decode step: host token ids in
-    (from pinned memory), host token ids out. Host clock, median block."""
+    (from pinned memory), host token ids out, every step; as the generation
+    loop calls it, saying that it will come back with the tokens it receives
+    (the step after is then started before this one's tokens are handed out;
+    not after a block's last step, so that a block runs exactly `steps`).
+    Host clock, median block."""
     import torch
     session = engine.decode_session(slots)
     tokens = [1] * len(slots)
@@ -161,8 +165,8 @@ def time_e2e(engine, slots, steps: int, warmup: int, blocks: int):
     for _ in range(blocks):
         torch.cuda.synchronize()
         started = time.perf_counter()
-        for _ in range(steps):
-            tokens = session.step_host(tokens)
+        for i in range(steps):
+            tokens = session.step_host(tokens, more=i + 1 < steps)
         torch.cuda.synchronize()
         out.append(((time.perf_counter() - started) / steps,))
     return median_block(out)[0], session.h2d_bytes_per_step, session.d2h_bytes_per_step

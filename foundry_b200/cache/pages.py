@@ -155,6 +155,17 @@ class SlotTable:
             group.grow(slot, length)
         self.length[slot] = length
 
+    def forget_from(self, slot: int, length: int) -> None:
+        """The slot's tokens from `length` on are given up: a step that was run
+        on a guess and is not wanted leaves the sequence as it was before it.
+        The slot keeps its pages (the next step writes the same rows again)."""
+        if not self.slots.is_held(slot):
+            raise CacheMisuse(f"slot {slot} is not held")
+        if not 0 <= length <= self.length[slot]:
+            raise CacheMisuse(f"slot {slot} holds {self.length[slot]} tokens, it cannot forget "
+                              f"from {length} on")
+        self.length[slot] = length
+
     def close(self, slot: int) -> None:
         if not self.slots.is_held(slot):
             raise CacheMisuse(f"slot {slot} is released but not held")

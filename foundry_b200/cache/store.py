@@ -22,7 +22,7 @@ from typing import Dict, List, Mapping, Optional, Sequence, Tuple, Union
 
 import torch
 
-from .pages import PAGE, CacheFull, GroupPages, SlotTable, pages_for
+from .pages import PAGE, CacheFull, CacheMisuse, GroupPages, SlotTable, pages_for
 
 
 @dataclass(frozen=True)
@@ -155,6 +155,14 @@ class SequenceCache:
                 f"{[g.pages.pool.count for g in self.groups]})")
         for slot, length in growth.items():
             self.table.grow(slot, length)
+
+    def forget_from(self, slot: int, length: int) -> None:
+        """Give up the slot's tokens from `length` on (see `SlotTable.forget_from`).
+        Only keys and values can be forgotten: state of fixed size has been
+        overwritten by the step, so a cache that holds any refuses."""
+        if self.state:
+            raise CacheMisuse("per-sequence state cannot be taken back a step")
+        self.table.forget_from(slot, length)
 
     def step_token_limit(self) -> Optional[int]:
         """The most tokens one sequence may bring in one step, or None for no

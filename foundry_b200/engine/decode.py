@@ -14,6 +14,15 @@ padding changes no result. The chosen token of each row is written where the
 next step reads its input, so steps can follow one another without the host
 seeing the tokens (`DecodeSession.step`), or with the host feeding and reading
 them every step (`step_host`, which is what generation uses).
+
+A host that reads every step's tokens before it decides on the next leaves the
+device idle while it decides. `step_host(..., more=True)` therefore starts the
+step after this one before it hands this one's tokens out, on the guess that
+the same rows go on with exactly those tokens (which is what a generation loop
+does until a row ends). The next call finds its step already running. If the
+guess was wrong (another token, a row less) the step is taken back:
+`cancel_ahead` gives up the one position it added to each sequence, and the
+rows it wrote are written again by the step that is wanted.
 """
 from __future__ import annotations
 
@@ -149,6 +158,8 @@ class DecodeSession:
         self.runner: Optional[DecodeRunner] = None
         self.h2d_bytes_per_step = 0
         self.d2h_bytes_per_step = 0
+        self._ahead: Optional[dict] = None  # the step that was started on a guess
+        self._read = torch.cuda.Event()     # behind the copy of a step's tokens to the host
 
     def _prepare(self) -> DecodeRunner:
         """Reserve one more token per sequence and refresh the host buffers."""
@@ -225,33 +236,98 @@ class DecodeSession:
 
     def set_tokens(self, tokens: Sequence[int]) -> None:
         """Device-resident stepping (`step`) starts from these input tokens."""
+        self.cancel_ahead()
         self._pending_tokens = list(tokens)
 
     def step(self) -> None:
         """One step whose input tokens are the previous step's choices, which
         stay on the device."""
-        runner = self._prepare()
-        self._upload(runner, getattr(self, "_pending_tokens", None))
+        self.cancel_ahead()
+        self._launch(getattr(self, "_pending_tokens", None))
         self._pending_tokens = None
-        runner.run()
-        self.counts = [c + 1 for c in self.counts]
 
-    def step_host(self, tokens: Sequence[int]) -> List[int]:
-        """One step fed from the host; returns the chosen tokens on the host."""
+    def _launch(self, tokens: Optional[Sequence[int]]) -> DecodeRunner:
         runner = self._prepare()
         self._upload(runner, tokens)
         runner.run()
+        self.counts = [c + 1 for c in self.counts]
+        return runner
+
+    # ------------------------------------------------------- a step ahead
+    def has_ahead(self) -> bool:
+        return self._ahead is not None
+
+    def _may_run_ahead(self) -> bool:
+        """A step may be started on a guess if it can be taken back and cannot
+        fail: no state of fixed size, a step that never reads the host, room in
+        the model's positions and in the cache."""
+        engine, cache = self.engine, self.engine.cache
+        if cache.state or not engine.model.replay_safe() or not engine.use_graphs:
+            return False
+        lengths = [cache.length(s) for s in self.slots]
+        if any(n + 1 > engine.spec.max_positions for n in lengths):
+            return False
+        return cache.table.can_grow({s: n + 1 for s, n in zip(self.slots, lengths)})
+
+    def cancel_ahead(self) -> None:
+        """Take back the step that was started on a guess, if there is one: every
+        sequence that is still the one it was gives up the position the step
+        added (a slot that was closed meanwhile, or closed and opened again,
+        is left alone)."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is None:
+            return
+        table = self.engine.cache.table
+        for slot, epoch, length in ahead["slots"]:
+            if table.slots.is_held(slot) and table.epoch[slot] == epoch \
+                    and table.length[slot] == length + 1:
+                self.engine.cache.forget_from(slot, length)
+        self.counts = list(ahead["counts"])
+
+    def step_host(self, tokens: Sequence[int], more: bool = False,
+                  counts: Optional[Sequence[int]] = None) -> List[int]:
+        """One step fed from the host; returns the chosen tokens on the host.
+        `counts`: how many tokens each row has generated before this step
+        (sampling only). `more`: the caller expects to come back with the same
+        rows and the tokens returned here, so the step after this one is
+        started before this one's tokens are handed out."""
+        tokens = [int(t) for t in tokens]
+        ahead = self._ahead
+        if ahead is not None and (ahead["tokens"] != tokens or
+                                  (counts is not None and list(counts) != ahead["counts"])):
+            self.cancel_ahead()
+            ahead = None
+        self._ahead = None
+        if ahead is None:
+            if counts is not None:
+                self.counts = list(counts)
+            runner = self._launch(tokens)
+        else:
+            runner = self.runner  # the step for these tokens is already on its way
         n = len(self.slots)
         runner.tokens_host[:n].copy_(runner.next_tokens[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        self._read.record()
+        guess = None
+        if more and self._may_run_ahead():
+            table = self.engine.cache.table
+            guess = {"slots": [(s, table.epoch[s], table.length[s]) for s in self.slots],
+                     "counts": list(self.counts)}
+            self._launch(None)  # its input tokens are where this step left them
+        self._read.synchronize()
         ops.raise_on_device_failure()
         self.d2h_bytes_per_step = n * 4
-        self.counts = [c + 1 for c in self.counts]
-        return runner.tokens_host[:n].tolist()
+        out = runner.tokens_host[:n].tolist()
+        if guess is not None:
+            guess["tokens"] = out
+            self._ahead = guess
+        return out
 
     def logits(self) -> torch.Tensor:
         """float32 logits [rows, vocab] of the last step (a buffer the next step
         reuses). Waits for the step and raises if one of its kernels gave up."""
+        if self._ahead is not None:
+            raise RuntimeError("a step was started ahead: its logits have replaced the last "
+                               "step's (use step_host(..., more=False) where logits are read)")
         torch.cuda.current_stream().synchronize()
         ops.raise_on_device_failure()
         return self.runner.logits[:len(self.slots)]

@@ -116,6 +116,12 @@ class Engine:
     def close_sequence(self, slot: int) -> None:
         self.cache.close_sequence(slot)
 
+    def _settle(self) -> None:
+        """Take back a decode step that the engine's session started on a guess
+        (`DecodeSession.step_host(more=True)`), before anything else runs."""
+        if self._session is not None:
+            self._session.cancel_ahead()
+
     def free_slots(self) -> int:
         return self.cache.table.slots.free
 
@@ -133,7 +139,8 @@ class Engine:
         """Run the given tokens from the cache; float32 logits [wanted, vocab]
         in the order of `steps` and of each `want`."""
         if self._is_decode(steps):
-            return self._decode(steps, SamplingParams(), None, None)[1].clone()
+            return self._decode(steps, SamplingParams(), None, None)[1].logits().clone()
+        self._settle()
         limit = self.cache.step_token_limit()
         if limit is not None and any(len(s.tokens) > limit for s in steps):
             return self._step_in_portions(steps, limit)
@@ -183,11 +190,14 @@ class Engine:
         return torch.stack(ordered)
 
     def step_select(self, steps: Sequence[SequenceStep], params: SamplingParams,
-                    keys: Sequence[int], counts: Sequence[int]) -> List[int]:
+                    keys: Sequence[int], counts: Sequence[int], more: bool = False) -> List[int]:
         """A step whose wanted logits are turned into tokens on the device;
-        only the token ids cross to the host."""
+        only the token ids cross to the host. `more`: the caller expects to
+        come back with the same sequences, each with the token returned here
+        (a generation loop whose rows all go on unless a stop token ends one);
+        single-token steps then start the next step before they return."""
         if self._is_decode(steps):
-            return self._decode(steps, params, keys, counts)[0]
+            return self._decode(steps, params, keys, counts, more)[0]
         logits = self.step(steps)
         tokens = self.sampler.select(logits, params, keys, counts)
         return tokens.tolist()
@@ -196,9 +206,9 @@ class Engine:
     def _is_decode(steps: Sequence[SequenceStep]) -> bool:
         return len(steps) > 0 and all(len(s.tokens) == 1 and list(s.want) == [0] for s in steps)
 
-    def _decode(self, steps, params, keys, counts):
+    def _decode(self, steps, params, keys, counts, more: bool = False):
         """One token per sequence, through a `DecodeSession` (fixed buffers,
-        replayed graph); returns (host tokens, logits buffer)."""
+        replayed graph); returns (host tokens, the session)."""
         slots = [s.slot for s in steps]
         if len(set(slots)) != len(slots):
             raise ValueError("a slot appears twice in one step")
@@ -212,16 +222,16 @@ class Engine:
         session = self._session
         if session is None or session.slots != slots or session.sampling != params \
                 or session.keys != keys:
+            self._settle()
             session = self._session = DecodeSession(self, slots, params, keys, counts)
-        elif counts is not None:
-            session.counts = list(counts)
-        tokens = session.step_host([int(s.tokens[0]) for s in steps])
-        return tokens, session.logits()
+        tokens = session.step_host([int(s.tokens[0]) for s in steps], more, counts)
+        return tokens, session
 
     # -------------------------------------------------------------- decode
     def decode_session(self, slots: Sequence[int], sampling: SamplingParams = SamplingParams(),
                        keys: Optional[Sequence[int]] = None,
                        counts: Optional[Sequence[int]] = None) -> "DecodeSession":
+        self._settle()
         return DecodeSession(self, slots, sampling, keys, counts)
 
     def decode_runner(self, bucket: int, width: int, unequal: bool = False) -> "DecodeRunner":

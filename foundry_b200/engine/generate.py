@@ -12,7 +12,9 @@ until all rows are done, mod.rs:70-88); more requests than fit are run as
 further batches; the next token may be sampled.
 
 The loop decides on the host and only talks to a `StepBackend`, so its
-decisions are tested without a GPU.
+decisions are tested without a GPU. It tells the backend when it expects to
+come back with the same rows and the tokens it is about to receive (`more`),
+so that a backend may have that step running while the loop decides.
 """
 from __future__ import annotations
 
@@ -53,7 +55,7 @@ class StepBackend(Protocol):
     def capacity_tokens(self) -> int: ...
     def max_positions(self) -> int: ...
     def step_select(self, steps: Sequence[SequenceStep], params: SamplingParams,
-                    keys: Sequence[int], counts: Sequence[int]) -> List[int]: ...
+                    keys: Sequence[int], counts: Sequence[int], more: bool = False) -> List[int]: ...
 
 
 def is_stopped(row: Sequence[int], eos_token_ids: Sequence[int]) -> bool:
@@ -130,7 +132,10 @@ def _run_batch(backend, batch, prompts, max_new_tokens, stops, sampling, result)
             started = time.perf_counter()
             steps = [SequenceStep(slot_of[r], [result.token_ids[r][-1]], [0]) for r in live]
             counts = [len(result.token_ids[r]) for r in live]
-            tokens = backend.step_select(steps, sampling, live, counts)
+            # unless a stop token ends a row, the same rows come back with the tokens
+            # of this step: the backend may start that step before it returns
+            more = all(c + 1 < max_new_tokens for c in counts)
+            tokens = backend.step_select(steps, sampling, live, counts, more)
             result.decode_steps.append(time.perf_counter() - started)
             live = _append(backend, live, tokens, slot_of, stops, max_new_tokens, result)
     finally:

@@ -143,3 +143,26 @@ def test_a_window_ring_limits_the_tokens_of_one_step():
                     assert not ok
     no_window = SequenceCache({0: KVRequest(2, 16)}, 1024, 2, torch.float32, torch.device("cpu"))
     assert no_window.step_token_limit() is None
+
+
+def test_a_step_can_be_taken_back():
+    """`forget_from` gives up a slot's last tokens and keeps its pages; it cannot
+    grow a slot, touch a free one, or take back state of fixed size."""
+    from foundry_b200.cache.pages import CacheMisuse, GroupPages, SlotTable
+    table = SlotTable(2, [GroupPages(4)])
+    slot = table.open()
+    table.grow(slot, 64)
+    table.grow(slot, 65)
+    pages = list(table.groups[0].pages(slot))
+    table.forget_from(slot, 64)
+    assert table.length[slot] == 64 and table.groups[0].pages(slot) == pages
+    table.grow(slot, 65)  # the same page serves again
+    assert table.groups[0].pages(slot) == pages
+    with pytest.raises(CacheMisuse):
+        table.forget_from(slot, 66)
+    with pytest.raises(CacheMisuse):
+        table.forget_from(slot, -1)
+    table.close(slot)
+    with pytest.raises(CacheMisuse):
+        table.forget_from(slot, 0)
+    table.check()

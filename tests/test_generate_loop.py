@@ -19,6 +19,7 @@ class ScriptedBackend:
         self.slots = FreeList(slots, "slot")
         self.length = {}
         self.log = []
+        self.more = []  # what the loop said about coming back, a step
 
     def open_sequence(self):
         (s,) = self.slots.take(1)
@@ -44,8 +45,9 @@ class ScriptedBackend:
     def max_positions(self):
         return self.positions
 
-    def step_select(self, steps, params, keys, counts):
+    def step_select(self, steps, params, keys, counts, more=False):
         assert len({s.slot for s in steps}) == len(steps)
+        self.more.append(more)
         for s in steps:
             assert self.slots.is_held(s.slot)
             self.length[s.slot] += len(s.tokens)
@@ -72,6 +74,9 @@ def test_unequal_prompts_rows_end_earlier_and_keep_their_stop_token():
     assert backend.log[3] == [(2, [32], 3)]
     assert len(backend.log) == 4 and len(out.decode_steps) == 3
     assert backend.slots.free == 4 and backend.length == {}
+    # the loop expects to come back with the same rows while none reaches its limit
+    # with the step's token (a stop token it cannot foresee); never for prompts
+    assert backend.more == [False, True, True, False]
 
 
 def test_the_prompt_step_gives_the_first_token_and_zero_tokens_touch_nothing():
@@ -130,10 +135,10 @@ def test_refusals():
 
 def test_slots_go_back_when_a_step_fails():
     class Failing(ScriptedBackend):
-        def step_select(self, steps, params, keys, counts):
+        def step_select(self, steps, params, keys, counts, more=False):
             if len(self.log) == 1:
                 raise RuntimeError("device failure")
-            return super().step_select(steps, params, keys, counts)
+            return super().step_select(steps, params, keys, counts, more)
     backend = Failing({0: [1, 2, 3], 1: [4, 5, 6]})
     with pytest.raises(RuntimeError):
         generate(backend, [[1], [2]], 3)

@@ -59,6 +59,81 @@ def test_greedy_generation_equals_the_plain_model(tiny_folders, name):
     assert engine.cache.table.slots.held == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_started_ahead_changes_no_token(tiny_folders, dtype):
+    """`step_host(more=True)` starts the next step before it returns. Fed what
+    it returned, the tokens are those of steps run one by one (bit for bit: the
+    same kernels on the same inputs); fed something else, or with a row less,
+    the step is taken back and the tokens are those of an engine that never
+    ran ahead. Across a page boundary, sampled as well as greedy."""
+    from foundry_b200 import SamplingParams
+    from foundry_b200.engine import SequenceStep
+    name = "tiny_b"
+    cfg, _ = plain.read_model(tiny_folders[name])
+    V = cfg["vocab_size"]
+    prompts = [tiny.random_tokens(900 + i, n, V) for i, n in enumerate((61, 5, 33))]
+
+    def run(ahead, sampling):
+        engine = engine_for(tiny_folders[name], dtype)
+        slots = [engine.open_sequence() for _ in prompts]
+        tokens = engine.step_select([SequenceStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)],
+                                    sampling, [0, 1, 2], [0, 0, 0])
+        session = engine.decode_session(slots, sampling, [0, 1, 2], [1, 1, 1])
+        out, count = [tokens], 1
+        for i in range(12):
+            if i == 5:
+                tokens = [(t + 1) % V for t in tokens]  # not what the step ahead was given
+            tokens = session.step_host(tokens, more=ahead, counts=[count] * 3)
+            assert session.has_ahead() == ahead
+            out.append(tokens)
+            count += 1
+        # a row less: the engine's own session, through the loop's entry point
+        session.cancel_ahead()
+        lengths = [engine.cache.length(s) for s in slots]
+        assert lengths == [len(p) + 12 for p in prompts]
+        current = dict(enumerate(out[-1]))
+        for rows in ([0, 1, 2], [0, 2], [0, 2], [2]):
+            steps = [SequenceStep(slots[r], [current[r]], [0]) for r in rows]
+            got = engine.step_select(steps, sampling, rows, [count] * len(rows), more=ahead)
+            current.update(zip(rows, got))
+            out.append(list(got))
+            count += 1
+        engine._settle()
+        assert [engine.cache.length(s) for s in slots] == \
+            [len(prompts[0]) + 15, len(prompts[1]) + 13, len(prompts[2]) + 16]
+        # logits after steps ahead: the step function takes a matching step over,
+        # or takes the guess back
+        logits = engine.step([SequenceStep(slots[2], [3], [0])])
+        for s in slots:
+            engine.close_sequence(s)
+        engine.cache.table.check()
+        return out, logits.cpu()
+
+    for sampling in (SamplingParams(), SamplingParams(temperature=0.9, seed=5)):
+        plain_out, plain_logits = run(False, sampling)
+        ahead_out, ahead_logits = run(True, sampling)
+        assert ahead_out == plain_out
+        assert torch.equal(ahead_logits, plain_logits)
+
+
+def test_generation_ahead_with_stop_tokens_equals_the_plain_model(tiny_folders):
+    """Rows end at different steps (a stop token that the loop cannot foresee,
+    and lengths): each time the step that was started for all rows is taken
+    back, and the survivors' tokens stay those of the plain model."""
+    name = "tiny_a"
+    cfg, w = plain.read_model(tiny_folders[name])
+    prompts = [tiny.random_tokens(80 + i, n, cfg["vocab_size"]) for i, n in enumerate((9, 64, 3, 30))]
+    free_run = [plain.greedy_generate(cfg, w, p, 12) for p in prompts]
+    stops = [free_run[0][3], free_run[2][7]]
+    want = [plain.greedy_generate(cfg, w, p, 12, eos=stops) for p in prompts]
+    assert len({len(t) for t in want}) > 1  # rows do end at different steps
+    engine = engine_for(tiny_folders[name], "float32")
+    out = engine.generate(prompts, 12, eos_token_id=stops)
+    assert out.token_ids == want
+    assert engine.cache.table.slots.held == 0
+    engine.cache.table.check()
+
+
 def test_stop_tokens_early_rows_and_slot_reuse(tiny_folders):
     """Make a stop token of what the plain model generates third for one
     prompt: that row ends there (keeping the token) while the others go on,
