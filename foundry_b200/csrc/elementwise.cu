@@ -60,6 +60,23 @@ __device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
   const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
   return make_float4(a.x, a.y, b.x, b.y);
 }
+// Four elements as they lie in memory (bfloat16: two registers instead of four
+// while they wait for their use), and their float32 values.
+template <typename TD> struct Raw4;
+template <> struct Raw4<float> { float4 bits; };
+template <> struct Raw4<__nv_bfloat16> { uint2 bits; };
+template <typename TD>
+__device__ __forceinline__ Raw4<TD> load_raw4(const TD* p) {
+  Raw4<TD> r;
+  r.bits = *reinterpret_cast<const decltype(r.bits)*>(p);
+  return r;
+}
+__device__ __forceinline__ float4 widen(const Raw4<float>& r) { return r.bits; }
+__device__ __forceinline__ float4 widen(const Raw4<__nv_bfloat16>& r) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.bits.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.bits.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
 template <typename TO>
 __device__ __forceinline__ void store4(TO* p, float4 v);
 template <>
@@ -87,6 +104,32 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* delt
   float* x = resid + row;
   float4 v[ITEMS];
   float ss = 0.f;
+  if (delta != nullptr && planes == 1) {
+    // One plane (every prompt step): the loads of all of a thread's groups go out
+    // before the first store. `delta` is not known to be another buffer than
+    // `resid`, so inside one loop a group's store would hold back the next group's
+    // loads, and a row would cost a round trip to memory per group.
+    Raw4<TD> raw[ITEMS];
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int i = (threadIdx.x + it * blockDim.x) * 4;
+      v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < H) {
+        v[it] = load4<float>(x + i);
+        raw[it] = load_raw4<TD>(delta + row + i);
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int i = (threadIdx.x + it * blockDim.x) * 4;
+      if (i < H) {
+        const float4 add = widen(raw[it]);
+        v[it].x += add.x; v[it].y += add.y; v[it].z += add.z; v[it].w += add.w;
+        store4<float>(x + i, v[it]);
+        ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
+      }
+    }
+  } else {
 #pragma unroll
   for (int it = 0; it < ITEMS; ++it) {
     const int i = (threadIdx.x + it * blockDim.x) * 4;
@@ -112,6 +155,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* delt
       }
       ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
     }
+  }
   }
   ss = fb_block_sum(ss, scratch);
   const float r = 1.0f / sqrtf(ss * inv_h + eps);
