@@ -1165,25 +1165,22 @@ DECODE_STREAM_BYTES_PER_SECOND = 6.5e12
 
 def decode_plan(pairs: int, pages: int, head_dim: int = 128, unequal: bool = False):
     """(splits, page buffers) of decode attention for `pairs` (sequence, kv head)
-    pairs of up to `pages` cache pages, as measured on B200. Three page buffers per
-    CTA (two pages on their way while one is multiplied); 2 CTAs of head size 128
-    fit an SM, 4 of 64 or less. Ranges are split while all CTAs stay resident at
-    once (a second round of CTAs cost 10 us a call), at most eightfold (one
-    cluster). Sequences of equal lengths are not split at all once their pairs
-    are many enough for memory to be the limit: a CTA walks a page in
-    DECODE_PAGE_SECONDS, so `pairs` CTAs ask for pairs * page bytes in that time,
-    and where that exceeds what memory delivers, more CTAs only add merges
-    (batch 16 of 8 kv heads of 128: 32.9 us unsplit, 34.6 in two ranges). With
-    unequal lengths the longest sequence's CTA is what the batch waits for, and
-    ranges are split as far as residency allows (32 sequences of 400 to 4,000
-    tokens, 8 kv heads of 64: 48.7 us unsplit, 34.6 in two ranges). A long context
-    with few pairs takes several clusters, whose results meet in the workspace."""
+    pairs of up to `pages` cache pages. Three page buffers per CTA (two pages on
+    their way while one is multiplied); 2 CTAs of head size 128 fit an SM, 4 of
+    64 or less. Ranges are split while all CTAs stay resident at once (a second
+    round of CTAs costs more than it gains), at most eightfold (one cluster).
+    Sequences of equal lengths are not split at all once their pairs are many
+    enough for memory to be the limit: a CTA walks a page in DECODE_PAGE_SECONDS,
+    so `pairs` CTAs ask for pairs * page bytes in that time, and where that
+    exceeds what memory delivers, more CTAs only add merges. With unequal lengths
+    the longest sequence's CTA is what the batch waits for, and ranges are split
+    as far as residency allows. A long context with few pairs takes several
+    clusters, whose results meet in the workspace."""
     resident = sm_count() * min(4, 256 // max(head_dim, 1))
     room = resident // max(pairs, 1)
     if room >= 16 and pages >= 160:
-        # clusters of 8 while a CTA keeps 4 pages or more; the second merge costs
-        # 3 to 4 us, which pays from about 10 K tokens on (batch 1 at 16 K tokens:
-        # 26.7 us with 8 shares, 19.4 with 32; at 4 K: 10.6 against 12.9)
+        # clusters of 8 while a CTA keeps 4 pages or more; the second merge pays
+        # from about 10 K tokens on
         return min(room // 8 * 8, max(16, pages // 4 // 8 * 8)), 3
     page_bytes = 2 * PAGE * head_dim * 2  # keys and values of one kv head
     if not unequal and pairs * page_bytes >= DECODE_PAGE_SECONDS * DECODE_STREAM_BYTES_PER_SECOND:
