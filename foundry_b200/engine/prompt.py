@@ -2,10 +2,9 @@
 
 A prompt step of the 3B model is some 230 kernel launches; from Python that is
 4 to 5 ms of host time, more than the GPU needs for a prompt of up to a few
-hundred tokens (measured: 20 tokens 4.0 -> 2.3 ms, 128 tokens 4.0 -> 2.65 ms,
-129 tokens 4.6 -> 3.6 ms, 300 tokens 4.6 -> 4.4 ms, 512 tokens 4.7 -> 4.5 ms;
-at 1,000 tokens 7.1 -> 6.8 ms, where the buffers a captured step keeps are no
-longer worth it). So steps of up to `PROMPT_GRAPH_TOKENS` tokens run like the
+hundred tokens (the gain shrinks with the step: at 20 tokens the step takes
+half the time, at 512 a few per cent less, and from about 1,000 tokens on the
+buffers that a captured step keeps are no longer worth it). So steps of up to `PROMPT_GRAPH_TOKENS` tokens run like the
 single-token steps (decode.py): padded up to a bucket (tokens, sequences,
 page-table width, wanted rows), described by fixed device buffers that one copy
 from pinned memory refreshes, captured once per bucket and replayed.
