@@ -427,6 +427,11 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
 // epilogue 1 fuses SiLU(gate) * up: the feature operand's rows are (gate, up)
 // pairs and `out` is [tokens, features / 2] bf16; the stride of the feature
 // dimension must be 1 and then indexes pairs.
+static int run_gemm_tc(const void* a, long long lda, const void* b, long long ldb, int bn,
+                       int splits, int persistent, const GemmParams& p, void* workspace,
+                       long long workspace_bytes, int* counters, int counters_len,
+                       int share_min_kblocks, cudaStream_t stream);
+
 FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, long long ldb,
                       int rows_b, int K, void* out, long long stride_a, long long stride_b,
                       int out_f32, int bn, int splits, long long split_stride, int epilogue,
@@ -467,6 +472,18 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
   p.rows = FbRowExtras{scale_ss, scale_count, scale_stride,
                        scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps, resid, ldr, gamma,
                        (__nv_bfloat16*)xg, ldxg, ss_out, ss_stride};
+  p.rope = FbRopeExtras{};
+  return run_gemm_tc(a, lda, b, ldb, bn, splits, persistent, p, workspace, workspace_bytes,
+                     counters, counters_len, share_min_kblocks, stream);
+}
+
+// The launch of a product whose parameters are complete: the form and the tile width
+// pick the kernel.
+static int run_gemm_tc(const void* a, long long lda, const void* b, long long ldb, int bn,
+                       int splits, int persistent, const GemmParams& p, void* workspace,
+                       long long workspace_bytes, int* counters, int counters_len,
+                       int share_min_kblocks, cudaStream_t stream) {
+  const int rows_a = p.rows_a, rows_b = p.rows_b, K = p.K;
   if (persistent == 2) {
     // two SMs per tile (gemm_tcgen05_pair.cu)
     FB_REQUIRE(splits == 1, "gemm_tc: the paired form takes one split");
@@ -506,6 +523,58 @@ FB_API int fb_gemm_tc(const void* a, long long lda, int rows_a, const void* b, l
     case 256: return launch<256>(ma, mb, p, grid, stream);
     default: return fb_fail(1, "gemm_tc: tile height %d is not one of 16, 32, 64, 128, 256", bn);
   }
+}
+
+// The fused q/k/v projection of many tokens: x [T, K] (row stride ldx) times
+// w [(A + 2 Kh) * D, K]^T with rotation and cache write in the epilogue (see
+// FbRopeExtras), an optional row scale of x as in fb_gemm_tc. `cs` comes from
+// fb_rope_table. D must be a multiple of 32 (a thread's 32 consecutive features
+// lie in one head) and the rotation pairs neighbouring features.
+FB_API int fb_gemm_tc_rope(const void* x, long long ldx, int T, const void* w, long long ldw, int K,
+                           int bn, int persistent, void* workspace, long long workspace_bytes,
+                           int* counters, int counters_len, int share_min_kblocks,
+                           const float* scale_ss, int scale_count, int scale_stride, int scale_dim,
+                           float scale_eps, const void* cs, int half, const int* positions,
+                           const int* seq_of_token, const int* page_table, int max_pages,
+                           int ring_pages, void* k_cache, void* v_cache, long long page_stride,
+                           long long head_stride, int A, int Kh, int D, int write_cache,
+                           void* q_out, long long ldq, cudaStream_t stream) {
+  FB_REQUIRE(T > 0 && K > 0 && A > 0 && Kh > 0 && D > 0, "gemm_tc_rope: bad sizes");
+  FB_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)x % 16) == 0 &&
+                 ((uintptr_t)w % 16) == 0,
+             "gemm_tc_rope: K, the row strides and the operands must keep 16-byte alignment");
+  FB_REQUIRE(D % 32 == 0 && half >= 0 && 2 * half <= D,
+             "gemm_tc_rope: head size %d must be a multiple of 32 and hold the rotary width %d", D,
+             2 * half);
+  FB_REQUIRE(half == 0 || (cs != nullptr && ((uintptr_t)cs % 8) == 0),
+             "gemm_tc_rope: the table of cos and sin is missing or misaligned");
+  FB_REQUIRE(q_out != nullptr && ldq % 8 == 0 && ldq >= (long long)A * D &&
+                 ((uintptr_t)q_out % 16) == 0,
+             "gemm_tc_rope: the query rows must be 16-byte aligned with a stride of %d or more",
+             A * D);
+  FB_REQUIRE(!write_cache || (k_cache && v_cache && page_table && page_stride % 8 == 0 &&
+                              head_stride % 8 == 0 && ((uintptr_t)k_cache % 16) == 0 &&
+                              ((uintptr_t)v_cache % 16) == 0),
+             "gemm_tc_rope: the cache is missing or its strides break 16-byte alignment");
+  FB_REQUIRE(positions && seq_of_token, "gemm_tc_rope: positions and sequence indices are missing");
+  bind_status_mirror(stream);
+  const int total_kb = (K + BK - 1) / BK;
+  GemmParams p;
+  p.rows_a = T; p.rows_b = (write_cache ? A + 2 * Kh : A) * D; p.K = K;  // w holds only the rows that are wanted
+  p.kblocks_per_split = total_kb;
+  p.stride_a = ldq; p.stride_b = 1; p.split_stride = 0;
+  p.out = q_out; p.out_f32 = 0; p.epilogue = 3;
+  p.constant_operand = 2;
+  p.full_tiles = 0; p.tail_splits = 1; p.tail_kblocks = total_kb; p.partial = nullptr;
+  p.tail_counters = nullptr;
+  p.rows = FbRowExtras{scale_ss, scale_count, scale_stride,
+                       scale_dim > 0 ? 1.0f / (float)scale_dim : 0.f, scale_eps, nullptr, 0,
+                       nullptr, nullptr, 0, nullptr, 0};
+  p.rope = FbRopeExtras{(const float2*)cs, half, positions, seq_of_token, page_table, max_pages,
+                        ring_pages, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_stride,
+                        head_stride, A, Kh, D, write_cache, (__nv_bfloat16*)q_out, ldq};
+  return run_gemm_tc(x, ldx, w, ldw, bn, 1, persistent, p, workspace, workspace_bytes, counters,
+                     counters_len, share_min_kblocks, stream);
 }
 
 // Reads and clears the device-side status: 0 when no wait ever ran out, else

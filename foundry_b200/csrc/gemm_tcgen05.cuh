@@ -27,6 +27,27 @@ struct FbRowExtras {
   int ss_stride;
 };
 
+// Epilogue 3, for the fused q/k/v projection with tokens as the A rows: feature
+// j is element j % D of head j / D (A query heads, Kh key heads, Kh value
+// heads). Queries and keys are rotated over neighbouring features (2i, 2i + 1)
+// by frequency i with the cos and sin of `cs`; queries go to `q_out`, keys and
+// values into the paged cache (rope_cache.cu has the formulas and the layout).
+struct FbRopeExtras {
+  const float2* cs;        // [half, rows_a]: (cos, sin) of frequency and token (a warp's 32
+                           // tokens read one frequency's angles as 256 contiguous bytes)
+  int half;                // rotary width / 2
+  const int* positions;    // [rows_a]
+  const int* seq_of_token; // [rows_a], -1: padding (nothing is written for it)
+  const int* page_table;   // [sequences, max_pages]
+  int max_pages, ring_pages;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  long long page_stride, head_stride;
+  int A, Kh, D, write_cache;
+  __nv_bfloat16* q_out;    // [rows_a, A * D], row stride ldq
+  long long ldq;
+};
+
 struct FbGemmParams {
   int rows_a, rows_b, K;
   int kblocks_per_split;      // K blocks of BK each CTA of a tile walks
@@ -37,7 +58,9 @@ struct FbGemmParams {
   int constant_operand;       // 1: A holds constants (weights), 2: B does, 0: neither
   int epilogue;               // 0: store D; 1: SiLU(gate) * up over interleaved feature pairs;
                               // 2: residual add in front of a norm (`rows`)
+                              // 3: rotation and cache write of a q/k/v projection (`rope`)
   FbRowExtras rows;
+  FbRopeExtras rope;
   // paired form only: the tiles of the last, partly filled round are shared along K
   int full_tiles;             // tiles [0, full_tiles) are computed whole
   int tail_splits;            // K shares of every later tile (1: whole too)
@@ -209,6 +232,59 @@ __device__ __forceinline__ float sink_chunk(const GemmParams& p, const float (&v
   return ss;
 }
 
+// Epilogue 3 for CHUNK consecutive features (j0 ..) of token i. The launcher
+// makes sure that a chunk lies inside one head (D is a multiple of CHUNK) and
+// that every store is 16 bytes on a 16-byte boundary.
+template <int CHUNK>
+__device__ __forceinline__ void rope_chunk(const GemmParams& p, float (&v)[CHUNK], long long i,
+                                           long long j0) {
+  const FbRopeExtras& r = p.rope;
+  if (i >= p.rows_a || j0 >= p.rows_b) return;
+  const int seq = r.seq_of_token[i];
+  if (seq < 0) return;  // padding token
+  const int head = (int)(j0 / r.D), e0 = (int)(j0 - (long long)head * r.D);
+  if (head >= r.A && !r.write_cache) return;  // keys and values are not wanted
+  if (head < r.A + r.Kh && e0 < 2 * r.half) {
+    // pairs (e0 + 2q, e0 + 2q + 1) turn by frequency e0 / 2 + q while they lie inside the rotary width
+    const float2* cs = r.cs + (size_t)(e0 >> 1) * p.rows_a + i;
+    float2 c[CHUNK / 2];
+#pragma unroll
+    for (int q = 0; q < CHUNK / 2; ++q)  // all loads go out before the first is used
+      c[q] = e0 + 2 * q < 2 * r.half ? __ldg(cs + (size_t)q * p.rows_a) : make_float2(1.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < CHUNK / 2; ++q) {
+      const float a = v[2 * q], b = v[2 * q + 1];
+      v[2 * q] = a * c[q].x - b * c[q].y;
+      v[2 * q + 1] = b * c[q].x + a * c[q].y;
+    }
+  }
+  __nv_bfloat16* dst;
+  if (head < r.A) {
+    dst = r.q_out + i * r.ldq + j0;
+  } else {
+    const int pos = r.positions[i];
+    int lp = pos / FB_PAGE;
+    if (r.ring_pages > 0) lp %= r.ring_pages;
+    const long long row = (long long)r.page_table[(size_t)seq * r.max_pages + lp] * r.page_stride +
+                          (long long)(pos % FB_PAGE) * r.D + e0;
+    dst = head < r.A + r.Kh ? r.k_cache + (long long)(head - r.A) * r.head_stride + row
+                            : r.v_cache + (long long)(head - r.A - r.Kh) * r.head_stride + row;
+  }
+#pragma unroll
+  for (int e = 0; e < CHUNK; e += 8) {
+    uint4 pk;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[e], v[e + 1]);
+    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[e + 2], v[e + 3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[e + 4], v[e + 5]);
+    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[e + 6], v[e + 7]);
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(dst + e) = pk;
+  }
+}
+
 // A chunk of a tile's epilogue with the row extras: scale, then sink or store.
 // Returns what the chunk adds to the token's sum of squares (epilogue 2, else 0).
 template <int CHUNK>
@@ -220,6 +296,10 @@ __device__ __forceinline__ float finish_chunk(const GemmParams& p, float (&v)[CH
     for (int e = 0; e < CHUNK; ++e) v[e] *= scale;
   }
   if (p.epilogue == 2) return sink_chunk<CHUNK>(p, v, i_global, j0);
+  if (p.epilogue == 3) {
+    rope_chunk<CHUNK>(p, v, i_global, j0);
+    return 0.f;
+  }
   store_chunk<CHUNK>(p, v, i_global, j0, lane, out_f, out_h);
   return 0.f;
 }

@@ -280,3 +280,35 @@ FB_API int fb_rope_kv_write(const void* src, int src_dtype, long long src_stride
 #undef FB_ROPE_LAUNCH
   return fb_check_launch("rope_kv_write");
 }
+
+// ---------------------------------------------------------------- the angles of a step
+// cs[i, t] = (cos, sin) of positions[t] * inv_freq[i], the product rounded once to 32
+// bits as above: what a product kernel that rotates in its epilogue reads instead of
+// computing the same angles once per head and layer. The positions are the same for
+// every layer of a step, so one table serves them all.
+__global__ void rope_table_kernel(const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int T, int half,
+                                  float2* __restrict__ cs) {
+  fb_pdl_launch();
+  fb_pdl_wait();
+  const long long n = (long long)T * half;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int i = (int)(idx / T), t = (int)(idx - (long long)i * T);  // tokens run fastest
+    float sn, c;
+    sincosf((float)positions[t] * inv_freq[i], &sn, &c);
+    cs[idx] = make_float2(c, sn);
+  }
+}
+
+FB_API int fb_rope_table(const int* positions, const float* inv_freq, int T, int half, void* cs,
+                         cudaStream_t stream) {
+  FB_REQUIRE(T >= 0 && half >= 0, "rope_table: bad sizes T=%d half=%d", T, half);
+  FB_REQUIRE(((uintptr_t)cs % 8) == 0, "rope_table: the table must be 8-byte aligned");
+  if (T == 0 || half == 0) return 0;
+  const long long n = (long long)T * half;
+  const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+  fb_launch(rope_table_kernel, dim3(blocks), dim3(256), 0, stream, positions, inv_freq, T, half,
+            (float2*)cs);
+  return fb_check_launch("rope_table");
+}

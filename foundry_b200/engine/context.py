@@ -63,6 +63,10 @@ class StepContext:
     # with the residual rows and a norm whose consumer takes it unscaled; the
     # part's last projection may then do both (set like `reads_after_part`).
     residual_sink: Optional[object] = None
+    # Tensors derived from the step that several parts share (the rotary angles of
+    # the step's positions, the same for every layer). Whoever runs another step on
+    # the same context clears it first (`Model.forward` does).
+    shared: Dict[object, torch.Tensor] = field(default_factory=dict)
 
     def page_table(self, group: KVGroup) -> torch.Tensor:
         """int32 [n_seqs, width]: the pages of each sequence in `group`."""

@@ -133,6 +133,9 @@ class Model:
     def forward(self, ctx, cache: SequenceCache) -> torch.Tensor:
         """Logits [wanted rows, vocab] in float32 for the step `ctx` describes."""
         spec = self.spec
+        shared = getattr(ctx, "shared", None)
+        if shared is not None:
+            shared.clear()  # what an earlier step on this context left
         resid = torch.empty((ctx.n_tokens, spec.hidden_size), dtype=torch.float32,
                             device=self.device)
         ops.embed_gather(self.embedding, ctx.token_ids, resid)

@@ -44,6 +44,11 @@ _SIGNATURES = {
                    c_int, c_int, c_ll, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int,
                    c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
                    c_void_p, c_ll, c_void_p, c_int, c_void_p],
+    "fb_gemm_tc_rope": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_ll,
+                        c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                        c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_ll,
+                        c_ll, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p],
+    "fb_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "fb_gemm_tc_status": [c_void_p],
     "fb_gemm_tc_pair_status": [c_void_p],
     "fb_gemm_skinny": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_int, c_int, c_int, c_int,
@@ -814,7 +819,88 @@ def gemm_rows_rope(x, w: torch.Tensor, positions: torch.Tensor, seq_of_token: to
     return q_out
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """float32 [frequencies, tokens, 2]: cos and sin of position * frequency, the
+    angle a 32-bit product as in the rotary kernels. One table serves every layer
+    of a step whose encodings share the frequencies."""
+    T, half = positions.numel(), inv_freq.numel()
+    cs = torch.empty((half, T, 2), dtype=torch.float32, device=positions.device)
+    _call("fb_rope_table", _dev(positions, "positions", torch.int32),
+          _dev(inv_freq, "inv_freq", torch.float32) if half else 0, T, half, cs.data_ptr(),
+          _stream())
+    return cs
+
+
+def qkv_tc_rope_fusable(x, w: torch.Tensor, rotary_dim: int, head_dim: int,
+                        k_cache: Optional[torch.Tensor], pairing: str) -> bool:
+    """Whether `gemm_tc_rope` takes this projection: more bfloat16 token rows than
+    the few-rows product takes, in a product form that is not split along K, heads
+    of whole 32-feature groups and a rotation of adjacent features."""
+    values = x.values if isinstance(x, RowScaled) else x
+    if not (FUSE_QKV_ROPE_MANY and values.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and pairing == "interleaved" and head_dim % 32 == 0 and rotary_dim % 2 == 0
+            and (k_cache is None or k_cache.dtype == torch.bfloat16)
+            and _tc_usable(values, w, values)):
+        return False
+    M, K = values.shape
+    # not where `gemm_bf16` would split K over CTAs (float32 planes): unsplit, those
+    # sizes run slower than the rotary kernel costs
+    splits, fits = _one_tile_plan(M, w.shape[0], K)
+    many = M > 128 and not (fits and M <= ONE_TILE_ROWS)
+    return many or splits == 1
+
+
+def gemm_tc_rope(x, w: torch.Tensor, cs: torch.Tensor, positions: torch.Tensor,
+                 seq_of_token: torch.Tensor, page_table: torch.Tensor, rotary_dim: int,
+                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                 num_heads: int, num_kv_heads: int, head_dim: int, ring_pages: int = 0,
+                 write_cache: bool = True) -> torch.Tensor:
+    """The fused q/k/v projection of many tokens on the token-major tcgen05
+    products, rotated and stored by their epilogue: queries come back, keys and
+    values go into the cache (see `gemm_skinny_rope`; the rotation pairs ADJACENT
+    features, `cs` is `rope_table`'s). The product's form is chosen as
+    `gemm_bf16` chooses it for these sizes."""
+    scale = _NO_SCALE
+    if isinstance(x, RowScaled):
+        scale, x = x.scales_args(), x.values
+    M, K = x.shape
+    rows = (num_heads + 2 * num_kv_heads) * head_dim
+    if w.shape != (rows, K):
+        raise KernelError(f"gemm_tc_rope: w is {tuple(w.shape)} for {num_heads}+2x{num_kv_heads} "
+                          f"heads of {head_dim} and K={K}")
+    if positions.numel() != M or seq_of_token.numel() != M or \
+            tuple(cs.shape) != (rotary_dim // 2, M, 2) or cs.dtype != torch.float32:
+        raise KernelError("gemm_tc_rope: positions / seq_of_token / the angle table do not fit")
+    q_out = torch.empty((M, num_heads * head_dim), dtype=torch.bfloat16, device=w.device)
+    kp = vp = page_stride = head_stride = 0
+    if write_cache:
+        _check_cache_views(k_cache, v_cache, num_kv_heads, head_dim, torch.bfloat16)
+        page_stride, head_stride = k_cache.stride(0), k_cache.stride(1)
+        kp, vp = k_cache.data_ptr(), v_cache.data_ptr()
+    else:
+        w = w[:num_heads * head_dim]  # keys and values are another layer's: not computed
+    N = w.shape[0]
+    splits, fits = _one_tile_plan(M, N, K)
+    many = M > 128 and not (fits and M <= ONE_TILE_ROWS and splits == 1)
+    bn, form = prompt_plan(M, N) if many else (128, 0)  # never split along K
+    scratch = (0, 0, 0, 0)
+    if form == 2 and PAIR_TAIL_SHARES:
+        work, counters = _pair_scratch(x.device)
+        scratch = (work.data_ptr(), work.numel() * 4, counters.data_ptr(), counters.numel())
+    _call("fb_gemm_tc_rope", _dev(x, "x", torch.bfloat16, contiguous=False), _rows(x, "x"), M,
+          _dev(w, "w", torch.bfloat16, contiguous=False), _rows(w, "w"), K, bn, form, *scratch,
+          PAIR_SHARE_MIN_KBLOCKS, *scale, cs.data_ptr(), rotary_dim // 2,
+          _dev(positions, "positions", torch.int32), _dev(seq_of_token, "seq_of_token", torch.int32),
+          _dev(page_table, "page_table", torch.int32), page_table.shape[1], ring_pages, kp, vp,
+          page_stride, head_stride, num_heads, num_kv_heads, head_dim, 1 if write_cache else 0,
+          q_out.data_ptr(), q_out.stride(0), _stream(),
+          tag=("m{} n{} k{} tile{}", M, N, K, bn))
+    return q_out
+
+
 FUSE_QKV_ROPE = _os.environ.get("FOUNDRY_B200_FUSE_QKV_ROPE", "1") != "0"
+# ... and in the token-major tcgen05 products' epilogue (prompt steps)
+FUSE_QKV_ROPE_MANY = _os.environ.get("FOUNDRY_B200_FUSE_QKV_ROPE_MANY", "1") != "0"
 ROPE_TRIGGER_PAGES = 64  # page-table width up to which the q/k/v product triggers its successor
 # the projections around a norm take the norm over (see `ResidualSink`, `RowScaled`)
 NORM_FUSION = _os.environ.get("FOUNDRY_B200_NORM_FUSION", "1") != "0"

@@ -51,11 +51,16 @@ class GQAAttention(Part):
         if position_encoding is None:
             self.rotary_dim = 0
             self.inv_freq = torch.zeros(0, dtype=torch.float32, device=device)
+            self.angles_key = ("rotary angles", b"")
             factor = 1.0
         else:
             enc = POSITION_ENCODINGS.build(position_encoding, dtype=dtype, device=device)
             self.rotary_dim, self.inv_freq, factor = enc.rotary_dim, enc.inv_freq, enc.attention_factor
             self.pairing = getattr(enc, "pairing", "half")
+            # layers whose encodings have the same frequencies share a step's angle table
+            # (an encoding without a host copy of its frequencies keeps a table of its own)
+            host = getattr(enc, "inv_freq_host", None)
+            self.angles_key = ("rotary angles", host.tobytes() if host is not None else id(enc))
         self.scale = factor / math.sqrt(head_dim)
 
     # ----------------------------------------------------------------- setup
@@ -120,6 +125,20 @@ class GQAAttention(Part):
                                    self.inv_freq, self.rotary_dim, cache.k, cache.v,
                                    self.num_heads, self.num_kv_heads, self.head_dim,
                                    ring_pages=cache.group.ring_pages, write_cache=cache.writes)
+        elif ops.qkv_tc_rope_fusable(x, self.qkv.weight, self.rotary_dim, self.head_dim, cache.k,
+                                     self.pairing):
+            # a prompt: the same in the epilogue of the products whose rows are tokens,
+            # with the step's angles from a table that the first layer of the step makes
+            shared = getattr(ctx, "shared", None)
+            cs = shared.get(self.angles_key) if shared is not None else None
+            if cs is None:
+                cs = ops.rope_table(ctx.positions, self.inv_freq)
+                if shared is not None:
+                    shared[self.angles_key] = cs
+            q = ops.gemm_tc_rope(x, self.qkv.weight, cs, ctx.positions, ctx.seq_of_token, table,
+                                 self.rotary_dim, cache.k, cache.v, self.num_heads,
+                                 self.num_kv_heads, self.head_dim,
+                                 ring_pages=cache.group.ring_pages, write_cache=cache.writes)
         else:
             # (a row-scaled input stays so: the tcgen05 products apply the scale)
             qkv = self.qkv.forward(x, allow_planes=True)  # a tensor or split-K planes

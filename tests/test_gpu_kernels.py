@@ -977,6 +977,87 @@ def test_gemm_rows_rope(ops, A, Kh, D, rot, T):
     assert ops.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("A,Kh,D,rot,T", [(4, 2, 64, 64, 130), (6, 2, 128, 128, 300), (3, 1, 32, 16, 200),
+                                          (8, 4, 64, 32, 700), (2, 2, 96, 0, 260), (24, 8, 128, 128, 520)])
+def test_gemm_tc_rope(ops, A, Kh, D, rot, T):
+    """Projection, rotation of adjacent feature pairs and cache write in the
+    epilogue of the products whose rows are tokens (one tile per CTA, and two SMs
+    per tile): far positions, padding tokens, scattered pages, partial and absent
+    rotation, a row-scaled input; without cache writes only the queries are
+    computed. Against the plain formulas in float64."""
+    K = 264 if A < 24 else 3072
+    positions = ([0, 1, 63, 64, 100000, 7] + list(range(200, 200 + T)))[:T]
+    seqs = ([0, 0, 1, 1, 2, -1] + [0] * T)[:T]
+    seqs[-1] = -1
+    width = (A + 2 * Kh) * D
+    n_pages = 1600
+    table = torch.zeros(3, 1563, dtype=torch.int32)
+    table[0, 0], table[1, 0], table[1, 1], table[2, 100000 // 64] = 5, 9, 2, 11
+    for i, lp in enumerate(range(3, (200 + T) // 64 + 1)):
+        table[0, lp] = 17 + 3 * i  # positions 200.. of sequence 0
+    inv_freq = (10000.0 ** (-np.arange(0, rot, 2, dtype=np.float32) / max(rot, 1))).astype(np.float32)
+    x, w = rnd(T, K, dtype=torch.bfloat16), rnd(width, K, dtype=torch.bfloat16, scale=0.1, seed=4)
+    ref = (x.double() @ w.double().T).cpu()
+    k_cache = torch.zeros(n_pages, Kh, 64, D, dtype=torch.bfloat16, device=DEV)
+    v_cache = torch.zeros_like(k_cache)
+    pos_d = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    freq_d = torch.from_numpy(inv_freq).to(DEV)
+    cs = ops.rope_table(pos_d, freq_d)
+    angle = (np.array(positions, dtype=np.float32)[:, None] * inv_freq[None, :]).astype(np.float32)
+    want_cs = np.stack([np.cos(angle.astype(np.float64)), np.sin(angle.astype(np.float64))], -1)
+    assert cs.shape == (rot // 2, T, 2)  # a frequency's angles of all tokens lie together
+    if rot:
+        assert float(np.abs(cs.cpu().numpy().transpose(1, 0, 2) - want_cs).max()) < 2e-6
+    args = (cs, pos_d, torch.tensor(seqs, dtype=torch.int32, device=DEV), table.to(DEV), rot)
+    assert ops.qkv_tc_rope_fusable(x, w, rot, D, k_cache, "interleaved")
+    q = ops.gemm_tc_rope(x, w, *args, k_cache, v_cache, A, Kh, D)
+    a, r = 2e-2, 8e-3
+    if K > 1000:
+        a = 6e-2
+    written = set()
+    for t in range(T):
+        if seqs[t] < 0:
+            continue
+        row = ref[t].view(A + 2 * Kh, D)
+        close(q[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot, "interleaved"), a, r)
+        page = int(table[seqs[t], positions[t] // 64])
+        written.add((page, positions[t] % 64))
+        close(k_cache[page, :, positions[t] % 64],
+              plain_rope(row[A:A + Kh], positions[t], inv_freq, rot, "interleaved"), a, r)
+        close(v_cache[page, :, positions[t] % 64], row[A + Kh:], a, r)
+    mask = torch.ones(n_pages, 64, dtype=torch.bool)
+    for p, rr in written:
+        mask[p, rr] = False
+    for cache in (k_cache, v_cache):
+        assert float(cache.float().abs().sum(dim=(1, 3)).cpu()[mask].max()) == 0.0
+    live = [t for t in range(T) if seqs[t] >= 0]
+    # the product followed by the rotary kernel rounds to 16 bits twice, this once: the
+    # two agree to three units of bfloat16's last place
+    qkv = ops.gemm_bf16(x, w)
+    k2, v2 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    q2 = ops.rope_kv_write(qkv, args[1], args[2], args[3], freq_d, rot, k2, v2, A, Kh, D,
+                           pairing="interleaved")
+    # (of the values that meet in a rotation, so of the largest of a token's row)
+    gap = (q2[live].float() - q[live].float()).abs().amax(dim=1)
+    assert bool((gap <= 3 * 2.0 ** -8 * q[live].float().abs().amax(dim=1)).all())
+    # a row-scaled input: the epilogue multiplies by the tokens' scales first
+    shares = torch.rand(3, T, device=DEV) + 0.5
+    scaled = ops.RowScaled(x, shares, 1e-5)
+    k3, v3 = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    q3 = ops.gemm_tc_rope(scaled, w, *args, k3, v3, A, Kh, D)
+    rstd = (1.0 / torch.sqrt(shares.double().sum(0) / K + 1e-5)).cpu()
+    for t in live[:40]:
+        row = (ref[t] * rstd[t]).view(A + 2 * Kh, D)
+        close(q3[t].view(A, D), plain_rope(row[:A], positions[t], inv_freq, rot, "interleaved"),
+              a * float(rstd[t]) + a, r)
+    # reading another layer's cache: no key or value is computed or stored
+    k_cache.zero_(), v_cache.zero_()
+    q4 = ops.gemm_tc_rope(x, w, *args, k_cache, v_cache, A, Kh, D, write_cache=False)
+    assert torch.equal(q4[live], q[live])
+    assert float(k_cache.float().abs().max()) == 0.0 and float(v_cache.float().abs().max()) == 0.0
+    assert ops.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("M,H,K", [(100, 200, 264), (128, 3072, 520), (300, 2048, 1024), (700, 3072, 8192),
                                    (2048, 3072, 3072), (2500, 1000, 264)])
 def test_gemm_many_rows_takes_the_norm_over(ops, monkeypatch, M, H, K):
