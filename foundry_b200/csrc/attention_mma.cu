@@ -131,6 +131,7 @@ struct AttnParams {
   int* counters; // [n_seqs, Kh]: CTAs that have delivered; zero between calls
   const void* next;      // constant data to bring into L2 for the kernel after this one
   long long next_bytes;  // 0 = none
+  int trigger_next;      // 1: let the next kernel's blocks be placed once a CTA's pages are in
 };
 
 // --------------------------------------------------------------------- prefill
@@ -709,6 +710,9 @@ attn_decode_kernel(const AttnParams p) {
   }
   cp_async_wait<0>();
   fb_prefetch_l2_slice(p.next, p.next_bytes);
+  // this CTA's pages are in: where the caller says so, the next kernel's blocks may be
+  // placed while the partial results are merged
+  if (p.trigger_next) fb_pdl_launch();
   // the lanes' shares of the sums meet: over the keys' lanes (g in the narrow form, t in the wide)
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -880,14 +884,17 @@ FB_API int fb_attention_prefill(const void* q, long long q_stride, void* out, lo
 // n_seqs*Kh ints that are zero when the call starts (the kernel leaves them zero
 // again); with one part per pair they are not used and may be null. `stages`
 // (2 or 3) is the number of page buffers per CTA. A sequence with kv_lens == 0
-// is padding: its output rows are zeros.
+// is padding: its output rows are zeros. `trigger_next`: see AttnParams (it pays in
+// front of the tcgen05 products and costs a third of the step in front of the
+// weight-streaming one, whose blocks then crowd in beside the attention's).
 FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                const int* cu_tokens, const int* kv_lens, const int* page_table,
                                int max_pages, const void* k_cache, const void* v_cache,
                                long long page_stride, long long head_stride, int n_seqs, int A,
                                int Kh, int D, float scale, int splits, int stages, int cluster,
                                float* ws_o, float* ws_ml, int* counters,
-                               const void* next, long long next_bytes, cudaStream_t stream) {
+                               const void* next, long long next_bytes, int trigger_next,
+                               cudaStream_t stream) {
   FB_REQUIRE(next_bytes >= 0 && next_bytes % 16 == 0 && ((uintptr_t)next % 16) == 0,
              "attention_decode: the prefetch range must be 16-byte aligned and a multiple of 16 bytes");
   int rc = check_common("attention_decode", n_seqs, A, Kh, D, q_stride, out_stride, q, k_cache,
@@ -912,6 +919,7 @@ FB_API int fb_attention_decode(const void* q, long long q_stride, void* out, lon
   p.splits = splits; p.cluster = cluster; p.parts = parts;
   p.ws_o = ws_o; p.ws_ml = ws_ml; p.counters = counters;
   p.next = next; p.next_bytes = next_bytes;
+  p.trigger_next = trigger_next ? 1 : 0;
   FB_REQUIRE(stages == 2 || stages == 3, "attention_decode: %d page buffers (2 or 3)", stages);
   if (stages == 2) {
     switch (D) {
@@ -998,5 +1006,5 @@ FB_API int fb_attention_decode_static(const void* q, long long q_stride, void* o
   float* ws_ml = ws_o + units * 16 * D;
   return fb_attention_decode(q, q_stride, out, out_stride, cu_tokens, kv_lens, page_table,
                              max_pages, k_cache, v_cache, page_stride, head_stride, n_seqs, A, Kh,
-                             D, scale, splits, 3, 1, ws_o, ws_ml, counters, nullptr, 0, stream);
+                             D, scale, splits, 3, 1, ws_o, ws_ml, counters, nullptr, 0, 0, stream);
 }

@@ -73,7 +73,7 @@ _SIGNATURES = {
     "fb_attention_decode": [c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_ll, c_ll, c_int, c_int, c_int, c_int, c_float,
                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_ll, c_void_p],
+                            c_ll, c_int, c_void_p],
     "fb_gemm_rows": [c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int,
                      c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_ll, c_void_p,
                      c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
@@ -1350,6 +1350,7 @@ def attention_decode(q, out, cu_tokens, kv_lens, page_table, k_cache, v_cache, n
           head_dim, float(scale), splits, stages, cluster,
           0 if ws_o is None else ws_o.data_ptr(), 0 if ws_ml is None else ws_ml.data_ptr(),
           0 if counters is None else counters.data_ptr(), *_prefetch_range(then_reads),
+          1 if n > SKINNY_ROWS else 0,  # what follows is a tcgen05 product, not the streaming one
           _stream())
     return out
 
