@@ -306,6 +306,12 @@ def run(args) -> dict:
     ms, mean_ctx = median_block(timed)
     step_bytes = decode_step_bytes(engine, mean_ctx)
     achieved = step_bytes / (ms * 1e-3) / 1e9
+    for s in slots:
+        engine.close_sequence(s)
+    # the end-to-end blocks on sequences of their own, centred on the same context
+    # length as the device-timed blocks (behind them they would read a longer cache)
+    first = max(1, CONTEXT * 3 // 4 - (blocks * e2e_steps + args.warmup) // 2)
+    slots = fill(engine, batch, first, seed=10 + batch)
     e2e_s, h2d, d2h = time_e2e(engine, slots, e2e_steps, args.warmup, blocks)
     for s in slots:
         engine.close_sequence(s)
