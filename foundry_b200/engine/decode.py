@@ -95,7 +95,8 @@ class DecodeRunner:
 
     def _body(self) -> None:
         engine = self.engine
-        self.logits = engine.model.forward(self.ctx, engine.cache)
+        with ops.scratch_owner(engine.scratch):
+            self.logits = engine.model.forward(self.ctx, engine.cache)
         b = self.bucket
         ops.select_tokens(self.logits, self.next_tokens, self.temperature, self.meta64[:b],
                           self.meta64[b:])

@@ -9,6 +9,8 @@ lengths and one shared position.
 """
 from __future__ import annotations
 
+import itertools
+import weakref
 from typing import List, Optional, Sequence
 
 import torch
@@ -26,6 +28,7 @@ from .decode import DecodeRunner, DecodeSession
 from .model import Model
 from ..kernels import ops
 
+_ENGINE_NUMBERS = itertools.count()
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "f32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -63,6 +66,9 @@ class Engine:
         self._graph_pool = None
         self._session = None
         self._prompts = None  # graphs of short prompt steps, made at the first one
+        # scratch memory that kernels share between their CTAs is this engine's own
+        self.scratch = ("engine", next(_ENGINE_NUMBERS))
+        weakref.finalize(self, ops.release_scratch, self.scratch)
 
     # ---------------------------------------------------------------- load
     @classmethod
@@ -151,7 +157,8 @@ class Engine:
         else:
             ctx = build_context(self.cache, steps, self.spec.vocab_size, self.device,
                                 self.spec.max_positions)
-            logits = self.model.forward(ctx, self.cache)
+            with ops.scratch_owner(self.scratch):
+                logits = self.model.forward(ctx, self.cache)
         if logits.shape[0]:
             # logits leave the engine: wait for them, and let none out after a
             # kernel gave up on a bounded wait

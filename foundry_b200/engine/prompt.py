@@ -104,7 +104,8 @@ class PromptRunner:
         self.fields.upload()
 
     def _body(self) -> None:
-        self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
+        with ops.scratch_owner(self.engine.scratch):
+            self.logits = self.engine.model.forward(self.ctx, self.engine.cache)
 
     def run(self) -> torch.Tensor:
         """One step over the buffers' contents; logits [want bucket, vocab] in a

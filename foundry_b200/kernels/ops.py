@@ -8,6 +8,7 @@ a reason to compute elsewhere.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Optional
 
 import os as _os
@@ -525,12 +526,47 @@ ONE_TILE_ROWS = int(_os.environ.get("FOUNDRY_B200_ONE_TILE_ROWS", "768"))
 PAIR_TAIL_SHARES = _os.environ.get("FOUNDRY_B200_PAIR_TAIL_SHARES", "1") != "0"
 PAIR_SHARE_MIN_KBLOCKS = 0  # K blocks of 64 a share keeps at least (0: the launcher's 32)
 _PAIR_SCRATCH = {}
+_SCRATCH_OWNER = threading.local()
+
+
+class scratch_owner:
+    """Within this block, kernels that need scratch memory between their CTAs
+    (the paired product's shares, decode attention's arrival counters) take the
+    scratch that belongs to `owner` (any hashable name): an engine runs its
+    steps inside one, so two engines on two streams never meet in one buffer.
+    Outside any block the scratch is the device's common one; calls that share a
+    scratch must follow one another on one stream."""
+
+    def __init__(self, owner):
+        self.owner = owner
+
+    def __enter__(self):
+        self.previous = getattr(_SCRATCH_OWNER, "key", None)
+        _SCRATCH_OWNER.key = self.owner
+        return self
+
+    def __exit__(self, *exc):
+        _SCRATCH_OWNER.key = self.previous
+        return False
+
+
+def release_scratch(owner) -> None:
+    """Forget the scratch of an owner that is gone."""
+    for table in (_PAIR_SCRATCH, _COUNTERS):
+        for key in [k for k in table if k[1] == owner]:
+            del table[key]
+
+
+def _scratch_key(device):
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return index, getattr(_SCRATCH_OWNER, "key", None)
 
 
 def _pair_scratch(device):
     """(float32 workspace for the partial tiles of one round: 74 tiles of
-    256 x 256; zeroed int32 counters, 8 per tile), one pair per device."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
+    256 x 256; zeroed int32 counters, 8 per tile), one pair per device and
+    scratch owner."""
+    key = _scratch_key(device)
     got = _PAIR_SCRATCH.get(key)
     if got is None:
         if torch.cuda.is_current_stream_capturing():
@@ -1359,13 +1395,14 @@ _COUNTERS = {}
 
 
 def _arrival_counters(device, count: int) -> torch.Tensor:
-    """Zeroed int32 counters shared by all decode-attention calls on a device:
-    each call finds them zero and leaves them zero (calls on one stream follow
-    one another, so sharing is safe there)."""
-    held = _COUNTERS.get(device)
+    """Zeroed int32 counters shared by the decode-attention calls of a device and
+    scratch owner: each call finds them zero and leaves them zero (an owner's
+    calls follow one another on one stream)."""
+    key = _scratch_key(device)
+    held = _COUNTERS.get(key)
     if held is None or held.numel() < count:
         held = torch.zeros(max(65536, count), dtype=torch.int32, device=device)
-        _COUNTERS[device] = held
+        _COUNTERS[key] = held
     return held
 
 

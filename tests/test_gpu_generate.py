@@ -134,6 +134,49 @@ def test_generation_ahead_with_stop_tokens_equals_the_plain_model(tiny_folders):
     engine.cache.table.check()
 
 
+def test_two_engines_on_two_streams_share_no_scratch(tiny_folders):
+    """Kernels that pass partial results between their CTAs take their scratch
+    from the engine that runs them: two engines working at the same time, each in
+    a thread and on a stream of its own, generate what each generates alone."""
+    import threading
+    from foundry_b200.kernels import ops
+    cfg, _ = plain.read_model(tiny_folders["tiny_b"])
+    V = cfg["vocab_size"]
+    prompts = [[tiny.random_tokens(300 + 7 * e + i, n, V) for i, n in enumerate((150, 9, 64))]
+               for e in range(2)]
+    engines = [engine_for(tiny_folders["tiny_b"], "bfloat16") for _ in range(2)]
+    assert engines[0].scratch != engines[1].scratch
+    alone = [e.generate(p, 24, eos_token_id=[]).token_ids for e, p in zip(engines, prompts)]
+    with ops.scratch_owner(engines[0].scratch):
+        a = ops._pair_scratch(torch.device("cuda:0"))[0]
+    with ops.scratch_owner(engines[1].scratch):
+        b = ops._pair_scratch(torch.device("cuda:0"))[0]
+    assert a.data_ptr() != b.data_ptr()
+    together, errors = [None, None], []
+
+    def work(i):
+        try:
+            with torch.cuda.stream(torch.cuda.Stream()):
+                for _ in range(3):
+                    together[i] = engines[i].generate(prompts[i], 24, eos_token_id=[]).token_ids
+                torch.cuda.current_stream().synchronize()
+        except Exception as exc:  # surfaces in the main thread below
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert together == alone
+    key = engines[1].scratch
+    del engines[1:]
+    import gc
+    gc.collect()
+    assert not [k for k in ops._PAIR_SCRATCH if k[1] == key]  # an engine's scratch goes with it
+
+
 def test_stop_tokens_early_rows_and_slot_reuse(tiny_folders):
     """Make a stop token of what the plain model generates third for one
     prompt: that row ends there (keeping the token) while the others go on,
