@@ -285,7 +285,11 @@ def run(args) -> dict:
     p_flops = step_flops(engine.model, [PREFILL_TOKENS])
     prefill = {"value": PREFILL_TOKENS / (p_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": p_ms,
                "frac": p_flops / (p_ms * 1e-3) / (tflops_burst * 1e12), "flops": p_flops,
-               "peak_tflops": tflops_burst}
+               "peak_tflops": tflops_burst,
+               # beside the burst peak (a product alone on a cool chip): the rate the same
+               # library product holds in a seconds-long loop under the power cap
+               "frac_of_sustained": p_flops / (p_ms * 1e-3) / (tflops_sustained * 1e12),
+               "peak_tflops_sustained": tflops_sustained}
 
     # ----------------------------------------------------------------- decode
     # the timed blocks are centred on 3/4 of the context: the mean of decoding from
