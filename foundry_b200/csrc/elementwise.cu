@@ -12,10 +12,26 @@
 //              (src/nn/activation.rs:18-27, src/models/llama/mlp.rs:56)
 #include "common.cuh"
 
+// Four consecutive elements as float32.
+template <typename TD>
+__device__ __forceinline__ float4 load4(const TD* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // ------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H, int V) {
+  fb_pdl_launch();  // a few small blocks: the norm behind them may be placed at once
   fb_pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -25,6 +41,24 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     return;
   }
   const T* src = table + (size_t)id * H;
+  if (H % 4 == 0 && (((uintptr_t)src | (uintptr_t)dst) % 16) == 0) {
+    // groups of four elements; a thread's loads all go out before its first store
+    constexpr int AHEAD = 4;
+    for (int i0 = threadIdx.x * 4; i0 < H; i0 += blockDim.x * 4 * AHEAD) {
+      float4 v[AHEAD];
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a) {
+        const int i = i0 + a * blockDim.x * 4;
+        if (i < H) v[a] = load4<T>(src + i);
+      }
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a) {
+        const int i = i0 + a * blockDim.x * 4;
+        if (i < H) *reinterpret_cast<float4*>(dst + i) = v[a];
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = fb_to_float<T>(src[i]);
 }
 
@@ -47,19 +81,6 @@ FB_API int fb_embed_gather(const void* table, int table_dtype, const int* ids, f
 // Each thread owns up to ITEMS groups of four consecutive elements; all loads of
 // a group (the residual and every plane) are issued before any is used, so a
 // row costs one round trip to memory, one block reduction and one store.
-template <typename TD>
-__device__ __forceinline__ float4 load4(const TD* p);
-template <>
-__device__ __forceinline__ float4 load4<float>(const float* p) {
-  return *reinterpret_cast<const float4*>(p);
-}
-template <>
-__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(p);
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-  return make_float4(a.x, a.y, b.x, b.y);
-}
 // Four elements as they lie in memory (bfloat16: two registers instead of four
 // while they wait for their use), and their float32 values.
 template <typename TD> struct Raw4;
