@@ -49,15 +49,28 @@ select_tokens_kernel(const float* logits, long long row_stride, int V, int chunk
   const int lo = c * chunk, hi = min(V, lo + chunk);
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    float v = row[i];
-    if (!greedy) {
-      const float u = uniform24(stream, step, (unsigned long long)i);
-      v = v * inv_t - logf(-logf(u));
+  // a thread's next eight values are asked for together, then compared in order
+  constexpr int AHEAD = 8;
+  for (int i0 = lo + threadIdx.x; i0 < hi; i0 += blockDim.x * AHEAD) {
+    float got[AHEAD];
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      const int i = i0 + a * (int)blockDim.x;
+      got[a] = i < hi ? row[i] : 0.f;
     }
-    // indices ascend within a thread, so `>` keeps the first of equal values;
-    // a NaN compares false and never wins
-    if (v == v && (bi == 0x7fffffff || v > bv)) { bv = v; bi = i; }
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      const int i = i0 + a * (int)blockDim.x;
+      if (i >= hi) break;
+      float v = got[a];
+      if (!greedy) {
+        const float u = uniform24(stream, step, (unsigned long long)i);
+        v = v * inv_t - logf(-logf(u));
+      }
+      // indices ascend within a thread, so `>` keeps the first of equal values;
+      // a NaN compares false and never wins
+      if (v == v && (bi == 0x7fffffff || v > bv)) { bv = v; bi = i; }
+    }
   }
   // reduce (value, index): larger value, then lower index
 #pragma unroll
